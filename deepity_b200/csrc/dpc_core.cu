@@ -1,0 +1,750 @@
+// Context, memory, CUDA graphs, plans and the phase entry points of the dpc_* C ABI.
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "dpc_internal.h"
+#include "dpc_simt.cuh"
+
+namespace dpc
+{
+static thread_local std::string g_error;
+
+void set_error(const std::string& msg)
+{
+  g_error = msg;
+}
+int fail(int code, const std::string& msg)
+{
+  g_error = msg;
+  return code;
+}
+int cuda_fail(cudaError_t err, const char* what)
+{
+  g_error = std::string(what) + ": " + cudaGetErrorString(err);
+  return err == cudaErrorNoDevice || err == cudaErrorInsufficientDriver ? DPC_ERR_NO_DEVICE
+                                                                         : DPC_ERR_CUDA;
+}
+
+static int check_launch(dpc_ctx* ctx, const char* what)
+{
+  ctx->launches += 1;
+  cudaError_t err = cudaPeekAtLastError();
+  if (err != cudaSuccess)
+    return cuda_fail(cudaGetLastError(), what);
+  return DPC_OK;
+}
+
+static int check_range(dpc_plan* p, int first, int count)
+{
+  if (!p)
+    return fail(DPC_ERR_INVALID, "null plan");
+  if (first < 0 || count < 0 || first + count > p->n)
+    return fail(DPC_ERR_INVALID, "layer range out of bounds");
+  return DPC_OK;
+}
+
+static inline int cdiv(int a, int b)
+{
+  return (a + b - 1) / b;
+}
+
+// Largest GEMM tile grid over a range for the given op.
+static void max_tiles(const dpc_plan* p, int first, int count, int op, int& tx, int& ty)
+{
+  tx = ty = 0;
+  for (int i = first; i < first + count; ++i)
+  {
+    const dpc_layer& L = p->h[i];
+    if (L.next_size <= 0)
+      continue;
+    int M, N;
+    if (op == OP_FWD)
+      M = p->batch, N = L.next_size;
+    else if (op == OP_FB)
+      M = p->batch, N = L.size;
+    else
+      M = L.next_size, N = L.size;
+    tx = std::max(tx, cdiv(N, BN));
+    ty = std::max(ty, cdiv(M, BM));
+  }
+}
+
+static int elem_blocks(const dpc_plan* p, size_t max_elems)
+{
+  size_t blocks = (max_elems + 1023) / 1024; // 256 threads x 4 elements each
+  size_t cap = (size_t)p->ctx->sm_count * 8;
+  if (blocks > cap)
+    blocks = cap;
+  return (int)std::max<size_t>(blocks, 1);
+}
+
+constexpr int kMaxZ = 32768; // layers per launch (gridDim.y/z limit is 65535)
+} // namespace dpc
+
+using namespace dpc;
+
+// The C linkage of every dpc_* definition below comes from its declaration in
+// deepity_b200.h.
+const char* dpc_last_error(void)
+{
+  return g_error.c_str();
+}
+
+const char* dpc_version(void)
+{
+  return "deepity_b200 0.1 (sm_100a)";
+}
+
+int dpc_create(int device, dpc_ctx** out)
+{
+  if (!out)
+    return fail(DPC_ERR_INVALID, "dpc_create: null out");
+  int n = 0;
+  cudaError_t err = cudaGetDeviceCount(&n);
+  if (err != cudaSuccess || n == 0)
+  {
+    cudaGetLastError();
+    return fail(DPC_ERR_NO_DEVICE, "no CUDA device available (this library has no CPU fallback)");
+  }
+  if (device < 0 || device >= n)
+    return fail(DPC_ERR_INVALID, "dpc_create: device index out of range");
+  DPC_CUDA(cudaSetDevice(device));
+  auto* ctx = new dpc_ctx();
+  ctx->device = device;
+  cudaDeviceProp prop;
+  DPC_CUDA(cudaGetDeviceProperties(&prop, device));
+  ctx->sm_count = prop.multiProcessorCount;
+  DPC_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+  *out = ctx;
+  return DPC_OK;
+}
+
+int dpc_destroy(dpc_ctx* ctx)
+{
+  if (!ctx)
+    return DPC_OK;
+  cudaSetDevice(ctx->device);
+  for (int s = 0; s < dpc_ctx::kSlots; ++s)
+  {
+    if (ctx->execs[s])
+      cudaGraphExecDestroy(ctx->execs[s]);
+    if (ctx->graphs[s])
+      cudaGraphDestroy(ctx->graphs[s]);
+  }
+  if (ctx->stream)
+  {
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamDestroy(ctx->stream);
+  }
+  delete ctx;
+  return DPC_OK;
+}
+
+int dpc_set_precision(dpc_ctx* ctx, int precision)
+{
+  if (!ctx || (precision != DPC_PRECISION_FP32 && precision != DPC_PRECISION_TF32))
+    return fail(DPC_ERR_INVALID, "dpc_set_precision: bad argument");
+  ctx->precision = precision;
+  return DPC_OK;
+}
+
+int dpc_get_precision(dpc_ctx* ctx)
+{
+  return ctx ? ctx->precision : DPC_ERR_INVALID;
+}
+
+void* dpc_stream(dpc_ctx* ctx)
+{
+  return ctx ? (void*)ctx->stream : nullptr;
+}
+
+int64_t dpc_launch_count(dpc_ctx* ctx)
+{
+  return ctx ? ctx->launches : 0;
+}
+
+int dpc_alloc(dpc_ctx* ctx, size_t bytes, void** out)
+{
+  if (!ctx || !out)
+    return fail(DPC_ERR_INVALID, "dpc_alloc: null argument");
+  DPC_CUDA(cudaSetDevice(ctx->device));
+  DPC_CUDA(cudaMalloc(out, bytes ? bytes : 16));
+  return DPC_OK;
+}
+
+int dpc_free(dpc_ctx* ctx, void* ptr)
+{
+  if (!ctx)
+    return fail(DPC_ERR_INVALID, "dpc_free: null context");
+  if (ptr)
+    DPC_CUDA(cudaFree(ptr));
+  return DPC_OK;
+}
+
+int dpc_zero(dpc_ctx* ctx, void* ptr, size_t bytes)
+{
+  if (!ctx || (!ptr && bytes))
+    return fail(DPC_ERR_INVALID, "dpc_zero: null argument");
+  DPC_CUDA(cudaMemsetAsync(ptr, 0, bytes, ctx->stream));
+  return DPC_OK;
+}
+
+int dpc_copy_d2d(dpc_ctx* ctx, void* dst, const void* src, size_t bytes)
+{
+  if (!ctx)
+    return fail(DPC_ERR_INVALID, "null context");
+  DPC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return DPC_OK;
+}
+
+int dpc_copy_h2d(dpc_ctx* ctx, void* dst, const void* host_src, size_t bytes)
+{
+  if (!ctx)
+    return fail(DPC_ERR_INVALID, "null context");
+  DPC_CUDA(cudaMemcpyAsync(dst, host_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return DPC_OK;
+}
+
+int dpc_copy_d2h(dpc_ctx* ctx, void* host_dst, const void* src, size_t bytes)
+{
+  if (!ctx)
+    return fail(DPC_ERR_INVALID, "null context");
+  DPC_CUDA(cudaMemcpyAsync(host_dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return DPC_OK;
+}
+
+int dpc_copy_h2d_sync(dpc_ctx* ctx, void* dst, const void* host_src, size_t bytes)
+{
+  int rc = dpc_copy_h2d(ctx, dst, host_src, bytes);
+  if (rc != DPC_OK)
+    return rc;
+  DPC_CUDA(cudaStreamSynchronize(ctx->stream));
+  return DPC_OK;
+}
+
+int dpc_copy_d2h_sync(dpc_ctx* ctx, void* host_dst, const void* src, size_t bytes)
+{
+  int rc = dpc_copy_d2h(ctx, host_dst, src, bytes);
+  if (rc != DPC_OK)
+    return rc;
+  DPC_CUDA(cudaStreamSynchronize(ctx->stream));
+  return DPC_OK;
+}
+
+int dpc_alloc_host(dpc_ctx* ctx, size_t bytes, void** out)
+{
+  if (!ctx || !out)
+    return fail(DPC_ERR_INVALID, "dpc_alloc_host: null argument");
+  DPC_CUDA(cudaMallocHost(out, bytes ? bytes : 16));
+  return DPC_OK;
+}
+
+int dpc_free_host(dpc_ctx* ctx, void* ptr)
+{
+  (void)ctx;
+  if (ptr)
+    DPC_CUDA(cudaFreeHost(ptr));
+  return DPC_OK;
+}
+
+int dpc_sync(dpc_ctx* ctx)
+{
+  if (!ctx)
+    return fail(DPC_ERR_INVALID, "null context");
+  DPC_CUDA(cudaStreamSynchronize(ctx->stream));
+  return DPC_OK;
+}
+
+int dpc_graph_begin(dpc_ctx* ctx, int slot)
+{
+  if (!ctx || slot < 0 || slot >= dpc_ctx::kSlots)
+    return fail(DPC_ERR_INVALID, "dpc_graph_begin: bad slot");
+  if (ctx->capturing_slot >= 0)
+    return fail(DPC_ERR_STATE, "dpc_graph_begin: a capture is already open");
+  DPC_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+  ctx->capturing_slot = slot;
+  ctx->launches_at_begin = ctx->launches;
+  return DPC_OK;
+}
+
+int dpc_graph_end(dpc_ctx* ctx, int slot)
+{
+  if (!ctx || slot != ctx->capturing_slot)
+    return fail(DPC_ERR_STATE, "dpc_graph_end: slot does not match the open capture");
+  ctx->capturing_slot = -1;
+  // Recorded launches run when the graph is replayed, not now.
+  ctx->graph_kernels[slot] = ctx->launches - ctx->launches_at_begin;
+  ctx->launches = ctx->launches_at_begin;
+  cudaGraph_t graph = nullptr;
+  DPC_CUDA(cudaStreamEndCapture(ctx->stream, &graph));
+  if (ctx->execs[slot])
+    cudaGraphExecDestroy(ctx->execs[slot]);
+  if (ctx->graphs[slot])
+    cudaGraphDestroy(ctx->graphs[slot]);
+  ctx->execs[slot] = nullptr;
+  ctx->graphs[slot] = graph;
+  DPC_CUDA(cudaGraphInstantiate(&ctx->execs[slot], graph, 0));
+  return DPC_OK;
+}
+
+int dpc_graph_launch(dpc_ctx* ctx, int slot)
+{
+  if (!ctx || slot < 0 || slot >= dpc_ctx::kSlots || !ctx->execs[slot])
+    return fail(DPC_ERR_STATE, "dpc_graph_launch: nothing captured in this slot");
+  DPC_CUDA(cudaGraphLaunch(ctx->execs[slot], ctx->stream));
+  ctx->launches += ctx->graph_kernels[slot];
+  return DPC_OK;
+}
+
+int dpc_graph_drop(dpc_ctx* ctx, int slot)
+{
+  if (!ctx || slot < 0 || slot >= dpc_ctx::kSlots)
+    return fail(DPC_ERR_INVALID, "dpc_graph_drop: bad slot");
+  if (ctx->execs[slot])
+    cudaGraphExecDestroy(ctx->execs[slot]);
+  if (ctx->graphs[slot])
+    cudaGraphDestroy(ctx->graphs[slot]);
+  ctx->execs[slot] = nullptr;
+  ctx->graphs[slot] = nullptr;
+  return DPC_OK;
+}
+
+// ------------------------------------------------------------------------------ plans
+static int validate_layers(const dpc_layer* layers, int n, int batch)
+{
+  if (!layers || n < 2 || batch <= 0)
+    return fail(DPC_ERR_INVALID, "plan: need at least two layers and a positive batch");
+  for (int i = 0; i < n; ++i)
+  {
+    const dpc_layer& L = layers[i];
+    if (L.size <= 0 || !L.z || !L.e)
+      return fail(DPC_ERR_INVALID, "plan: layer " + std::to_string(i) + " lacks z/e or size");
+    if (i + 1 < n)
+    {
+      if (L.next_size != layers[i + 1].size)
+        return fail(DPC_ERR_INVALID, "plan: next_size of layer " + std::to_string(i) +
+                                         " does not match the size of the layer above");
+      if (!L.W || !L.b || !L.mu)
+        return fail(DPC_ERR_INVALID, "plan: layer " + std::to_string(i) + " lacks W/b/mu");
+      const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+      if (!simple && (!L.preact || !L.fe))
+        return fail(DPC_ERR_INVALID, "plan: layer " + std::to_string(i) + " lacks preact/fe");
+      if (simple && !L.zF)
+        return fail(DPC_ERR_INVALID, "plan: SimplePC layer " + std::to_string(i) + " lacks zF");
+      if ((L.flags & DPC_LAYER_RESIDUAL) && L.size != L.next_size)
+        return fail(DPC_ERR_INVALID, "plan: residual layer must be square");
+      if (L.opt != DPC_OPT_SGD && (!L.m_W || !L.v_W || !L.m_b || !L.v_b || !L.t))
+        return fail(DPC_ERR_INVALID, "plan: Adam state missing on layer " + std::to_string(i));
+      if (L.Psi && L.opt_psi != DPC_OPT_SGD && (!L.m_Psi || !L.v_Psi || !L.t_Psi))
+        return fail(DPC_ERR_INVALID, "plan: Psi Adam state missing on layer " + std::to_string(i));
+      if (L.Psi && (L.psi_stride < L.terminal_size || L.terminal_size != layers[n - 1].size))
+        return fail(DPC_ERR_INVALID, "plan: terminal_size / psi_stride mismatch on layer " +
+                                         std::to_string(i));
+    }
+    else if (L.next_size != 0)
+      return fail(DPC_ERR_INVALID, "plan: the last layer must be the weight-less terminal layer");
+  }
+  return DPC_OK;
+}
+
+int dpc_plan_create(dpc_ctx* ctx, const dpc_layer* layers, int n_layers, int batch,
+                    dpc_plan** out)
+{
+  if (!ctx || !out)
+    return fail(DPC_ERR_INVALID, "dpc_plan_create: null argument");
+  int rc = validate_layers(layers, n_layers, batch);
+  if (rc != DPC_OK)
+    return rc;
+  auto* p = new dpc_plan();
+  p->ctx = ctx;
+  p->n = n_layers;
+  p->batch = batch;
+  p->h.assign(layers, layers + n_layers);
+  cudaError_t err = cudaMalloc(&p->d, sizeof(dpc_layer) * n_layers);
+  if (err == cudaSuccess)
+    err = cudaMalloc(&p->energy, sizeof(double));
+  if (err == cudaSuccess)
+    err = cudaMallocHost(&p->energy_host, sizeof(double));
+  if (err == cudaSuccess)
+    err = cudaMemcpy(p->d, layers, sizeof(dpc_layer) * n_layers, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess)
+    err = cudaMemset(p->energy, 0, sizeof(double));
+  if (err != cudaSuccess)
+  {
+    dpc_plan_destroy(p);
+    return cuda_fail(err, "dpc_plan_create");
+  }
+  rc = tc_plan_init(p);
+  if (rc < 0)
+  {
+    dpc_plan_destroy(p);
+    return rc;
+  }
+  *out = p;
+  return DPC_OK;
+}
+
+int dpc_plan_update(dpc_plan* p, const dpc_layer* layers, int n_layers)
+{
+  if (!p || n_layers != p->n)
+    return fail(DPC_ERR_INVALID, "dpc_plan_update: layer count differs from the plan");
+  int rc = validate_layers(layers, n_layers, p->batch);
+  if (rc != DPC_OK)
+    return rc;
+  DPC_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  p->h.assign(layers, layers + n_layers);
+  DPC_CUDA(cudaMemcpy(p->d, layers, sizeof(dpc_layer) * n_layers, cudaMemcpyHostToDevice));
+  tc_plan_free(p);
+  rc = tc_plan_init(p);
+  return rc < 0 ? rc : DPC_OK;
+}
+
+int dpc_plan_destroy(dpc_plan* p)
+{
+  if (!p)
+    return DPC_OK;
+  tc_plan_free(p);
+  if (p->d)
+    cudaFree(p->d);
+  if (p->energy)
+    cudaFree(p->energy);
+  if (p->energy_host)
+    cudaFreeHost(p->energy_host);
+  delete p;
+  return DPC_OK;
+}
+
+int dpc_plan_tensor_run(dpc_plan* p, int* first, int* count)
+{
+  if (!p)
+    return fail(DPC_ERR_INVALID, "null plan");
+  if (first)
+    *first = p->run.first;
+  if (count)
+    *count = p->run.count;
+  return DPC_OK;
+}
+
+// ------------------------------------------------------------------------------ phases
+static int forward_simt(dpc_plan* p, int first, int count, int flags)
+{
+  cudaStream_t st = p->ctx->stream;
+  for (int f = first; f < first + count; f += kMaxZ)
+  {
+    const int c = std::min(kMaxZ, first + count - f);
+    if (flags & DPC_FWD_CACHED)
+    {
+      size_t mx = 0;
+      for (int i = f; i < f + c; ++i)
+        mx = std::max(mx, (size_t)p->batch * std::max(p->h[i].next_size, 0));
+      dim3 grid(elem_blocks(p, mx), c);
+      cached_forward_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, flags, p->energy);
+    }
+    else
+    {
+      int tx, ty;
+      max_tiles(p, f, c, OP_FWD, tx, ty);
+      if (tx == 0)
+        continue;
+      dim3 grid(tx, ty, c);
+      pc_gemm_kernel<OP_FWD><<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, flags, 0,
+                                                       p->energy);
+    }
+    int rc = check_launch(p->ctx, "forward kernel");
+    if (rc != DPC_OK)
+      return rc;
+  }
+  return DPC_OK;
+}
+
+// Splits [first, first+count) into the part the tensor-core path takes and the rest.
+template <typename TcFn, typename SimtFn>
+static int dispatch_range(dpc_plan* p, int first, int count, TcFn tc, SimtFn simt)
+{
+  if (count == 0)
+    return DPC_OK;
+  const int r0 = std::max(first, p->run.first);
+  const int r1 = std::min(first + count, p->run.first + p->run.count);
+  if (p->run.count > 0 && r1 > r0)
+  {
+    int rc = tc(r0, r1 - r0);
+    if (rc < 0)
+      return rc;
+    if (rc == DPC_OK)
+    {
+      if (r0 > first && (rc = simt(first, r0 - first)) != DPC_OK)
+        return rc;
+      if (first + count > r1 && (rc = simt(r1, first + count - r1)) != DPC_OK)
+        return rc;
+      return DPC_OK;
+    }
+  }
+  return simt(first, count);
+}
+
+int dpc_forward(dpc_plan* p, int first, int count, int flags)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK)
+    return rc;
+  if (flags & DPC_FWD_CACHED)
+    return forward_simt(p, first, count, flags);
+  return dispatch_range(
+      p, first, count, [&](int f, int c) { return tc_forward(p, f, c, flags); },
+      [&](int f, int c) { return forward_simt(p, f, c, flags); });
+}
+
+int dpc_project_forward(dpc_plan* p, int first, int count, int skip_last_copy)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK)
+    return rc;
+  for (int i = first; i < first + count; ++i)
+  {
+    if (p->h[i].next_size <= 0)
+      continue;
+    int flags = DPC_FWD_COPY_NEXT;
+    if (skip_last_copy && i + 2 == p->n)
+      flags = 0;
+    rc = dpc_forward(p, i, 1, flags);
+    if (rc != DPC_OK)
+      return rc;
+  }
+  return DPC_OK;
+}
+
+int dpc_error(dpc_plan* p, int layer, int with_energy)
+{
+  int rc = check_range(p, layer, 1);
+  if (rc != DPC_OK)
+    return rc;
+  if (layer == 0)
+    return fail(DPC_ERR_INVALID, "dpc_error: the input layer has no prediction below it");
+  const dpc_layer& L = p->h[layer];
+  cudaStream_t st = p->ctx->stream;
+  if (L.flags & DPC_LAYER_SOFTMAX_CE)
+  {
+    int blocks = std::min(cdiv(p->batch, NTHREADS / 32), p->ctx->sm_count * 8);
+    softmax_ce_kernel<<<blocks, NTHREADS, 0, st>>>(p->d, layer, p->batch, with_energy, p->energy);
+  }
+  else
+  {
+    error_kernel<<<elem_blocks(p, (size_t)p->batch * L.size), NTHREADS, 0, st>>>(
+        p->d, layer, p->batch, with_energy, p->energy);
+  }
+  return check_launch(p->ctx, "error kernel");
+}
+
+int dpc_feedback_error(dpc_plan* p, int first, int count)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK || count == 0)
+    return rc;
+  for (int f = first; f < first + count; f += kMaxZ)
+  {
+    const int c = std::min(kMaxZ, first + count - f);
+    size_t mx = 0;
+    for (int i = f; i < f + c; ++i)
+      mx = std::max(mx, (size_t)p->batch * std::max(p->h[i].next_size, 0));
+    dim3 grid(elem_blocks(p, mx), c);
+    feedback_error_kernel<<<grid, NTHREADS, 0, p->ctx->stream>>>(p->d, f, p->n, p->batch);
+    if ((rc = check_launch(p->ctx, "feedback_error kernel")) != DPC_OK)
+      return rc;
+  }
+  return DPC_OK;
+}
+
+static int update_state_simt(dpc_plan* p, int first, int count)
+{
+  cudaStream_t st = p->ctx->stream;
+  for (int f = first; f < first + count; f += kMaxZ)
+  {
+    const int c = std::min(kMaxZ, first + count - f);
+    int tx, ty;
+    // Layers whose upper neighbour does not exist are handled by the relax kernel below.
+    int cg = (f + c == p->n) ? c - 1 : c;
+    if (cg > 0)
+    {
+      max_tiles(p, f, cg, OP_FB, tx, ty);
+      if (tx > 0)
+      {
+        dim3 grid(tx, ty, cg);
+        pc_gemm_kernel<OP_FB><<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, 0, 0, p->energy);
+        int rc = check_launch(p->ctx, "update_state kernel");
+        if (rc != DPC_OK)
+          return rc;
+      }
+    }
+    bool any_weightless = false;
+    size_t mx = 0;
+    for (int i = f; i < f + c; ++i)
+      if (p->h[i].next_size <= 0 || i + 1 >= p->n)
+      {
+        any_weightless = true;
+        mx = std::max(mx, (size_t)p->batch * p->h[i].size);
+      }
+    if (any_weightless)
+    {
+      dim3 grid(elem_blocks(p, mx), c);
+      relax_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, 1);
+      int rc = check_launch(p->ctx, "relax kernel");
+      if (rc != DPC_OK)
+        return rc;
+    }
+  }
+  return DPC_OK;
+}
+
+int dpc_update_state(dpc_plan* p, int first, int count)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK)
+    return rc;
+  return dispatch_range(
+      p, first, count, [&](int f, int c) { return tc_update_state(p, f, c); },
+      [&](int f, int c) { return update_state_simt(p, f, c); });
+}
+
+int dpc_relax(dpc_plan* p, int layer)
+{
+  int rc = check_range(p, layer, 1);
+  if (rc != DPC_OK)
+    return rc;
+  dim3 grid(elem_blocks(p, (size_t)p->batch * p->h[layer].size), 1);
+  relax_kernel<<<grid, NTHREADS, 0, p->ctx->stream>>>(p->d, layer, p->n, p->batch, 0);
+  return check_launch(p->ctx, "relax kernel");
+}
+
+static int weight_gemm_simt(dpc_plan* p, int first, int count, int mode, int flags)
+{
+  for (int f = first; f < first + count; f += kMaxZ)
+  {
+    const int c = std::min(kMaxZ, first + count - f);
+    int tx, ty;
+    max_tiles(p, f, c, OP_WG, tx, ty);
+    if (tx == 0)
+      continue;
+    dim3 grid(tx, ty, c);
+    pc_gemm_kernel<OP_WG><<<grid, NTHREADS, 0, p->ctx->stream>>>(p->d, f, p->n, p->batch, flags,
+                                                                mode, p->energy);
+    int rc = check_launch(p->ctx, "weight kernel");
+    if (rc != DPC_OK)
+      return rc;
+  }
+  return DPC_OK;
+}
+
+int dpc_direct_feedback(dpc_plan* p, int first, int count, int decay_w)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK || count == 0)
+    return rc;
+  // Only layers with an upper neighbour can take part.
+  if (first + count == p->n)
+    count -= 1;
+  if (count <= 0)
+    return DPC_OK;
+  cudaStream_t st = p->ctx->stream;
+  for (int f = first; f < first + count; f += kMaxZ)
+  {
+    const int c = std::min(kMaxZ, first + count - f);
+    size_t mx = 0;
+    for (int i = f; i < f + c; ++i)
+      mx = std::max(mx, (size_t)p->batch * std::max(p->h[i].next_size, 0));
+    dim3 grid(elem_blocks(p, mx), c);
+    dfa_proj_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch);
+    if ((rc = check_launch(p->ctx, "dfa_proj kernel")) != DPC_OK)
+      return rc;
+  }
+  const int flags = decay_w ? 1 : 0;
+  if (!decay_w)
+  {
+    return dispatch_range(
+        p, first, count, [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_DFA); },
+        [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA, flags); });
+  }
+  return weight_gemm_simt(p, first, count, WG_DFA, flags);
+}
+
+int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK || count == 0)
+    return rc;
+  if (first + count == p->n)
+    count -= 1;
+  if (count <= 0)
+    return DPC_OK;
+  cudaStream_t st = p->ctx->stream;
+  bool any_adam = false, any_psi = false;
+  int max_next = 0, max_size = 0;
+  for (int i = first; i < first + count; ++i)
+  {
+    const dpc_layer& L = p->h[i];
+    any_adam |= L.opt != DPC_OPT_SGD || (L.Psi && L.opt_psi != DPC_OPT_SGD);
+    any_psi |= L.Psi != nullptr && !(L.flags & DPC_LAYER_INPUT_ACT);
+    max_next = std::max(max_next, L.next_size);
+    max_size = std::max(max_size, L.size);
+  }
+  if (any_adam)
+  {
+    bump_counters_kernel<<<cdiv(count, 256), 256, 0, st>>>(p->d, first, count, p->n);
+    if ((rc = check_launch(p->ctx, "bump_counters kernel")) != DPC_OK)
+      return rc;
+  }
+  rc = dispatch_range(
+      p, first, count,
+      [&](int f, int c)
+      {
+        for (int i = f; i < f + c; ++i)
+          if (p->h[i].opt != DPC_OPT_SGD)
+            return 1;
+        return tc_weight_gemm(p, f, c, WG_LEARN);
+      },
+      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_LEARN, 0); });
+  if (rc != DPC_OK)
+    return rc;
+  for (int f = first; f < first + count; f += kMaxZ)
+  {
+    const int c = std::min(kMaxZ, first + count - f);
+    dim3 gb(std::max(1, cdiv(max_next, 128)), c);
+    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch);
+    if ((rc = check_launch(p->ctx, "bias_update kernel")) != DPC_OK)
+      return rc;
+    if (any_psi)
+    {
+      dim3 gp(std::max(1, cdiv(max_size, 128)), c);
+      psi_update_kernel<<<gp, 128, 0, st>>>(p->d, f, p->n, p->batch);
+      if ((rc = check_launch(p->ctx, "psi_update kernel")) != DPC_OK)
+        return rc;
+    }
+    if (center_rows)
+    {
+      dim3 gc(std::min(max_next, 1024), c);
+      center_rows_kernel<<<gc, 256, 0, st>>>(p->d, f, p->n);
+      if ((rc = check_launch(p->ctx, "center_rows kernel")) != DPC_OK)
+        return rc;
+    }
+  }
+  return DPC_OK;
+}
+
+int dpc_energy_reset(dpc_plan* p)
+{
+  if (!p)
+    return fail(DPC_ERR_INVALID, "null plan");
+  DPC_CUDA(cudaMemsetAsync(p->energy, 0, sizeof(double), p->ctx->stream));
+  return DPC_OK;
+}
+
+int dpc_energy_read(dpc_plan* p, double* out)
+{
+  if (!p || !out)
+    return fail(DPC_ERR_INVALID, "null argument");
+  DPC_CUDA(cudaMemcpyAsync(p->energy_host, p->energy, sizeof(double), cudaMemcpyDeviceToHost,
+                           p->ctx->stream));
+  DPC_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  *out = *p->energy_host;
+  return DPC_OK;
+}

@@ -1,0 +1,73 @@
+// Internal declarations shared by the translation units of libdeepity_b200.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "deepity_b200.h"
+
+namespace dpc
+{
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+int cuda_fail(cudaError_t err, const char* what);
+
+#define DPC_CUDA(call)                                                                            \
+  do                                                                                              \
+  {                                                                                               \
+    cudaError_t err__ = (call);                                                                   \
+    if (err__ != cudaSuccess)                                                                     \
+      return dpc::cuda_fail(err__, #call);                                                        \
+  } while (0)
+
+// Description of the maximal run of identical square layers that the tensor-core
+// kernels can process with one 3-D tensor map per operand (layer = outermost coordinate).
+struct TensorRun
+{
+  int first = 0, count = 0; // layers [first, first+count), 0 = none
+  int width = 0;            // size == next_size == width
+  // element strides between consecutive layers of the run
+  int64_t z_stride = 0, w_stride = 0, b_stride = 0, out_stride = 0;
+};
+} // namespace dpc
+
+struct dpc_ctx
+{
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int precision = DPC_PRECISION_FP32;
+  int sm_count = 0;
+  int64_t launches = 0;
+  static constexpr int kSlots = 8;
+  cudaGraph_t graphs[kSlots] = {};
+  cudaGraphExec_t execs[kSlots] = {};
+  int capturing_slot = -1;
+  int64_t launches_at_begin = 0;
+  int64_t graph_kernels[kSlots] = {};
+};
+
+struct dpc_plan
+{
+  dpc_ctx* ctx = nullptr;
+  int n = 0, batch = 0;
+  std::vector<dpc_layer> h; // host copy of the table
+  dpc_layer* d = nullptr;   // device copy
+  double* energy = nullptr; // device accumulator
+  double* energy_host = nullptr; // pinned
+  dpc::TensorRun run;
+  void* tc = nullptr; // tensor-core path state (tensor maps), owned by dpc_tc.cu
+};
+
+namespace dpc
+{
+// dpc_tc.cu — tensor-core (tcgen05/TMEM/TMA) path.  Each returns DPC_OK when it handled
+// layers [first, first+count) completely, 1 when the range is not eligible (the caller
+// then uses the CUDA-core kernels), or a negative status.
+int tc_plan_init(dpc_plan* plan);
+void tc_plan_free(dpc_plan* plan);
+int tc_forward(dpc_plan* plan, int first, int count, int flags);
+int tc_update_state(dpc_plan* plan, int first, int count);
+int tc_weight_gemm(dpc_plan* plan, int first, int count, int mode);
+} // namespace dpc

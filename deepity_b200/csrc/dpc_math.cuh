@@ -1,0 +1,137 @@
+// Device math shared by all kernels: activations, their derivatives from the
+// pre-activation value, and the Adam update.  Formulas follow the reference's scalar
+// definitions (include/deepity/utils/Activations.h:44-115, constants
+// include/deepity/utils/activations/Gelu.h:19-22); transcendental functions use the
+// accurate CUDA libm routines (tanhf/expf, <= 2 ulp) rather than the .approx PTX forms
+// the reference GPU backend uses (src/backend/cuda/CUDACommon.cuh:42-93), because the
+// parity target is the CPU path at 1e-4.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "deepity_b200.h"
+
+namespace dpc
+{
+constexpr float kGelu1 = 0.7978845608f;
+constexpr float kGelu2 = 0.044715f;
+
+__device__ __forceinline__ float act_fwd(int act, float z)
+{
+  switch (act)
+  {
+  case DPC_ACT_RELU:
+    return z > 0.0f ? z : 0.0f;
+  case DPC_ACT_GELU:
+  {
+    float zsq = z * z;
+    float inner = kGelu1 * z + (kGelu2 * kGelu1) * zsq * z;
+    return 0.5f * z * (1.0f + tanhf(inner));
+  }
+  case DPC_ACT_SIGMOID:
+    return 1.0f / (1.0f + expf(-z));
+  case DPC_ACT_ESIGMOID:
+    return 0.5f + 0.5f * (z / (1.0f + fabsf(z)));
+  case DPC_ACT_TANH:
+    return tanhf(z);
+  case DPC_ACT_HARD_TANH:
+    return fminf(fmaxf(z, -1.0f), 1.0f);
+  default:
+    return z;
+  }
+}
+
+__device__ __forceinline__ float act_deriv(int act, float z)
+{
+  switch (act)
+  {
+  case DPC_ACT_RELU:
+    return z > 0.0f ? 1.0f : 0.0f;
+  case DPC_ACT_GELU:
+  {
+    float zsq = z * z;
+    float inner = kGelu1 * z + (kGelu2 * kGelu1) * zsq * z;
+    float t = tanhf(inner);
+    float gprime = kGelu1 + (3.0f * kGelu2 * kGelu1) * zsq;
+    return 0.5f * (1.0f + t) + 0.5f * z * gprime * (1.0f - t * t);
+  }
+  case DPC_ACT_SIGMOID:
+  {
+    float s = 1.0f / (1.0f + expf(-z));
+    return s * (1.0f - s);
+  }
+  case DPC_ACT_ESIGMOID:
+  {
+    float a = 1.0f + fabsf(z);
+    return 0.5f / (a * a);
+  }
+  case DPC_ACT_TANH:
+  {
+    float t = tanhf(z);
+    return 1.0f - t * t;
+  }
+  case DPC_ACT_HARD_TANH:
+    return (z > -1.0f && z < 1.0f) ? 1.0f : 0.0f;
+  default:
+    return 1.0f;
+  }
+}
+
+// Activation and derivative together (one transcendental for tanh / sigmoid / gelu).
+__device__ __forceinline__ void act_both(int act, float z, float& f, float& d)
+{
+  switch (act)
+  {
+  case DPC_ACT_TANH:
+  {
+    float t = tanhf(z);
+    f = t;
+    d = 1.0f - t * t;
+    return;
+  }
+  case DPC_ACT_SIGMOID:
+  {
+    float s = 1.0f / (1.0f + expf(-z));
+    f = s;
+    d = s * (1.0f - s);
+    return;
+  }
+  case DPC_ACT_GELU:
+  {
+    float zsq = z * z;
+    float inner = kGelu1 * z + (kGelu2 * kGelu1) * zsq * z;
+    float t = tanhf(inner);
+    float gprime = kGelu1 + (3.0f * kGelu2 * kGelu1) * zsq;
+    f = 0.5f * z * (1.0f + t);
+    d = 0.5f * (1.0f + t) + 0.5f * z * gprime * (1.0f - t * t);
+    return;
+  }
+  default:
+    f = act_fwd(act, z);
+    d = act_deriv(act, z);
+  }
+}
+
+// Adam / AdamW step size, src/backend/CPUBackend.cpp:721-772:
+// step = lr*sqrt(1-beta2^t)/(1-beta1^t), t already incremented (clamped to >= 1).
+__device__ __forceinline__ float adam_step_size(float lr, int t)
+{
+  float tf = (float)(t < 1 ? 1 : t);
+  float b1t = 1.0f - powf(0.9f, tf);
+  float b2t = 1.0f - powf(0.999f, tf);
+  return lr * sqrtf(b2t) / b1t;
+}
+
+// One element of the chunk kernels (src/backend/CPUBackendHighway.cpp:799-805,832-839).
+// lr_wd < 0 means plain Adam, otherwise AdamW's decoupled decay p -= lr_wd*p first.
+__device__ __forceinline__ float adam_update(float p, float g, float& m, float& v, float step,
+                                              float lr_wd)
+{
+  const float b1 = 0.9f, b2 = 0.999f, eps = 1e-8f;
+  m = b1 * m + (1.0f - b1) * g;
+  v = b2 * v + (1.0f - b2) * (g * g);
+  if (lr_wd >= 0.0f)
+    p -= lr_wd * p;
+  p -= step * m / (sqrtf(v) + eps);
+  return p;
+}
+} // namespace dpc

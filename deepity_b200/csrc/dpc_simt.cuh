@@ -1,0 +1,719 @@
+// CUDA-core (fp32 FFMA) kernels for every phase of the predictive-coding train step.
+// They handle any shape (ragged, tiny terminal widths, unaligned leading dimensions) and
+// are the path for layers outside the tensor-core run.  One launch covers a whole range
+// of layers: blockIdx.z selects the layer, blockIdx.x/y the output tile; CTAs outside a
+// layer's own tile grid return at once.
+#pragma once
+#include "dpc_math.cuh"
+
+namespace dpc
+{
+constexpr int BM = 64, BN = 64, BK = 16, NTHREADS = 256, PAD = 4;
+
+enum GemmOp
+{
+  OP_FWD = 0, // mu = f(a z W^T + b)             M=B  N=next K=size
+  OP_FB = 1,  // z += ir (a fe W - e)            M=B  N=size K=next
+  OP_WG = 2   // W += alpha g^T zin              M=next N=size K=B
+};
+
+// mode of OP_WG
+enum
+{
+  WG_LEARN = 0, // UpdateWeights: g = fe (or e_above for Simple), rate lr, optimizer
+  WG_DFA = 1    // DirectFeedbackUpdate: g = fe (holds proj), rate fl, plain accumulate
+};
+
+struct Tile
+{
+  float a[BK][BM + PAD];
+  float b[BK][BN + PAD];
+};
+
+// Operand whose rows are the M/N index with k contiguous: G[(row0+r)*ld + k0+k].
+template <bool kAct>
+__device__ __forceinline__ void fetch_kmajor(float (&reg)[4], const float* __restrict__ G, int ld,
+                                             int row0, int k0, int nrows, int K, bool vec,
+                                             int act)
+{
+  const int t = threadIdx.x;
+  const int r = row0 + (t >> 2), k = k0 + ((t & 3) << 2);
+  if (r < nrows && vec && k + 3 < K)
+  {
+    float4 v = *reinterpret_cast<const float4*>(G + (size_t)r * ld + k);
+    reg[0] = v.x, reg[1] = v.y, reg[2] = v.z, reg[3] = v.w;
+  }
+  else
+  {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      reg[j] = (r < nrows && k + j < K) ? G[(size_t)r * ld + k + j] : 0.0f;
+  }
+  if (kAct)
+  {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      reg[j] = (r < nrows && k + j < K) ? act_fwd(act, reg[j]) : 0.0f;
+  }
+}
+
+template <int COLS>
+__device__ __forceinline__ void stash_kmajor(float (*S)[COLS + PAD], const float (&reg)[4])
+{
+  const int t = threadIdx.x;
+  const int r = t >> 2, k = (t & 3) << 2;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    S[k + j][r] = reg[j];
+}
+
+// Operand stored [K, cols] with cols contiguous: G[(k0+k)*ld + col0+c].
+__device__ __forceinline__ void fetch_mnmajor(float (&reg)[4], const float* __restrict__ G, int ld,
+                                              int col0, int k0, int ncols, int K, bool vec)
+{
+  const int t = threadIdx.x;
+  const int k = k0 + (t >> 4), c = col0 + ((t & 15) << 2);
+  if (k < K && vec && c + 3 < ncols)
+  {
+    float4 v = *reinterpret_cast<const float4*>(G + (size_t)k * ld + c);
+    reg[0] = v.x, reg[1] = v.y, reg[2] = v.z, reg[3] = v.w;
+  }
+  else
+  {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      reg[j] = (k < K && c + j < ncols) ? G[(size_t)k * ld + c + j] : 0.0f;
+  }
+}
+
+template <int COLS>
+__device__ __forceinline__ void stash_mnmajor(float (*S)[COLS + PAD], const float (&reg)[4])
+{
+  const int t = threadIdx.x;
+  const int k = t >> 4, c = (t & 15) << 2;
+  *reinterpret_cast<float4*>(&S[k][c]) = make_float4(reg[0], reg[1], reg[2], reg[3]);
+}
+
+__device__ __forceinline__ bool aligned16(const void* p)
+{
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
+__device__ __forceinline__ void block_energy_add(float local, double* energy)
+{
+  __shared__ float warp_sums[NTHREADS / 32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((threadIdx.x & 31) == 0)
+    warp_sums[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0)
+  {
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NTHREADS / 32; ++w)
+      s += warp_sums[w];
+    atomicAdd(energy, (double)(0.5f * s));
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// The grouped GEMM kernel.  OP selects operand layouts and the fused epilogue.
+// ---------------------------------------------------------------------------------------
+template <int OP>
+__global__ void __launch_bounds__(NTHREADS)
+    pc_gemm_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
+                   int flags, int mode, double* energy)
+{
+  const int li = first + blockIdx.z;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0)
+    return;
+  const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+
+  int M, N, K;
+  if (OP == OP_FWD)
+    M = batch, N = L.next_size, K = L.size;
+  else if (OP == OP_FB)
+    M = batch, N = L.size, K = L.next_size;
+  else
+    M = L.next_size, N = L.size, K = batch;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  if (m0 >= M || n0 >= N)
+    return;
+  if (OP == OP_WG && mode == WG_DFA)
+  {
+    // DirectFeedbackUpdate is a no-op unless the layer above owns feedback weights.
+    if (li + 1 >= n_layers || layers[li + 1].Psi == nullptr || layers[li + 1].next_size <= 0)
+      return;
+  }
+
+  const dpc_layer* Lup = (li + 1 < n_layers) ? &layers[li + 1] : nullptr;
+  const float* A;
+  const float* Bm;
+  int lda, ldb;
+  if (OP == OP_FWD)
+    A = L.z, lda = L.size, Bm = L.W, ldb = L.size;
+  else if (OP == OP_FB)
+    A = simple ? Lup->e : L.fe, lda = L.next_size, Bm = L.W, ldb = L.size;
+  else
+    A = (simple && mode == WG_LEARN) ? Lup->e : L.fe, lda = L.next_size,
+    Bm = simple ? L.zF : L.z, ldb = L.size;
+
+  __shared__ Tile tile;
+  const bool vecA = aligned16(A) && (lda % 4 == 0);
+  const bool vecB = aligned16(Bm) && (ldb % 4 == 0);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      acc[i][j] = 0.0f;
+
+  float ra[4], rb[4];
+  auto fetch = [&](int k0)
+  {
+    if (OP == OP_FWD)
+    {
+      if (simple)
+        fetch_kmajor<true>(ra, A, lda, m0, k0, M, K, vecA, L.act);
+      else
+        fetch_kmajor<false>(ra, A, lda, m0, k0, M, K, vecA, 0);
+      fetch_kmajor<false>(rb, Bm, ldb, n0, k0, N, K, vecB, 0);
+    }
+    else if (OP == OP_FB)
+    {
+      fetch_kmajor<false>(ra, A, lda, m0, k0, M, K, vecA, 0);
+      fetch_mnmajor(rb, Bm, ldb, n0, k0, N, K, vecB);
+    }
+    else
+    {
+      fetch_mnmajor(ra, A, lda, m0, k0, M, K, vecA);
+      fetch_mnmajor(rb, Bm, ldb, n0, k0, N, K, vecB);
+    }
+  };
+  auto stash = [&](int k0)
+  {
+    if (OP == OP_WG)
+      stash_mnmajor<BM>(tile.a, ra);
+    else
+      stash_kmajor<BM>(tile.a, ra);
+    if (OP == OP_FWD)
+      stash_kmajor<BN>(tile.b, rb);
+    else
+      stash_mnmajor<BN>(tile.b, rb);
+    if (OP == OP_FWD && simple && blockIdx.x == 0 && L.zF != nullptr)
+    {
+      // SimplePC keeps f(z) as last fed to the GEMM for its weight update
+      // (src/layers/SimplePCLayer.cpp:146-150).
+      const int t = threadIdx.x;
+      const int r = m0 + (t >> 2), k = k0 + ((t & 3) << 2);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (r < M && k + j < K)
+          L.zF[(size_t)r * L.size + k + j] = ra[j];
+    }
+  };
+
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  for (int k0 = 0; k0 < K; k0 += BK)
+  {
+    const bool more = k0 + BK < K;
+    if (more)
+      fetch(k0 + BK);
+#pragma unroll
+    for (int k = 0; k < BK; ++k)
+    {
+      const float4 av = *reinterpret_cast<const float4*>(&tile.a[k][ty * 4]);
+      const float4 bv = *reinterpret_cast<const float4*>(&tile.b[k][tx * 4]);
+      const float a4[4] = {av.x, av.y, av.z, av.w};
+      const float b4[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[i][j] = fmaf(a4[i], b4[j], acc[i][j]);
+    }
+    __syncthreads();
+    if (more)
+    {
+      stash(k0 + BK);
+      __syncthreads();
+    }
+  }
+
+  // ------------------------------------------------------------------ epilogues
+  float esum = 0.0f;
+  if (OP == OP_FWD)
+  {
+    const bool next_ce = Lup && (Lup->flags & DPC_LAYER_SOFTMAX_CE);
+    const bool do_err = (flags & DPC_FWD_ERR_NEXT) && Lup && !next_ce;
+    const bool do_fe = (flags & DPC_FWD_FE) && Lup && !simple && !(next_ce && (flags & DPC_FWD_ERR_NEXT));
+    const bool do_copy = (flags & DPC_FWD_COPY_NEXT) && Lup;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+      const int m = m0 + ty * 4 + i;
+      if (m >= M)
+        continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+      {
+        const int n = n0 + tx * 4 + j;
+        if (n >= N)
+          continue;
+        const size_t o = (size_t)m * N + n;
+        const float pre = L.a * acc[i][j] + L.b[n];
+        float mu, d = 1.0f;
+        if (simple)
+          mu = pre;
+        else
+        {
+          if (do_fe)
+            act_both(L.act, pre, mu, d);
+          else
+            mu = act_fwd(L.act, pre);
+          if (L.flags & DPC_LAYER_RESIDUAL)
+            mu += L.z[o];
+        }
+        if (L.preact)
+          L.preact[o] = pre;
+        L.mu[o] = mu;
+        if (do_copy)
+          Lup->z[o] = mu;
+        float e = 0.0f;
+        if (do_err)
+        {
+          e = (do_copy ? mu : Lup->z[o]) - mu;
+          Lup->e[o] = e;
+          esum += e * e;
+        }
+        else if (do_fe)
+          e = Lup->e[o];
+        if (do_fe)
+          L.fe[o] = e * d;
+      }
+    }
+    if (flags & DPC_FWD_ENERGY)
+      block_energy_add(do_err ? esum : 0.0f, energy);
+  }
+  else if (OP == OP_FB)
+  {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+      const int m = m0 + ty * 4 + i;
+      if (m >= M)
+        continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+      {
+        const int n = n0 + tx * 4 + j;
+        if (n >= N)
+          continue;
+        const size_t o = (size_t)m * N + n;
+        float z = L.z[o];
+        if (simple)
+        {
+          z += L.ir * (acc[i][j] * act_deriv(L.act, z) - L.e[o]);
+        }
+        else
+        {
+          const float fb = L.a * acc[i][j] - L.e[o];
+          if (L.v)
+          {
+            const float v = L.momentum_beta * L.v[o] + (1.0f - L.momentum_beta) * fb;
+            L.v[o] = v;
+            z += L.ir * v;
+          }
+          else
+            z += L.ir * fb;
+          if (L.flags & DPC_LAYER_RESIDUAL)
+            z += L.ir * Lup->e[o];
+        }
+        L.z[o] = z;
+      }
+    }
+  }
+  else
+  {
+    const float Bf = (float)batch;
+    const bool adam = (mode == WG_LEARN) && (L.opt != DPC_OPT_SGD);
+    float alpha, decay = 1.0f, step = 0.0f, lr_wd = -1.0f;
+    if (mode == WG_DFA)
+    {
+      alpha = L.fl * L.a / Bf;
+      if ((flags & 1) && L.lmbda > 0.0f && L.fl != 0.0f)
+        decay = 1.0f - L.lmbda;
+    }
+    else if (!adam)
+    {
+      alpha = simple ? (L.lr / Bf) : (L.a * L.lr / Bf);
+      if (L.lmbda > 0.0f)
+        decay = 1.0f - L.lmbda;
+    }
+    else
+    {
+      alpha = -1.0f * L.a;
+      step = adam_step_size(L.lr, *L.t);
+      if (L.opt == DPC_OPT_ADAMW)
+        lr_wd = L.lr * L.lmbda;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+      const int m = m0 + ty * 4 + i;
+      if (m >= M)
+        continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+      {
+        const int n = n0 + tx * 4 + j;
+        if (n >= N)
+          continue;
+        const size_t o = (size_t)m * N + n;
+        float w = L.W[o];
+        if (!adam)
+        {
+          if (decay != 1.0f)
+            w *= decay;
+          w = fmaf(alpha, acc[i][j], w);
+        }
+        else
+        {
+          float mm = L.m_W[o], vv = L.v_W[o];
+          w = adam_update(w, alpha * acc[i][j], mm, vv, step, lr_wd);
+          L.m_W[o] = mm;
+          L.v_W[o] = vv;
+        }
+        L.W[o] = w;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Elementwise / skinny kernels (grouped over layers with blockIdx.y = layer in range).
+// ---------------------------------------------------------------------------------------
+
+// The forward epilogue for a layer whose prediction is cached (clamped input layer):
+// no GEMM, preact/mu are read from memory.
+__global__ void cached_forward_kernel(const dpc_layer* __restrict__ layers, int first,
+                                      int n_layers, int batch, int flags, double* energy)
+{
+  const int li = first + blockIdx.y;
+  const dpc_layer L = layers[li];
+  const dpc_layer* Lup = (li + 1 < n_layers) ? &layers[li + 1] : nullptr;
+  float esum = 0.0f;
+  if (L.next_size > 0 && Lup)
+  {
+    const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+    const bool next_ce = (Lup->flags & DPC_LAYER_SOFTMAX_CE) != 0;
+    const bool do_err = (flags & DPC_FWD_ERR_NEXT) && !next_ce;
+    const bool do_fe = (flags & DPC_FWD_FE) && !simple && !(next_ce && (flags & DPC_FWD_ERR_NEXT));
+    const bool do_copy = (flags & DPC_FWD_COPY_NEXT) != 0;
+    const size_t total = (size_t)batch * L.next_size;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+         o += (size_t)gridDim.x * blockDim.x)
+    {
+      const float mu = L.mu[o];
+      if (do_copy)
+        Lup->z[o] = mu;
+      float e = 0.0f;
+      if (do_err)
+      {
+        e = (do_copy ? mu : Lup->z[o]) - mu;
+        Lup->e[o] = e;
+        esum += e * e;
+      }
+      else if (do_fe)
+        e = Lup->e[o];
+      if (do_fe)
+        L.fe[o] = e * act_deriv(L.act, L.preact[o]);
+    }
+  }
+  if (flags & DPC_FWD_ENERGY)
+    block_energy_add(esum, energy);
+}
+
+// e = z - mu_below (+ energy), src/backend/CPUBackend.cpp:602-629.
+__global__ void error_kernel(const dpc_layer* __restrict__ layers, int li, int batch,
+                             int with_energy, double* energy)
+{
+  const dpc_layer L = layers[li];
+  const dpc_layer Lb = layers[li - 1];
+  const size_t total = (size_t)batch * L.size;
+  float esum = 0.0f;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+       o += (size_t)gridDim.x * blockDim.x)
+  {
+    const float e = L.z[o] - Lb.mu[o];
+    L.e[o] = e;
+    esum += e * e;
+  }
+  if (with_energy)
+    block_energy_add(esum, energy);
+}
+
+// Softmax cross-entropy error, one warp per batch row:
+// e = z - softmax(mu_below), E = -sum z*log(p + 1e-8)   (CPUBackend.cpp:658-695).
+__global__ void softmax_ce_kernel(const dpc_layer* __restrict__ layers, int li, int batch,
+                                  int with_energy, double* energy)
+{
+  const dpc_layer L = layers[li];
+  const float* mu = layers[li - 1].mu;
+  const int n = L.size;
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  float row_energy = 0.0f;
+  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < batch; r += gridDim.x * warps)
+  {
+    const float* mrow = mu + (size_t)r * n;
+    const float* zrow = L.z + (size_t)r * n;
+    float* erow = L.e + (size_t)r * n;
+    float mx = -INFINITY;
+    for (int j = lane; j < n; j += 32)
+      mx = fmaxf(mx, mrow[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float s = 0.0f;
+    for (int j = lane; j < n; j += 32)
+      s += expf(mrow[j] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+    for (int j = lane; j < n; j += 32)
+    {
+      const float p = expf(mrow[j] - mx) / s;
+      const float z = zrow[j];
+      row_energy -= z * logf(p + 1e-8f);
+      erow[j] = z - p;
+    }
+  }
+  if (with_energy)
+  {
+    // block_energy_add halves its input (Gaussian energy); cross-entropy is not halved.
+    block_energy_add(2.0f * row_energy, energy);
+  }
+}
+
+// fe[l] = e[l+1] * f'(preact[l])
+__global__ void feedback_error_kernel(const dpc_layer* __restrict__ layers, int first,
+                                      int n_layers, int batch)
+{
+  const int li = first + blockIdx.y;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0 || (L.flags & DPC_LAYER_INPUT_ACT))
+    return;
+  const float* e_up = layers[li + 1].e;
+  const size_t total = (size_t)batch * L.next_size;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+       o += (size_t)gridDim.x * blockDim.x)
+    L.fe[o] = e_up[o] * act_deriv(L.act, L.preact[o]);
+}
+
+// z -= ir*e for layers of the range that have no weights or no upper neighbour.
+__global__ void relax_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
+                             int batch, int only_weightless)
+{
+  const int li = first + blockIdx.y;
+  const dpc_layer L = layers[li];
+  if (only_weightless && L.next_size > 0 && li + 1 < n_layers)
+    return;
+  const size_t total = (size_t)batch * L.size;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+       o += (size_t)gridDim.x * blockDim.x)
+    L.z[o] -= L.ir * L.e[o];
+}
+
+// DFA projection: fe[l] = (e_T · Psi[l+1]^T) * f'(preact[l])   (K = terminal_size).
+__global__ void dfa_proj_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
+                                int batch)
+{
+  const int li = first + blockIdx.y;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  const dpc_layer Lup = layers[li + 1];
+  if (L.next_size <= 0 || Lup.Psi == nullptr || Lup.next_size <= 0)
+    return;
+  const float* eT = layers[n_layers - 1].e;
+  const int TS = L.terminal_size, n = L.next_size;
+  const size_t total = (size_t)batch * n;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+       o += (size_t)gridDim.x * blockDim.x)
+  {
+    const int b = (int)(o / n), j = (int)(o % n);
+    const float* er = eT + (size_t)b * TS;
+    const float* pr = Lup.Psi + (size_t)j * Lup.psi_stride;
+    float s = 0.0f;
+    for (int k = 0; k < TS; ++k)
+      s = fmaf(er[k], pr[k], s);
+    L.fe[o] = s * act_deriv(L.act, L.preact[o]);
+  }
+}
+
+// Adam step counters: t += 1 once per UpdateWeights (src/backend/cuda/CUDABackendOptimizer.cu:20-31).
+__global__ void bump_counters_kernel(const dpc_layer* __restrict__ layers, int first, int count,
+                                     int n_layers)
+{
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count)
+    return;
+  const int li = first + i;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0 || li + 1 >= n_layers)
+    return;
+  if (L.opt != DPC_OPT_SGD && L.t)
+    *L.t += 1;
+  if (!(L.flags & DPC_LAYER_INPUT_ACT) && L.opt_psi != DPC_OPT_SGD && L.t_Psi)
+    *L.t_Psi += 1;
+}
+
+// Bias update from the column sums of the local gradient: one thread per output unit,
+// summing the batch in row order like CPUBackend::SumRows (CPUBackend.cpp:243-248).
+__global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
+                                   int batch)
+{
+  const int li = first + blockIdx.y;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0)
+    return;
+  const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+  const float* g = simple ? layers[li + 1].e : L.fe;
+  const int n = L.next_size;
+  for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x)
+  {
+    float s = 0.0f;
+    for (int b = 0; b < batch; ++b)
+      s += g[(size_t)b * n + j];
+    if (L.opt == DPC_OPT_SGD)
+      L.b[j] += (L.lr / (float)batch) * s;
+    else
+    {
+      float m = L.m_b[j], v = L.v_b[j];
+      L.b[j] = adam_update(L.b[j], -s, m, v, adam_step_size(L.lr, *L.t), -1.0f);
+      L.m_b[j] = m;
+      L.v_b[j] = v;
+    }
+  }
+}
+
+// Feedback-weight update Psi[l] (+)= (fl*a/B) z[l]^T e_T, one thread per row of Psi with the
+// terminal columns in registers (chunks of 16).
+__global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
+                                  int batch)
+{
+  const int li = first + blockIdx.y;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0 || L.Psi == nullptr || (L.flags & DPC_LAYER_INPUT_ACT))
+    return;
+  const float* eT = layers[n_layers - 1].e;
+  const int TS = L.terminal_size, s = L.size;
+  const bool full_kind = (L.flags & DPC_LAYER_FULLPC_PSI) != 0;
+  const float rate = full_kind ? L.fl * L.a : L.fl;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < s; i += gridDim.x * blockDim.x)
+  {
+    for (int kc = 0; kc < TS; kc += 16)
+    {
+      float acc[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        acc[k] = 0.0f;
+      const int kn = min(16, TS - kc);
+      for (int b = 0; b < batch; ++b)
+      {
+        const float zv = L.z[(size_t)b * s + i];
+        const float* er = eT + (size_t)b * TS + kc;
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if (k < kn)
+            acc[k] = fmaf(zv, er[k], acc[k]);
+      }
+      float* prow = L.Psi + (size_t)i * L.psi_stride + kc;
+      if (L.opt_psi == DPC_OPT_SGD)
+      {
+        const float decay = (!full_kind && L.psi_decay > 0.0f) ? 1.0f - L.psi_decay : 1.0f;
+        const float alpha = rate / (float)batch;
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if (k < kn)
+          {
+            float p = prow[k];
+            if (decay != 1.0f)
+              p *= decay;
+            prow[k] = fmaf(alpha, acc[k], p);
+          }
+      }
+      else
+      {
+        const float step = adam_step_size(rate, *L.t_Psi);
+        float lr_wd = -1.0f;
+        if (L.opt_psi == DPC_OPT_ADAMW)
+          lr_wd = rate * ((!full_kind && L.psi_decay >= 0.0f) ? L.psi_decay : L.lmbda);
+        float* mrow = L.m_Psi + (size_t)i * L.psi_stride + kc;
+        float* vrow = L.v_Psi + (size_t)i * L.psi_stride + kc;
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if (k < kn)
+          {
+            float m = mrow[k], v = vrow[k];
+            prow[k] = adam_update(prow[k], -acc[k], m, v, step, lr_wd);
+            mrow[k] = m;
+            vrow[k] = v;
+          }
+      }
+    }
+  }
+}
+
+// Row centring of W: subtract each row's mean (src/backend/CPUBackend.cpp:250-272).
+__global__ void center_rows_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers)
+{
+  const int li = first + blockIdx.y;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0)
+    return;
+  __shared__ float red[32];
+  for (int r = blockIdx.x; r < L.next_size; r += gridDim.x)
+  {
+    float* row = L.W + (size_t)r * L.size;
+    float s = 0.0f;
+    for (int c = threadIdx.x; c < L.size; c += blockDim.x)
+      s += row[c];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0)
+      red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32)
+    {
+      float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (threadIdx.x == 0)
+        red[0] = t;
+    }
+    __syncthreads();
+    const float mean = red[0] / (float)L.size;
+    for (int c = threadIdx.x; c < L.size; c += blockDim.x)
+      row[c] -= mean;
+    __syncthreads();
+  }
+}
+} // namespace dpc

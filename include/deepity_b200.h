@@ -1,0 +1,282 @@
+/*
+ * deepity_b200 — C ABI of the B200 (sm_100a) predictive-coding train-step library.
+ *
+ * Two levels, both plain C (pointers, sizes, opaque handles, int status codes; no
+ * exceptions cross this boundary, no torch types):
+ *
+ *   dpc_*   phase kernels on DEVICE pointers.  They stand where the reference's layer
+ *           classes call its compute backend (include/deepity/backend/IComputeBackend.h)
+ *           — but one call covers a whole phase of many layers instead of one primitive
+ *           of one layer.  All work is stream-ordered on the context's stream; only the
+ *           functions marked "synchronous" wait for the GPU.
+ *   dpcn_*  whole networks (SimplePC / DirectKPPC / FullPC) with HOST buffers in and
+ *           out.  They are what the reference's Python binding binds
+ *           (bindings/NetworkBindings.cpp:562-646, 836-1067, 1069-1357).
+ *
+ * Every function returns DPC_OK (0) or a negative dpc_status; dpc_last_error() gives
+ * the message of the last failure on the calling thread.  There is no CPU fallback:
+ * without a CUDA device every call fails with DPC_ERR_NO_DEVICE.
+ */
+#ifndef DEEPITY_B200_H
+#define DEEPITY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DPC_API __attribute__((visibility("default")))
+#else
+#define DPC_API
+#endif
+
+typedef enum dpc_status
+{
+  DPC_OK = 0,
+  DPC_ERR_INVALID = -1,   /* bad argument / shape / handle            */
+  DPC_ERR_NO_DEVICE = -2, /* no usable CUDA device                    */
+  DPC_ERR_CUDA = -3,      /* a CUDA runtime or driver call failed     */
+  DPC_ERR_STATE = -4,     /* call order (e.g. train step before compile) */
+  DPC_ERR_TIMEOUT = -5,   /* a bounded device-side wait gave up       */
+  DPC_ERR_TOO_LARGE = -6  /* size beyond a documented fixed maximum   */
+} dpc_status;
+
+/* Activation ids: the forward enumerators of Deep::ActivationType
+ * (include/deepity/utils/ActivationType.h:15-32), so a host that already holds that
+ * enum passes it through unchanged.  The derivative is implied. */
+typedef enum dpc_act
+{
+  DPC_ACT_RELU = 0,
+  DPC_ACT_GELU = 2,
+  DPC_ACT_SIGMOID = 4,
+  DPC_ACT_ESIGMOID = 6,
+  DPC_ACT_TANH = 8,
+  DPC_ACT_LINEAR = 10,
+  DPC_ACT_HARD_TANH = 12
+} dpc_act;
+
+/* Deep::OptimizerType, include/deepity/utils/AdamOptimizer.h:12-17. */
+typedef enum dpc_opt
+{
+  DPC_OPT_SGD = 0,
+  DPC_OPT_ADAM = 1,
+  DPC_OPT_ADAMW = 2
+} dpc_opt;
+
+/* GEMM arithmetic.  FP32: every product and sum in fp32 (CUDA cores, or 3xTF32 split on
+ * the tensor cores where the shape allows) — the mode judged at 1e-4 against the CPU
+ * reference.  TF32: one tensor-core pass with fp32 accumulation, the analogue of the
+ * reference's default cuBLAS TF32 math mode (src/backend/cuda/CUDABackendCore.cu:54-67,
+ * IComputeBackend::SetAllowTF32); judged at the reference's own 1e-2 CPU-vs-GPU bound. */
+typedef enum dpc_precision
+{
+  DPC_PRECISION_FP32 = 0,
+  DPC_PRECISION_TF32 = 1
+} dpc_precision;
+
+typedef struct dpc_ctx dpc_ctx;
+typedef struct dpc_plan dpc_plan;
+
+/* ------------------------------------------------------------------------------------
+ * Context: device, stream, graph slots.  Replaces CUDABackend's constructor and the
+ * plugin entry Deepity_CreateCUDABackend (src/backend/cuda/CUDAPluginExports.cpp:12-21,
+ * src/backend/cuda/CUDABackendCore.cu:26-73).
+ * ---------------------------------------------------------------------------------- */
+DPC_API const char* dpc_last_error(void);
+DPC_API const char* dpc_version(void);
+DPC_API int dpc_create(int device, dpc_ctx** out);
+DPC_API int dpc_destroy(dpc_ctx* ctx);
+DPC_API int dpc_set_precision(dpc_ctx* ctx, int precision); /* IComputeBackend::SetAllowTF32 */
+DPC_API int dpc_get_precision(dpc_ctx* ctx);
+/* cudaStream_t of the context, as void* (IComputeBackend::GetStreamHandle). */
+DPC_API void* dpc_stream(dpc_ctx* ctx);
+/* Number of kernels this library has launched on the context since creation. */
+DPC_API int64_t dpc_launch_count(dpc_ctx* ctx);
+
+/* Memory (IComputeBackend::Allocate/Free/Zero/Copy/CopyFromHost/CopyToHost,
+ * include/deepity/backend/IComputeBackend.h:52-77).  Sizes in BYTES.  alloc/free and the
+ * *_sync copies are synchronous; the others are stream-ordered. */
+DPC_API int dpc_alloc(dpc_ctx* ctx, size_t bytes, void** out);
+DPC_API int dpc_free(dpc_ctx* ctx, void* ptr);
+DPC_API int dpc_zero(dpc_ctx* ctx, void* ptr, size_t bytes);
+DPC_API int dpc_copy_d2d(dpc_ctx* ctx, void* dst, const void* src, size_t bytes);
+DPC_API int dpc_copy_h2d(dpc_ctx* ctx, void* dst, const void* host_src, size_t bytes);
+DPC_API int dpc_copy_d2h(dpc_ctx* ctx, void* host_dst, const void* src, size_t bytes);
+DPC_API int dpc_copy_h2d_sync(dpc_ctx* ctx, void* dst, const void* host_src, size_t bytes);
+DPC_API int dpc_copy_d2h_sync(dpc_ctx* ctx, void* host_dst, const void* src, size_t bytes);
+DPC_API int dpc_alloc_host(dpc_ctx* ctx, size_t bytes, void** out); /* pinned */
+DPC_API int dpc_free_host(dpc_ctx* ctx, void* ptr);
+DPC_API int dpc_sync(dpc_ctx* ctx); /* IComputeBackend::Synchronize */
+
+/* CUDA graphs (IComputeBackend::BeginGraphCapture/EndGraphCapture/ReplayGraph,
+ * src/backend/cuda/CUDABackendCore.cu:120-187).  slot in [0, 8). */
+DPC_API int dpc_graph_begin(dpc_ctx* ctx, int slot);
+DPC_API int dpc_graph_end(dpc_ctx* ctx, int slot);
+DPC_API int dpc_graph_launch(dpc_ctx* ctx, int slot);
+DPC_API int dpc_graph_drop(dpc_ctx* ctx, int slot);
+
+/* ------------------------------------------------------------------------------------
+ * Layer description.  One entry per layer of a network, input layer first, the
+ * weight-less terminal layer last (next_size == 0, parameter pointers NULL).  Tensors are
+ * fp32 row-major:  z,e,zF,v [B,size];  W [next_size,size];  b [next_size];
+ * preact,mu,fe [B,next_size];  Psi [size,psi_stride] (terminal_size logical columns).
+ * The fields mirror DirectKPPCLayer::ExternalMemory
+ * (include/deepity/layers/DirectKPPCLayer.h:165-199).
+ * ---------------------------------------------------------------------------------- */
+enum
+{
+  DPC_LAYER_INPUT_ACT = 1 << 0, /* SimplePC convention: mu = f(z)·Wᵀ + b, derivative applied at
+                                   the destination (src/layers/SimplePCLayer.cpp:132-257).
+                                   Otherwise mu = f(a·z·Wᵀ + b) (DirectKP/Full). */
+  DPC_LAYER_RESIDUAL = 1 << 1,  /* FullPC: mu += z  (src/layers/FullPCLayer.cpp:283-289) */
+  DPC_LAYER_SOFTMAX_CE = 1 << 2, /* this layer's error is z - softmax(mu_below)
+                                    (src/backend/CPUBackend.cpp:658-714) */
+  DPC_LAYER_FULLPC_PSI = 1 << 3  /* FullPC's feedback-weight rule: rate fl*a, AdamW decay lmbda,
+                                    no psi_decay (src/layers/FullPCLayer.cpp:466-510) */
+};
+
+typedef struct dpc_layer
+{
+  int32_t size, next_size, terminal_size, psi_stride;
+  int32_t act;   /* dpc_act */
+  int32_t flags; /* DPC_LAYER_* */
+  float a;       /* muPC forward scale, 1 when unused (FullPCLayer::SetMuPCScale) */
+  float lr, ir, fl, lmbda;
+  float psi_decay;     /* < 0: optimizer default (DirectKPPCLayer.cpp:444-446,492-494) */
+  float momentum_beta; /* used when v != NULL (FullPCLayer.cpp:353-363) */
+  int32_t opt, opt_psi; /* dpc_opt */
+  float *z, *e;
+  float *W, *b;
+  float *preact, *mu, *fe;
+  float* Psi;
+  float* zF; /* DPC_LAYER_INPUT_ACT only: f(z) as last fed to the GEMM */
+  float* v;  /* state momentum or NULL */
+  float *m_W, *v_W, *m_b, *v_b, *m_Psi, *v_Psi; /* Adam moments or NULL */
+  int32_t *t, *t_Psi;                           /* Adam step counters on the device or NULL */
+} dpc_layer;
+
+/* A plan = the layer table uploaded once, plus whatever the kernels precompute for it
+ * (uniform runs for the tensor-core path, tensor maps).  Replaces what
+ * DirectKPPCNetwork::Compile() prepares for its batched run
+ * (src/networks/DirectKPPCNetwork.cpp:692-944). */
+DPC_API int dpc_plan_create(dpc_ctx* ctx, const dpc_layer* layers, int n_layers, int batch,
+                            dpc_plan** out);
+/* Re-upload after a hyper-parameter / optimizer / pointer change (same layer count). */
+DPC_API int dpc_plan_update(dpc_plan* plan, const dpc_layer* layers, int n_layers);
+DPC_API int dpc_plan_destroy(dpc_plan* plan);
+/* Layers [first, first+count) that the tensor-core path covers (0 if none). */
+DPC_API int dpc_plan_tensor_run(dpc_plan* plan, int* first, int* count);
+
+/* ---- phases.  Layer ranges are [first, first+count) over the plan's table. ---------- */
+enum
+{
+  DPC_FWD_COPY_NEXT = 1 << 0, /* z[l+1] = mu[l]  (ProjectForward's copy)                  */
+  DPC_FWD_ERR_NEXT = 1 << 1,  /* e[l+1] = z[l+1] - mu[l]  (ComputeError of the layer above)*/
+  DPC_FWD_ENERGY = 1 << 2,    /* with ERR_NEXT: energy += 0.5*sum e[l+1]^2                 */
+  DPC_FWD_FE = 1 << 3,        /* fe[l] = e[l+1] * f'(preact[l]); e[l+1] is the one just
+                                 computed with ERR_NEXT, else the one in memory            */
+  DPC_FWD_CACHED = 1 << 4     /* skip the GEMM, reuse preact/mu in memory (a clamped layer's
+                                 cached prediction, DirectKPPCLayer.cpp:275-280)          */
+};
+
+/* ComputeMuOnly for every layer of the range, all independent
+ * (DirectKPPCLayer.cpp:267-310, FullPCLayer.cpp:246-298, SimplePCLayer.cpp:132-183),
+ * with the error of the layer above and the feedback error fused in on request. */
+DPC_API int dpc_forward(dpc_plan* plan, int first, int count, int flags);
+/* The sequential forward sweep: for l in range: ComputeMuOnly(l); z[l+1] = mu[l] unless
+ * l+1 is the last layer and skip_last_copy != 0 (a clamped target)
+ * (DirectKPPCNetwork::ProjectForward, src/networks/DirectKPPCNetwork.cpp:349-371). */
+DPC_API int dpc_project_forward(dpc_plan* plan, int first, int count, int skip_last_copy);
+/* Error of one layer against the prediction below: Gaussian e = z - mu, or softmax
+ * cross-entropy when the layer has DPC_LAYER_SOFTMAX_CE.  with_energy accumulates into the
+ * plan's energy accumulator (CPUBackend.cpp:602-629, 658-714). */
+DPC_API int dpc_error(dpc_plan* plan, int layer, int with_energy);
+/* fe[l] = e[l+1] * f'(preact[l]) over a range (the first two lines of UpdateState /
+ * UpdateWeights, DirectKPPCLayer.cpp:334-335,372-373). */
+DPC_API int dpc_feedback_error(dpc_plan* plan, int first, int count);
+/* UpdateState for every layer of the range (all independent, Jacobi):
+ * DirectKP/Full z += ir*(a*fe·W - e) (+momentum, +residual), Simple
+ * z += ir*(f'(z)*(e_above·W) - e); layers without weights or upper neighbour: z -= ir*e
+ * (DirectKPPCLayer.cpp:318-359, FullPCLayer.cpp:300-380, SimplePCLayer.cpp:185-257).
+ * Layers listed as clamped by the caller must simply be left out of the range. */
+DPC_API int dpc_update_state(dpc_plan* plan, int first, int count);
+/* z -= ir*e for one layer (the "output layer" branch of UpdateState). */
+DPC_API int dpc_relax(dpc_plan* plan, int layer);
+/* DirectFeedbackUpdate for every layer of the range whose upper neighbour has Psi:
+ * proj = (e_T·Psi[l+1]ᵀ) * f'(preact[l]);  W[l] += (fl*a/B) projᵀ·z[l]
+ * (DirectKPPCLayer.cpp:503-549, FullPCLayer.cpp:514-572; decay_w applies the FullPC
+ * (1-lmbda) pre-scale). */
+DPC_API int dpc_direct_feedback(dpc_plan* plan, int first, int count, int decay_w);
+/* UpdateWeights for every layer of the range from fe[l] (DirectKP/Full) or e[l+1]
+ * (Simple): W, b and Psi with SGD / Adam / AdamW, optional row centring
+ * (DirectKPPCLayer.cpp:361-501, FullPCLayer.cpp:382-512, SimplePCLayer.cpp:259-350,
+ * CPUBackend.cpp:250-272, 721-772). */
+DPC_API int dpc_update_weights(dpc_plan* plan, int first, int count, int center_rows);
+/* Energy accumulator of the plan (device-resident double). */
+DPC_API int dpc_energy_reset(dpc_plan* plan);
+DPC_API int dpc_energy_read(dpc_plan* plan, double* out); /* synchronous */
+
+/* ------------------------------------------------------------------------------------
+ * Networks with host buffers: the binding surface.  kind: 0 SimplePCNetwork,
+ * 1 DirectKPPCNetwork, 2 FullPCNetwork (include/deepity/networks/*.h).
+ * ---------------------------------------------------------------------------------- */
+typedef struct dpcn_net dpcn_net;
+
+DPC_API int dpcn_create(int kind, int batch, int device, dpcn_net** out);
+DPC_API int dpcn_destroy(dpcn_net* net);
+/* AddLayer(size, nextSize, terminalSize, lr, ir, fl, lmbda, aType, dType)
+ * (include/deepity/networks/DirectKPPCNetwork.h:80-81); terminal_size and fl are ignored
+ * for kind 0. */
+DPC_API int dpcn_add_layer(dpcn_net* net, int size, int next_size, int terminal_size, float lr,
+                           float ir, float fl, float lmbda, int act);
+/* Options by name, before or after compile as the reference allows: "optimizer",
+ * "psi_optimizer" (ivalue = dpc_opt), "center_weights", "psi_decay" (fvalue),
+ * "learning_rate", "feedback_rate", "inference_rate" (fvalue), "cross_entropy", "mupc",
+ * "residual", "ipc", "momentum" (ivalue on/off, fvalue beta), "precision" (dpc_precision),
+ * "use_graph" (capture the step into a CUDA graph, default on). */
+DPC_API int dpcn_set_option(dpcn_net* net, const char* name, int ivalue, float fvalue);
+DPC_API int dpcn_compile(dpcn_net* net);
+DPC_API int dpcn_num_layers(dpcn_net* net);
+/* Tensor access by layer and name: "z" "e" "mu" "preact" "W" "b" "Psi" "weight.m"
+ * "weight.v" "bias.m" "bias.v" "psi.m" "psi.v" (Layer::GetStateDict names,
+ * src/layers/DirectKPPCLayer.cpp:219-241).  count = logical element count. */
+DPC_API int64_t dpcn_tensor_size(dpcn_net* net, int layer, const char* name);
+DPC_API int dpcn_get_tensor(dpcn_net* net, int layer, const char* name, float* host_out,
+                            int64_t count);
+DPC_API int dpcn_set_tensor(dpcn_net* net, int layer, const char* name, const float* host_in,
+                            int64_t count);
+/* Device pointer of a tensor (zero-copy consumers; FullPCNetwork::TrainStepDevice idea). */
+DPC_API int dpcn_tensor_ptr(dpcn_net* net, int layer, const char* name, void** out,
+                            int64_t* row_stride);
+/* RandomizeWeights(rng, distribution): N(0, sqrt(2/(size+next))) for W and
+ * N(0, sqrt(2/(size+terminal))) for Psi from a host mt19937 stream
+ * (src/layers/DirectKPPCLayer.cpp:184-217); parity tests set weights explicitly. */
+DPC_API int dpcn_randomize(dpcn_net* net, uint32_t seed);
+/* TrainStep(x, y, T) -> energy; x,y host pointers (synchronous: returns the energy). */
+DPC_API int dpcn_train_step(dpcn_net* net, const float* x, int64_t nx, const float* y,
+                            int64_t ny, int steps, float* energy_out);
+/* Same with x,y already on this device; energy_out may be NULL to skip the read-back
+ * (then the call is stream-ordered only). */
+DPC_API int dpcn_train_step_device(dpcn_net* net, const float* x_dev, int64_t nx,
+                                   const float* y_dev, int64_t ny, int steps,
+                                   float* energy_out);
+/* SimplePCNetwork::TrainStepWithProjection (src/networks/SimplePCNetwork.cpp:179-252) and the
+ * Python-level SimplePCN.train_step loop (deepity/SimplePCN.py:269-293; mode 2 returns the
+ * SUM of per-step energies).  mode: 0 TrainStep, 1 with projection, 2 python loop. */
+DPC_API int dpcn_train_step_mode(dpcn_net* net, int mode, const float* x, int64_t nx,
+                                 const float* y, int64_t ny, int steps, float* energy_out);
+/* Predict(x, T) -> terminal beliefs [B, terminal] into host_out. */
+DPC_API int dpcn_predict(dpcn_net* net, const float* x, int64_t nx, int steps,
+                         int with_projection, float* host_out, int64_t nout);
+/* Kernel launches issued by the network's context so far. */
+DPC_API int64_t dpcn_launch_count(dpcn_net* net);
+/* Algorithmic FLOPs of one train step with `steps` settling steps (GEMM terms only). */
+DPC_API double dpcn_train_step_flops(dpcn_net* net, int steps);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEEPITY_B200_H */

@@ -1,0 +1,116 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Every case runs K train steps on identical seeded inputs and explicitly set W/b/Psi and
+compares the energy of every step, every layer's z and e after the last step, the updated
+W, b and Psi, and a prediction — against the golden fixtures (outputs of the reference's own
+CPU code) and against the numpy oracle run live.  Bound: common.TOL (1e-4 relative per
+tensor) for the fp32 path, common.ADAM_TOL where an Adam-type optimizer is on.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from common import (ADAM_TOL, TF32_TOL, TOL, compare_outputs, run_gpu, run_oracle)
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+CASES = json.load(open(os.path.join(GOLDEN, "cases.json")))
+
+
+def case_tol(case):
+    o = case.get("options", {})
+    adam = o.get("optimizer", "SGD") != "SGD" or o.get("psi_optimizer", "SGD") != "SGD"
+    return ADAM_TOL if adam else TOL
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_gpu_matches_golden(name, built_library):
+    case = CASES[name]
+    ref = dict(np.load(os.path.join(GOLDEN, name + ".npz")))
+    got = run_gpu(case)
+    compare_outputs(ref, got, case_tol(case), name)
+
+
+@pytest.mark.parametrize("name", ["dkp_tanh_small", "full_gelu_ce_adam", "simple_sigmoid_small"])
+def test_gpu_without_graph_matches_golden(name, built_library):
+    case = CASES[name]
+    ref = dict(np.load(os.path.join(GOLDEN, name + ".npz")))
+    compare_outputs(ref, run_gpu(case, use_graph=False), case_tol(case), name)
+
+
+EXTRA = {
+    # ragged everything: widths not multiples of 4, batch not a multiple of the tile
+    "dkp_ragged": dict(kind="dkp", sizes=[13, 37, 37, 5, 3], batch=7, T=3, steps=2,
+                       hyper=dict(lr=0.02, ir=0.1, fl=0.01, lmbda=0.0, act="sigmoid")),
+    "dkp_single_weight_layer": dict(kind="dkp", sizes=[9, 4], batch=5, T=2, steps=2,
+                                    hyper=dict(lr=0.02, ir=0.1, fl=0.01, lmbda=0.0, act="tanh")),
+    "dkp_batch_one": dict(kind="dkp", sizes=[16, 16, 16, 4], batch=1, T=2, steps=2,
+                          hyper=dict(lr=0.02, ir=0.1, fl=0.01, lmbda=0.0, act="tanh")),
+    "dkp_wide_uniform": dict(kind="dkp", sizes=[64] + [128] * 6 + [10], batch=128, T=2, steps=2,
+                             hyper=dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.0, act="tanh")),
+    "dkp_esigmoid_hardtanh": dict(kind="dkp", sizes=[20, 30, 30, 6], batch=10, T=2, steps=2,
+                                  hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0,
+                                             act="esigmoid")),
+    "dkp_zero_steps": dict(kind="dkp", sizes=[20, 30, 30, 6], batch=10, T=0, steps=2,
+                           hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="hard_tanh")),
+    "simple_relu_ce": dict(kind="simple", sizes=[30, 40, 10], batch=16, T=5, steps=3,
+                           hyper=dict(lr=0.01, ir=0.1, lmbda=0.0, act="relu"),
+                           options=dict(cross_entropy=1)),
+    "full_plain": dict(kind="full", sizes=[30, 40, 40, 10], batch=16, T=4, steps=3,
+                       hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="gelu")),
+    "full_adamw": dict(kind="full", sizes=[33, 40, 40, 10], batch=24, T=3, steps=3,
+                       hyper=dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.01, act="tanh"),
+                       options=dict(optimizer="ADAMW", psi_optimizer="ADAMW")),
+}
+
+
+@pytest.mark.parametrize("name", sorted(EXTRA))
+def test_gpu_matches_live_oracle(name, built_library):
+    case = EXTRA[name]
+    compare_outputs(run_oracle(case), run_gpu(case), case_tol(case), name)
+
+
+def test_training_continues_to_track_the_oracle(built_library):
+    """Ten consecutive steps: errors must not accumulate beyond the bound."""
+    case = dict(kind="dkp", sizes=[32, 64, 64, 64, 10], batch=32, T=2, steps=10,
+                hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="tanh"))
+    compare_outputs(run_oracle(case), run_gpu(case), TOL, "ten steps")
+
+
+def test_energy_decreases_over_training(built_library):
+    # the sanity property of the reference's t*TrainStepSanity tests
+    case = dict(kind="dkp", sizes=[32, 64, 64, 10], batch=32, T=2, steps=8,
+                hyper=dict(lr=0.02, ir=0.1, fl=0.01, lmbda=0.0, act="tanh"))
+    e = run_gpu(case)["energies"]
+    assert np.all(np.isfinite(e)) and e[-1] < e[0]
+
+
+def test_train_step_device_matches_host_entry(built_library):
+    import torch
+    from common import build_gpu_net
+    case = CASES["dkp_tanh_small"]
+    a, x, y = build_gpu_net(case)
+    b, _, _ = build_gpu_net(case)
+    xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+    torch.cuda.synchronize()
+    for _ in range(2):
+        ea = a.train_step(x, y, case["T"])
+        eb = b.train_step_device(xd, yd, case["T"])
+        assert abs(ea - eb) <= 1e-6 * max(1.0, abs(ea))
+    for l in range(len(case["sizes"]) - 1):
+        assert np.array_equal(a.get_tensor(l, "W"), b.get_tensor(l, "W"))
+
+
+def test_launch_counter_counts_graph_replays(built_library):
+    from common import build_gpu_net
+    net, x, y = build_gpu_net(CASES["dkp_tanh_small"])
+    net.train_step(x, y, 2)
+    n0 = net.launch_count
+    net.train_step(x, y, 2)
+    per_step = net.launch_count - n0
+    assert per_step > 5
+    net.train_step(x, y, 2)
+    assert net.launch_count - n0 == 2 * per_step
