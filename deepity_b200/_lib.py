@@ -69,6 +69,8 @@ SIGNATURES = {
     "dpcn_train_step_device": (_i, [_vp, _vp, _i64, _vp, _i64, _i, c_f32p]),
     "dpcn_train_step_mode": (_i, [_vp, _i, c_f32p, _i64, c_f32p, _i64, _i, c_f32p]),
     "dpcn_predict": (_i, [_vp, c_f32p, _i64, _i, _i, c_f32p, _i64]),
+    "dpcn_context": (_vp, [_vp]),
+    "dpcn_plan": (_vp, [_vp]),
     "dpcn_launch_count": (_i64, [_vp]),
     "dpcn_train_step_flops": (ctypes.c_double, [_vp, _i]),
 }

@@ -1267,6 +1267,19 @@ int dpcn_predict(dpcn_net* net, const float* x, int64_t nx, int steps, int with_
   });
 }
 
+dpc_ctx* dpcn_context(dpcn_net* net)
+{
+  return net ? net->net->Context() : nullptr;
+}
+
+dpc_plan* dpcn_plan(dpcn_net* net)
+{
+  if (!net)
+    return nullptr;
+  net->net->FlushSettings();
+  return net->net->Plan();
+}
+
 int64_t dpcn_launch_count(dpcn_net* net)
 {
   return net ? net->net->LaunchCount() : 0;

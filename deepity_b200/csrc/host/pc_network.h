@@ -150,6 +150,8 @@ public:
   dpc_ctx* Context() noexcept { return ctx; }
   dpc_plan* Plan() noexcept { return plan; }
   bool IsCompiled() const noexcept { return plan != nullptr; }
+  // Re-uploads the layer table if a setter changed it since the last step.
+  void FlushSettings() { SyncPlan(); }
   int64_t LaunchCount() const;
   double TrainStepFlops(int steps) const;
 

@@ -271,6 +271,11 @@ DPC_API int dpcn_train_step_mode(dpcn_net* net, int mode, const float* x, int64_
 /* Predict(x, T) -> terminal beliefs [B, terminal] into host_out. */
 DPC_API int dpcn_predict(dpcn_net* net, const float* x, int64_t nx, int steps,
                          int with_projection, float* host_out, int64_t nout);
+/* The network's context and plan, for callers that drive single phases themselves
+ * (layer-sharded multi-GPU stepping, per-kernel timing).  Valid after dpcn_compile;
+ * owned by the network. */
+DPC_API dpc_ctx* dpcn_context(dpcn_net* net);
+DPC_API dpc_plan* dpcn_plan(dpcn_net* net);
 /* Kernel launches issued by the network's context so far. */
 DPC_API int64_t dpcn_launch_count(dpcn_net* net);
 /* Algorithmic FLOPs of one train step with `steps` settling steps (GEMM terms only). */
