@@ -746,5 +746,5 @@ int dpc_energy_read(dpc_plan* p, double* out)
                            p->ctx->stream));
   DPC_CUDA(cudaStreamSynchronize(p->ctx->stream));
   *out = *p->energy_host;
-  return DPC_OK;
+  return tc_check_error(p);
 }

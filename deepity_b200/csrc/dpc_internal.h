@@ -70,4 +70,7 @@ void tc_plan_free(dpc_plan* plan);
 int tc_forward(dpc_plan* plan, int first, int count, int flags);
 int tc_update_state(dpc_plan* plan, int first, int count);
 int tc_weight_gemm(dpc_plan* plan, int first, int count, int mode);
+// Synchronous: reads the device-side status flag the kernels raise when a bounded wait runs
+// out; DPC_ERR_TIMEOUT if it was raised.
+int tc_check_error(dpc_plan* plan);
 } // namespace dpc

@@ -281,9 +281,12 @@ __global__ void __launch_bounds__(NTHREADS)
           if (L.flags & DPC_LAYER_RESIDUAL)
             mu += L.z[o];
         }
-        if (L.preact)
-          L.preact[o] = pre;
-        L.mu[o] = mu;
+        if (!(flags & DPC_FWD_TRANSIENT))
+        {
+          if (L.preact)
+            L.preact[o] = pre;
+          L.mu[o] = mu;
+        }
         if (do_copy)
           Lup->z[o] = mu;
         float e = 0.0f;

@@ -1,25 +1,896 @@
-// Tensor-core (tcgen05 / TMEM / TMA) path — placeholder until the kernels land: every
-// entry reports "range not eligible" so the CUDA-core kernels run.
+// Tensor-core path: grouped, persistent, warp-specialised GEMM kernels for sm_100a.
+//
+//   * operands staged by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a multi-stage
+//     shared-memory ring, one tensor map per operand with the LAYER as outermost coordinate,
+//     so one launch walks every (layer, tile) of a run of identical square layers;
+//   * tcgen05.mma (kind::tf32, M=128, N=128|256, K=8) issued by one thread, fp32 accumulators
+//     in tensor memory, double-buffered so the epilogue of tile i overlaps the main loop of
+//     tile i+1;
+//   * fp32 mode = 3xTF32: the raw fp32 tile feeds the tensor core as the "high" part (the
+//     hardware reads the top 19 bits), four extra warps compute the exact remainders into a
+//     second pair of tiles, and each k-step issues A*B_lo + A_lo*B + A*B;
+//   * the predictive-coding elementwise work runs in the epilogue straight out of tensor
+//     memory: bias + activation + error + energy + feedback error (forward), the state
+//     update (feedback), the SGD weight update (weight-shaped product).
+//
+// Three operand layouts are needed (row-major fp32 everywhere):
+//   forward   D[B,n]  = z[B,s]  · W[n,s]^T      A K-major,  B K-major
+//   feedback  D[B,s]  = fe[B,n] · W[n,s]        A K-major,  B MN-major
+//   weights   D[n,s]  = fe[B,n]^T · z[B,s]      A MN-major, B MN-major
+//
+// Every wait on an mbarrier is bounded by a clock; on expiry the kernel raises a flag in
+// global memory, all roles drain and the CTA frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
 #include "dpc_internal.h"
+#include "dpc_math.cuh"
 
 namespace dpc
 {
+namespace
+{
+constexpr int TBM = 128;  // UMMA M (rows of D per tile)
+constexpr int TBK = 32;   // fp32 elements per pipeline stage along K = one 128-byte swizzle row
+constexpr int UMMA_K = 8; // K of one tcgen05.mma.kind::tf32
+constexpr long long kWaitCycles = 4000000000LL; // ~2 s at 1.9 GHz
+
+enum
+{
+  TC_FWD = 0,
+  TC_FB = 1,
+  TC_WG = 2
+};
+constexpr int WG_LEARN_MODE = 0, WG_DFA_MODE = 1;
+
+struct TcState
+{
+  bool ok = false;
+  CUtensorMap z_km, fe_km, w_km128, w_km256, z_mn, fe_mn, w_mn;
+  int* error_flag = nullptr; // device
+  int* error_host = nullptr; // pinned
+  int max_smem = 0;
+};
+
+struct TcParams
+{
+  const dpc_layer* layers;
+  int first, count, n_layers, batch;
+  int run_first;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int flags, mode;
+  double* energy;
+  int* error_flag;
+};
+
+// ------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(smem_u32(bar)), "r"(parity)
+               : "memory");
+  return ok;
+}
+// Bounded wait: false when the wait was abandoned (own clock ran out, or another role
+// already gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
+{
+  if (mbar_try_wait(bar, parity))
+    return true;
+  const long long t0 = clock64();
+  for (;;)
+  {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity))
+        return true;
+    if (*abort_flag)
+      return false;
+    if (clock64() - t0 > kWaitCycles)
+    {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1, int c2)
+{
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+               " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before()
+{
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after()
+{
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar)
+{
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
+{
+  uint32_t r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+               "[%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                 "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                 "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                 "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+                 "=r"(r[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor (descriptor version 1).  layout: 2 = 128-byte swizzle of
+// 16-byte chunks (K-major tiles), 1 = 128-byte swizzle of 32-byte chunks, the only layout the
+// tensor core accepts for MN-major 32-bit operands.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout)
+{
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+
+// 256-bit global accesses: eight consecutive floats, 32-byte aligned (one full sector).
+__device__ __forceinline__ void ld8(const float* p, float* r)
+{
+  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]),
+                 "=f"(r[7])
+               : "l"(p));
+}
+__device__ __forceinline__ void st8(float* p, const float* r)
+{
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(r[0]),
+               "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7])
+               : "memory");
+}
+
+// ------------------------------------------------------------------------------ kernel
+// Warp roles: 0 TMA producer, 1 MMA issuer (+ tensor-memory owner), 2..9 epilogue,
+// 10..13 remainder ("lo") transform (3xTF32 only).
+template <int OP, int BN, bool THREE_X>
+struct Cfg
+{
+  static constexpr bool A_MN = (OP == TC_WG);
+  static constexpr bool B_MN = (OP != TC_FWD);
+  static constexpr int A_BYTES = TBM * TBK * 4;
+  static constexpr int B_BYTES = BN * TBK * 4;
+  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (THREE_X ? 2 : 1);
+  static constexpr int STAGES = (196608 / STAGE_BYTES) < 2 ? 2 : (196608 / STAGE_BYTES);
+  static constexpr int EPI_WARPS = 8;
+  static constexpr int THREADS = (2 + EPI_WARPS + (THREE_X ? 4 : 0)) * 32;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                                    ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                    ((uint32_t)(TBM >> 4) << 24);
+};
+
+template <int OP, int BN, bool THREE_X>
+__global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
+    pc_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 const TcParams P)
+{
+  using C = Cfg<OP, BN, THREE_X>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* xf = bars + 2 * C::STAGES;
+  uint64_t* tfull = bars + 3 * C::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_per_layer = P.tiles_m * P.tiles_n;
+  const int total_tiles = P.count * tiles_per_layer;
+  const int kblocks = P.K / TBK;
+
+  if (threadIdx.x == 0)
+  {
+    for (int s = 0; s < C::STAGES; ++s)
+    {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&xf[s], 4);
+    }
+    for (int a = 0; a < 2; ++a)
+    {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], C::EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1)
+  {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_holder)),
+                 "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0)
+  {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0)
+    {
+      int it = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x)
+      {
+        const int lrel = t / tiles_per_layer, rem = t % tiles_per_layer;
+        const int m0 = (rem / P.tiles_n) * TBM, n0 = (rem % P.tiles_n) * BN;
+        const int lcoord = P.first + lrel - P.run_first;
+        for (int kb = 0; kb < kblocks; ++kb, ++it)
+        {
+          const int s = it % C::STAGES;
+          if (!mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag))
+          {
+            alive = false;
+            break;
+          }
+          uint8_t* a_dst = stage_base + s * C::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + C::A_BYTES;
+          mbar_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
+          const int k0 = kb * TBK;
+          if (!C::A_MN)
+            tma_load_3d(a_dst, &mapA, &full[s], k0, m0, lcoord);
+          else
+            for (int i = 0; i < TBM / 32; ++i)
+              tma_load_3d(a_dst + i * (TBK * 128), &mapA, &full[s], m0 + 32 * i, k0, lcoord);
+          if (!C::B_MN)
+            tma_load_3d(b_dst, &mapB, &full[s], k0, n0, lcoord);
+          else
+            for (int i = 0; i < BN / 32; ++i)
+              tma_load_3d(b_dst + i * (TBK * 128), &mapB, &full[s], n0 + 32 * i, k0, lcoord);
+        }
+      }
+      if (!alive)
+      {
+        // Let copies already in flight land before the CTA's shared memory goes away.
+        for (int s = 0; s < C::STAGES; ++s)
+        {
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000LL)
+          {
+          }
+        }
+      }
+    }
+  }
+  else if (warp == 1)
+  {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0)
+    {
+      int it = 0, tile_iter = 0;
+      bool alive = true;
+      const uint32_t a_lbo = C::A_MN ? TBK * 128 : 16, b_lbo = C::B_MN ? TBK * 128 : 16;
+      const uint32_t a_adv = C::A_MN ? 1024 : UMMA_K * 4, b_adv = C::B_MN ? 1024 : UMMA_K * 4;
+      // MN-major tiles: 4 k-rows of 128 bytes per swizzle atom (512 B between k-groups), slabs of
+      // 32 columns TBK*128 bytes apart.  K-major tiles: 8 rows per atom (1024 B between groups).
+      const uint32_t a_sbo = C::A_MN ? 512 : 1024, b_sbo = C::B_MN ? 512 : 1024;
+      const uint32_t a_lay = C::A_MN ? 1 : 2, b_lay = C::B_MN ? 1 : 2;
+      for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++tile_iter)
+      {
+        const int acc = tile_iter & 1;
+        if (!mbar_wait(&tempty[acc], ((tile_iter >> 1) & 1) ^ 1, abort_flag))
+          break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it)
+        {
+          const int s = it % C::STAGES;
+          uint64_t* ready = THREE_X ? &xf[s] : &full[s];
+          if (!mbar_wait(ready, (it / C::STAGES) & 1, abort_flag))
+          {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(stage_base + s * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+          const uint32_t alo_addr = b_addr + C::B_BYTES;
+          const uint32_t blo_addr = alo_addr + C::A_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < TBK / UMMA_K; ++ks)
+          {
+            const uint64_t da = make_desc(a_addr + ks * a_adv, a_lbo, a_sbo, a_lay);
+            const uint64_t db = make_desc(b_addr + ks * b_adv, b_lbo, b_sbo, b_lay);
+            const uint32_t first = (kb | ks) != 0;
+            if (THREE_X)
+            {
+              const uint64_t dal = make_desc(alo_addr + ks * a_adv, a_lbo, a_sbo, a_lay);
+              const uint64_t dbl = make_desc(blo_addr + ks * b_adv, b_lbo, b_sbo, b_lay);
+              tc_mma_tf32(d_tmem, da, dbl, C::IDESC, first);
+              tc_mma_tf32(d_tmem, dal, db, C::IDESC, 1);
+              tc_mma_tf32(d_tmem, da, db, C::IDESC, 1);
+            }
+            else
+              tc_mma_tf32(d_tmem, da, db, C::IDESC, first);
+          }
+          tc_commit(&empty[s]);
+        }
+        if (alive)
+          tc_commit(&tfull[acc]);
+      }
+    }
+  }
+  else if (warp < 2 + C::EPI_WARPS)
+  {
+    // ---------------------------------------------------------------- epilogue
+    // Two (or more) warps share each 32-lane quarter of tensor memory and take alternate
+    // 32-column chunks.  Per chunk: issue every global load first (256-bit vectors, one
+    // full 32-byte sector per lane), then read the accumulators, compute, store.
+    const int quarter = warp & 3; // tensor-memory lanes this warp may read
+    const int grp = (warp - 2) >> 2;
+    constexpr int GROUPS = C::EPI_WARPS / 4;
+    float esum = 0.0f;
+    int tile_iter = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter)
+    {
+      const int lrel = t / tiles_per_layer, rem = t % tiles_per_layer;
+      const int m = (rem / P.tiles_n) * TBM + quarter * 32 + lane;
+      const int n0 = (rem % P.tiles_n) * BN;
+      const int li = P.first + lrel;
+      const dpc_layer L = P.layers[li];
+      const dpc_layer* Lup = (li + 1 < P.n_layers) ? &P.layers[li + 1] : nullptr;
+      const int acc = tile_iter & 1;
+      if (!mbar_wait(&tfull[acc], (tile_iter >> 1) & 1, abort_flag))
+        break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+
+      if (OP == TC_FWD)
+      {
+        const bool next_ce = Lup && (Lup->flags & DPC_LAYER_SOFTMAX_CE);
+        const bool do_err = (P.flags & DPC_FWD_ERR_NEXT) && Lup && !next_ce;
+        const bool do_fe = (P.flags & DPC_FWD_FE) && Lup && !(next_ce && (P.flags & DPC_FWD_ERR_NEXT));
+        const bool do_copy = (P.flags & DPC_FWD_COPY_NEXT) && Lup;
+        const bool store = !(P.flags & DPC_FWD_TRANSIENT);
+        const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
+        // What the epilogue reads from the layer above: its belief (fresh error) or its
+        // stored error (feedback error from the error already in memory).
+        const float* up_src = (do_err && !do_copy) ? Lup->z : ((do_fe && !do_err) ? Lup->e : nullptr);
+        for (int c = grp; c < BN / 32; c += GROUPS)
+        {
+          const size_t o = (size_t)m * P.N + n0 + c * 32;
+          float up[32], v[32];
+          if (up_src)
+          {
+#pragma unroll
+            for (int k = 0; k < 32; k += 8)
+              ld8(up_src + o + k, &up[k]);
+          }
+          tc_ld32(taddr + c * 32, v);
+#pragma unroll
+          for (int k = 0; k < 32; k += 8)
+          {
+            float bb[8], pre[8], mu[8], d[8], e[8];
+            ld8(L.b + n0 + c * 32 + k, bb);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+            {
+              pre[q] = L.a * v[k + q] + bb[q];
+              if (do_fe)
+                act_both(L.act, pre[q], mu[q], d[q]);
+              else
+                mu[q] = act_fwd(L.act, pre[q]), d[q] = 1.0f;
+            }
+            if (residual)
+            {
+              float zz[8];
+              ld8(L.z + o + k, zz);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                mu[q] += zz[q];
+            }
+            if (store)
+            {
+              st8(L.preact + o + k, pre);
+              st8(L.mu + o + k, mu);
+            }
+            if (do_copy)
+              st8(Lup->z + o + k, mu);
+            if (do_err)
+            {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+              {
+                e[q] = do_copy ? 0.0f : up[k + q] - mu[q];
+                esum += e[q] * e[q];
+              }
+              st8(Lup->e + o + k, e);
+            }
+            else if (do_fe)
+            {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                e[q] = up[k + q];
+            }
+            if (do_fe)
+            {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                e[q] *= d[q];
+              st8(L.fe + o + k, e);
+            }
+          }
+        }
+      }
+      else if (OP == TC_FB)
+      {
+        const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
+        for (int c = grp; c < BN / 32; c += GROUPS)
+        {
+          const size_t o = (size_t)m * P.N + n0 + c * 32;
+          float ee[32], zz[32], v[32];
+#pragma unroll
+          for (int k = 0; k < 32; k += 8)
+          {
+            ld8(L.e + o + k, &ee[k]);
+            ld8(L.z + o + k, &zz[k]);
+          }
+          tc_ld32(taddr + c * 32, v);
+#pragma unroll
+          for (int k = 0; k < 32; k += 8)
+          {
+            float fb[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              fb[q] = L.a * v[k + q] - ee[k + q];
+            if (L.v)
+            {
+              float vv[8];
+              ld8(L.v + o + k, vv);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+              {
+                vv[q] = L.momentum_beta * vv[q] + (1.0f - L.momentum_beta) * fb[q];
+                zz[k + q] += L.ir * vv[q];
+              }
+              st8(L.v + o + k, vv);
+            }
+            else
+            {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                zz[k + q] += L.ir * fb[q];
+            }
+            if (residual)
+            {
+              float uu[8];
+              ld8(Lup->e + o + k, uu);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                zz[k + q] += L.ir * uu[q];
+            }
+            st8(L.z + o + k, &zz[k]);
+          }
+        }
+      }
+      else
+      {
+        const float Bf = (float)P.batch;
+        float alpha, decay = 1.0f;
+        if (P.mode == WG_DFA_MODE)
+          alpha = L.fl * L.a / Bf;
+        else
+        {
+          alpha = L.a * L.lr / Bf;
+          if (L.lmbda > 0.0f)
+            decay = 1.0f - L.lmbda;
+        }
+        for (int c = grp; c < BN / 32; c += GROUPS)
+        {
+          const size_t o = (size_t)m * P.N + n0 + c * 32;
+          float w[32], v[32];
+#pragma unroll
+          for (int k = 0; k < 32; k += 8)
+            ld8(L.W + o + k, &w[k]);
+          tc_ld32(taddr + c * 32, v);
+#pragma unroll
+          for (int k = 0; k < 32; k += 8)
+          {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+            {
+              if (decay != 1.0f)
+                w[k + q] *= decay;
+              w[k + q] = fmaf(alpha, v[k + q], w[k + q]);
+            }
+            st8(L.W + o + k, &w[k]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&tempty[acc]);
+    }
+    if (OP == TC_FWD && (P.flags & DPC_FWD_ENERGY))
+    {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        esum += __shfl_xor_sync(0xffffffffu, esum, o);
+      if (lane == 0)
+        atomicAdd(P.energy, (double)(0.5f * esum));
+    }
+  }
+  else if (THREE_X)
+  {
+    // ---------------------------------------------------------------- remainder transform
+    // lo = x - (x with the low 13 mantissa bits cleared): exactly what the tensor core drops
+    // when it reads the raw tile as TF32.  Elementwise on identical offsets, so the swizzled
+    // layout of the tile carries over unchanged.
+    const int tid = threadIdx.x - (2 + C::EPI_WARPS) * 32;
+    int it = 0;
+    bool alive = true;
+    for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x)
+    {
+      for (int kb = 0; kb < kblocks; ++kb, ++it)
+      {
+        const int s = it % C::STAGES;
+        if (!mbar_wait(&full[s], (it / C::STAGES) & 1, abort_flag))
+        {
+          alive = false;
+          break;
+        }
+        const float4* src = reinterpret_cast<const float4*>(stage_base + s * C::STAGE_BYTES);
+        float4* dst = reinterpret_cast<float4*>(stage_base + s * C::STAGE_BYTES + C::A_BYTES +
+                                                C::B_BYTES);
+        constexpr int N4 = (C::A_BYTES + C::B_BYTES) / 16;
+#pragma unroll 4
+        for (int i = tid; i < N4; i += 128)
+        {
+          const float4 x = src[i];
+          float4 r;
+          r.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xffffe000u);
+          r.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
+          r.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xffffe000u);
+          r.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xffffe000u);
+          dst[i] = r;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&xf[s]);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag)
+    atomicExch(P.error_flag, 1);
+  if (warp == 1)
+  {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+  static EncodeTiledFn fn = nullptr;
+  if (!fn)
+  {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// fp32 tensor [layers][rows][cols] (cols contiguous) with a (32 x box_rows x 1) box.
+bool make_map(CUtensorMap* map, const float* base, int cols, int rows, int layers,
+              int64_t layer_stride_elems, int box_rows, bool mn_major)
+{
+  EncodeTiledFn fn = encode_fn();
+  if (!fn)
+    return false;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)layers};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * 4, (cuuint64_t)layer_stride_elems * 4};
+  cuuint32_t box[3] = {32, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int OP, int BN, bool THREE_X>
+int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P)
+{
+  using C = Cfg<OP, BN, THREE_X>;
+  static bool configured = false;
+  auto kern = pc_tc_kernel<OP, BN, THREE_X>;
+  if (!configured)
+  {
+    if (C::SMEM_BYTES > st->max_smem)
+      return 1;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::SMEM_BYTES);
+    if (e != cudaSuccess)
+      return cuda_fail(e, "cudaFuncSetAttribute(tensor-core kernel)");
+    configured = true;
+  }
+  const int total = P.count * P.tiles_m * P.tiles_n;
+  const int grid = std::min(total, p->ctx->sm_count);
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, p->ctx->stream>>>(a, b, P);
+  p->ctx->launches += 1;
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess)
+    return cuda_fail(cudaGetLastError(), "tensor-core kernel launch");
+  return DPC_OK;
+}
+
+bool range_in_run(const dpc_plan* p, int first, int count)
+{
+  return p->run.count > 0 && count > 0 && first >= p->run.first &&
+         first + count <= p->run.first + p->run.count;
+}
+} // namespace
+
 int tc_plan_init(dpc_plan* plan)
 {
   plan->run = TensorRun();
+  auto* st = new TcState();
+  plan->tc = st;
+  if (getenv("DPC_DISABLE_TENSOR_CORES"))
+    return DPC_OK;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, plan->ctx->device) != cudaSuccess || prop.major != 10)
+    return DPC_OK; // tcgen05 exists on sm_100 only; other devices keep the CUDA-core path
+  st->max_smem = (int)prop.sharedMemPerBlockOptin;
+  const int B = plan->batch, n = plan->n;
+  if (B % TBM != 0)
+    return DPC_OK;
+  // Longest run of identical square DirectKP/Full layers at constant strides.
+  int best_first = 0, best_count = 0;
+  int i = 0;
+  while (i + 1 < n)
+  {
+    const dpc_layer& L0 = plan->h[i];
+    const bool ok0 = L0.next_size == L0.size && L0.size % 256 == 0 && L0.size >= 256 &&
+                     !(L0.flags & DPC_LAYER_INPUT_ACT) && L0.fe && L0.preact &&
+                     ((uintptr_t)L0.z % 128 == 0) && ((uintptr_t)L0.W % 128 == 0) &&
+                     ((uintptr_t)L0.fe % 128 == 0);
+    if (!ok0)
+    {
+      ++i;
+      continue;
+    }
+    int j = i + 1;
+    int64_t zs = 0, ws = 0, fs = 0;
+    while (j + 1 < n)
+    {
+      const dpc_layer& Lj = plan->h[j];
+      const dpc_layer& Lp = plan->h[j - 1];
+      if (Lj.size != L0.size || Lj.next_size != L0.size || (Lj.flags & DPC_LAYER_INPUT_ACT))
+        break;
+      const int64_t dz = Lj.z - Lp.z, dw = Lj.W - Lp.W, df = Lj.fe - Lp.fe;
+      if (j == i + 1)
+        zs = dz, ws = dw, fs = df;
+      if (dz != zs || dw != ws || df != fs || dz <= 0 || dw <= 0 || df <= 0)
+        break;
+      ++j;
+    }
+    if (j - i > best_count)
+    {
+      best_first = i, best_count = j - i;
+      plan->run.z_stride = zs, plan->run.w_stride = ws, plan->run.out_stride = fs;
+    }
+    i = j;
+  }
+  if (best_count < 1)
+    return DPC_OK;
+  if (best_count == 1)
+  {
+    const dpc_layer& L0 = plan->h[best_first];
+    plan->run.z_stride = (int64_t)B * L0.size;
+    plan->run.w_stride = (int64_t)L0.size * L0.size;
+    plan->run.out_stride = (int64_t)B * L0.size;
+  }
+  const dpc_layer& L0 = plan->h[best_first];
+  const int H = L0.size;
+  bool ok = true;
+  ok &= make_map(&st->z_km, L0.z, H, B, best_count, plan->run.z_stride, TBM, false);
+  ok &= make_map(&st->fe_km, L0.fe, H, B, best_count, plan->run.out_stride, TBM, false);
+  ok &= make_map(&st->w_km128, L0.W, H, H, best_count, plan->run.w_stride, 128, false);
+  ok &= make_map(&st->w_km256, L0.W, H, H, best_count, plan->run.w_stride, 256, false);
+  ok &= make_map(&st->z_mn, L0.z, H, B, best_count, plan->run.z_stride, 32, true);
+  ok &= make_map(&st->fe_mn, L0.fe, H, B, best_count, plan->run.out_stride, 32, true);
+  ok &= make_map(&st->w_mn, L0.W, H, H, best_count, plan->run.w_stride, 32, true);
+  if (!ok)
+    return DPC_OK; // the driver refused a tensor map: stay on the CUDA-core path
+  if (cudaMalloc(&st->error_flag, sizeof(int)) != cudaSuccess ||
+      cudaMemset(st->error_flag, 0, sizeof(int)) != cudaSuccess ||
+      cudaMallocHost(&st->error_host, sizeof(int)) != cudaSuccess)
+    return DPC_OK;
+  *st->error_host = 0;
+  st->ok = true;
+  plan->run.first = best_first;
+  plan->run.count = best_count;
+  plan->run.width = H;
   return DPC_OK;
 }
-void tc_plan_free(dpc_plan*) {}
-int tc_forward(dpc_plan*, int, int, int)
+
+void tc_plan_free(dpc_plan* plan)
 {
-  return 1;
+  auto* st = static_cast<TcState*>(plan->tc);
+  if (!st)
+    return;
+  if (st->error_flag)
+    cudaFree(st->error_flag);
+  if (st->error_host)
+    cudaFreeHost(st->error_host);
+  delete st;
+  plan->tc = nullptr;
+  plan->run = TensorRun();
 }
-int tc_update_state(dpc_plan*, int, int)
+
+int tc_check_error(dpc_plan* plan)
 {
-  return 1;
+  auto* st = static_cast<TcState*>(plan->tc);
+  if (!st || !st->ok)
+    return DPC_OK;
+  if (cudaMemcpyAsync(st->error_host, st->error_flag, sizeof(int), cudaMemcpyDeviceToHost,
+                      plan->ctx->stream) != cudaSuccess ||
+      cudaStreamSynchronize(plan->ctx->stream) != cudaSuccess)
+    return fail(DPC_ERR_CUDA, "reading the tensor-core status flag failed");
+  if (*st->error_host)
+  {
+    cudaMemsetAsync(st->error_flag, 0, sizeof(int), plan->ctx->stream);
+    return fail(DPC_ERR_TIMEOUT, "a tensor-core kernel gave up waiting on a pipeline barrier");
+  }
+  return DPC_OK;
 }
-int tc_weight_gemm(dpc_plan*, int, int, int)
+
+static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int M, int N, int K,
+                            int BN, int flags, int mode)
 {
-  return 1;
+  TcParams P;
+  P.layers = p->d;
+  P.first = first;
+  P.count = count;
+  P.n_layers = p->n;
+  P.batch = p->batch;
+  P.run_first = p->run.first;
+  P.M = M, P.N = N, P.K = K;
+  P.tiles_m = M / TBM;
+  P.tiles_n = N / BN;
+  P.flags = flags;
+  P.mode = mode;
+  P.energy = p->energy;
+  P.error_flag = st->error_flag;
+  return P;
+}
+
+int tc_forward(dpc_plan* p, int first, int count, int flags)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (!st || !st->ok || !range_in_run(p, first, count))
+    return 1;
+  const int H = p->run.width, B = p->batch;
+  if (p->ctx->precision == DPC_PRECISION_TF32)
+    return launch<TC_FWD, 256, false>(p, st, st->z_km, st->w_km256,
+                                      base_params(p, st, first, count, B, H, H, 256, flags, 0));
+  return launch<TC_FWD, 128, true>(p, st, st->z_km, st->w_km128,
+                                   base_params(p, st, first, count, B, H, H, 128, flags, 0));
+}
+
+int tc_update_state(dpc_plan* p, int first, int count)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (!st || !st->ok || !range_in_run(p, first, count))
+    return 1;
+  const int H = p->run.width, B = p->batch;
+  if (p->ctx->precision == DPC_PRECISION_TF32)
+    return launch<TC_FB, 256, false>(p, st, st->fe_km, st->w_mn,
+                                     base_params(p, st, first, count, B, H, H, 256, 0, 0));
+  return launch<TC_FB, 128, true>(p, st, st->fe_km, st->w_mn,
+                                  base_params(p, st, first, count, B, H, H, 128, 0, 0));
+}
+
+int tc_weight_gemm(dpc_plan* p, int first, int count, int mode)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (!st || !st->ok || !range_in_run(p, first, count))
+    return 1;
+  for (int i = first; i < first + count; ++i)
+  {
+    const dpc_layer& L = p->h[i];
+    if (mode == WG_LEARN_MODE && L.opt != DPC_OPT_SGD)
+      return 1;
+    if (mode == WG_DFA_MODE && (i + 1 >= p->n || !p->h[i + 1].Psi || p->h[i + 1].next_size <= 0))
+      return 1;
+  }
+  const int H = p->run.width, B = p->batch;
+  if (p->ctx->precision == DPC_PRECISION_TF32)
+    return launch<TC_WG, 256, false>(p, st, st->fe_mn, st->z_mn,
+                                     base_params(p, st, first, count, H, H, B, 256, 0, mode));
+  return launch<TC_WG, 128, true>(p, st, st->fe_mn, st->z_mn,
+                                  base_params(p, st, first, count, H, H, B, 128, 0, mode));
 }
 } // namespace dpc

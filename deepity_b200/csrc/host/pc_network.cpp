@@ -527,7 +527,7 @@ float PCNetwork::CalculateState(bool needEnergy)
   RequireCompiled();
   const int n = (int)layers.size();
   Check(dpc_zero(ctx, layers[0]->d.e, (size_t)batchSize * layers[0]->d.size * sizeof(float)));
-  ForwardRange(0, n - 1, StateFlags(kind, needEnergy));
+  ForwardRange(0, n - 1, StateFlags(kind, needEnergy) | (needEnergy ? 0 : transientFlag));
   if (layers.back()->d.flags & DPC_LAYER_SOFTMAX_CE)
   {
     Check(dpc_error(plan, n - 1, needEnergy ? 1 : 0));
@@ -589,14 +589,27 @@ void PCNetwork::UpdateWeights()
   {
     // preact/mu are one settling step behind z: refresh them, and with them the local
     // gradient fe = e_above * f'(preact) (src/networks/DirectKPPCNetwork.cpp:481-495).
-    ForwardRange(0, n - 1, DPC_FWD_FE);
+    ForwardRange(0, n - 1, DPC_FWD_FE | transientFlag);
   }
   Check(dpc_update_weights(plan, 0, n - 1, centerWeights ? 1 : 0));
 }
 
+// Inside a whole train step the predictions of the settling passes and of the pre-update
+// refresh are consumed only through the fused e / fe outputs (the final energy pass
+// recomputes and stores them), so those passes need not write preact/mu at all.  A softmax
+// head reads preact of the layer below through a separate kernel, so it keeps the stores.
+struct TransientScope
+{
+  int& flag;
+  TransientScope(int& f, bool on) : flag(f) { flag = on ? DPC_FWD_TRANSIENT : 0; }
+  ~TransientScope() { flag = 0; }
+};
+
 void PCNetwork::RunTrainPhases(int mode, int steps)
 {
   const int n = (int)layers.size();
+  TransientScope scope(transientFlag, kind != NetworkKind::SIMPLE &&
+                                          !(layers.back()->d.flags & DPC_LAYER_SOFTMAX_CE));
   auto settle = [&](bool energy)
   {
     CalculateState(energy);

@@ -184,6 +184,7 @@ private:
   bool useIPC = false, useMomentum = false, useGraph = true, dirty = false;
   bool adamAllocated = false, psiAdamAllocated = false, pendingAsync = false;
   float momentumBeta = 0.9f, psiDecay = -1.0f;
+  int transientFlag = 0; // DPC_FWD_TRANSIENT while a whole train step is being issued
   // key of the graph captured in slot s: mode*1e6+steps (train) or steps (predict); -1 none
   long graphKey[4] = {-1, -1, -1, -1};
 };

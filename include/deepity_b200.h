@@ -178,8 +178,11 @@ enum
   DPC_FWD_ENERGY = 1 << 2,    /* with ERR_NEXT: energy += 0.5*sum e[l+1]^2                 */
   DPC_FWD_FE = 1 << 3,        /* fe[l] = e[l+1] * f'(preact[l]); e[l+1] is the one just
                                  computed with ERR_NEXT, else the one in memory            */
-  DPC_FWD_CACHED = 1 << 4     /* skip the GEMM, reuse preact/mu in memory (a clamped layer's
+  DPC_FWD_CACHED = 1 << 4,    /* skip the GEMM, reuse preact/mu in memory (a clamped layer's
                                  cached prediction, DirectKPPCLayer.cpp:275-280)          */
+  DPC_FWD_TRANSIENT = 1 << 8  /* preact/mu of this pass are consumed only through the fused
+                                 e/fe outputs and recomputed before anyone reads them: do
+                                 not write them to memory                                  */
 };
 
 /* ComputeMuOnly for every layer of the range, all independent

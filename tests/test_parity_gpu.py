@@ -73,6 +73,47 @@ def test_gpu_matches_live_oracle(name, built_library):
     compare_outputs(run_oracle(case), run_gpu(case), case_tol(case), name)
 
 
+# Shapes the tensor-core (tcgen05) kernels take: square layers, width a multiple of 256,
+# batch a multiple of 128, with ordinary CUDA-core layers on both sides of the run.
+TENSOR = {
+    "dkp_tensor_run": dict(kind="dkp", sizes=[256] * 5 + [10], batch=128, T=2, steps=2,
+                           hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="tanh")),
+    "dkp_tensor_run_mixed": dict(kind="dkp", sizes=[100] + [512] * 4 + [10], batch=256, T=3,
+                                 steps=2,
+                                 hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="gelu")),
+    "full_tensor_run_residual_momentum": dict(
+        kind="full", sizes=[64] + [256] * 4 + [10], batch=128, T=3, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="tanh"),
+        options=dict(mupc=1, residual=1, momentum=0.9)),
+}
+
+
+def _tensor_run_of(case, precision):
+    import ctypes
+    from common import build_gpu_net
+    from deepity_b200 import _lib
+    net, _, _ = build_gpu_net(case, precision)
+    lib = _lib.load()
+    first, count = ctypes.c_int(), ctypes.c_int()
+    lib.dpc_plan_tensor_run(lib.dpcn_plan(net._h), ctypes.byref(first), ctypes.byref(count))
+    return first.value, count.value
+
+
+@pytest.mark.parametrize("name", sorted(TENSOR))
+def test_tensor_core_path_fp32_parity(name, built_library):
+    """3xTF32 on the tensor cores is held to the same 1e-4 bound as the CUDA-core path."""
+    case = TENSOR[name]
+    assert _tensor_run_of(case, "fp32")[1] >= 3, "the tensor-core run was not detected"
+    compare_outputs(run_oracle(case), run_gpu(case, precision="fp32"), TOL, name)
+
+
+@pytest.mark.parametrize("name", sorted(TENSOR))
+def test_tensor_core_path_tf32_bound(name, built_library):
+    """One TF32 pass: the reference's own 1e-2 CPU-vs-GPU bound."""
+    case = TENSOR[name]
+    compare_outputs(run_oracle(case), run_gpu(case, precision="tf32"), TF32_TOL, name)
+
+
 def test_training_continues_to_track_the_oracle(built_library):
     """Ten consecutive steps: errors must not accumulate beyond the bound."""
     case = dict(kind="dkp", sizes=[32, 64, 64, 64, 10], batch=32, T=2, steps=10,
