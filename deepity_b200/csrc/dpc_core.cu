@@ -500,7 +500,20 @@ int dpc_project_forward(dpc_plan* p, int first, int count, int skip_last_copy)
   int rc = check_range(p, first, count);
   if (rc != DPC_OK)
     return rc;
-  for (int i = first; i < first + count; ++i)
+  int i0 = first;
+  // The part of the sweep inside the tensor-core run goes out as one persistent launch.
+  if (p->run.count > 0 && first <= p->run.first && first + count >= p->run.first + p->run.count &&
+      !(skip_last_copy && p->run.first + p->run.count + 1 == p->n))
+  {
+    for (int i = first; i < p->run.first; ++i)
+      if ((rc = dpc_forward(p, i, 1, DPC_FWD_COPY_NEXT)) != DPC_OK)
+        return rc;
+    rc = tc_project_forward(p, p->run.first, p->run.count, DPC_FWD_COPY_NEXT);
+    if (rc < 0)
+      return rc;
+    i0 = rc == DPC_OK ? p->run.first + p->run.count : p->run.first;
+  }
+  for (int i = i0; i < first + count; ++i)
   {
     if (p->h[i].next_size <= 0)
       continue;

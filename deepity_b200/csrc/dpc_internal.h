@@ -69,6 +69,7 @@ int tc_plan_init(dpc_plan* plan);
 void tc_plan_free(dpc_plan* plan);
 int tc_forward(dpc_plan* plan, int first, int count, int flags);
 int tc_update_state(dpc_plan* plan, int first, int count);
+int tc_project_forward(dpc_plan* plan, int first, int count, int flags);
 int tc_weight_gemm(dpc_plan* plan, int first, int count, int mode);
 // Synchronous: reads the device-side status flag the kernels raise when a bounded wait runs
 // out; DPC_ERR_TIMEOUT if it was raised.

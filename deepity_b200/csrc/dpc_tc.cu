@@ -51,7 +51,8 @@ constexpr int WG_LEARN_MODE = 0, WG_DFA_MODE = 1;
 struct TcState
 {
   bool ok = false;
-  CUtensorMap z_km, fe_km, w_km128, w_km256, z_mn, fe_mn, w_mn;
+  CUtensorMap z_km, fe_km, w_km64, w_km128, w_km256, z_mn, fe_mn, w_mn;
+  int* chain_counters = nullptr; // device: [layers of the run][row blocks]
   int* error_flag = nullptr; // device
   int* error_host = nullptr; // pinned
   int max_smem = 0;
@@ -67,6 +68,12 @@ struct TcParams
   int flags, mode;
   double* energy;
   int* error_flag;
+  // Chain mode (the sequential forward sweep): CTA b owns output tile b of EVERY layer and
+  // walks the layers in order; chain_counters[layer][row block] counts the epilogue warps
+  // that have published their part of the next layer's input rows.
+  int chain;
+  int* chain_counters;
+  int chain_target;
 };
 
 // ------------------------------------------------------------------------------ PTX
@@ -171,6 +178,21 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
     v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16])
+{
+  uint32_t r[16];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                 "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    v[i] = __uint_as_float(r[i]);
+}
+
 // Shared-memory matrix descriptor (descriptor version 1).  layout: 2 = 128-byte swizzle of
 // 16-byte chunks (K-major tiles), 1 = 128-byte swizzle of 32-byte chunks, the only layout the
 // tensor core accepts for MN-major 32-bit operands.
@@ -186,6 +208,29 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// Chain mode: wait (bounded) until `target` epilogue warps have published one row block of the
+// previous layer's output, then order the TMA (async proxy) reads after that observation.
+__device__ __forceinline__ bool chain_wait(const int* ctr, int target, volatile int* abort_flag)
+{
+  const long long t0 = clock64();
+  for (;;)
+  {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= target)
+      break;
+    if (*abort_flag)
+      return false;
+    if (clock64() - t0 > kWaitCycles)
+    {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
+
 // 256-bit global accesses: eight consecutive floats, 32-byte aligned (one full sector).
 __device__ __forceinline__ void ld8(const float* p, float* r)
 {
@@ -199,6 +244,129 @@ __device__ __forceinline__ void st8(float* p, const float* r)
   asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(r[0]),
                "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7])
                : "memory");
+}
+
+// Forward epilogue of one 128 x BN tile for the 32 rows of one warp.  ACT >= 0 fixes the
+// activation at compile time (the per-element switch disappears), ACT < 0 reads it from the
+// layer.  The operand read from the layer above is fetched one chunk ahead when PREFETCH.
+template <int ACT, int BN, int GROUPS, bool PREFETCH>
+__device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const dpc_layer* Lp,
+                                                  const dpc_layer* Lup, uint32_t taddr, int m,
+                                                  int n0, int grp, float& esum)
+{
+  // Only the fields this pass needs are pulled out of the layer table (registers are scarce).
+  struct
+  {
+    float a;
+    int flags;
+    const float* b;
+    const float* z;
+    float *preact, *mu, *fe;
+  } L;
+  L.a = Lp->a, L.flags = Lp->flags, L.b = Lp->b, L.z = Lp->z;
+  L.preact = Lp->preact, L.mu = Lp->mu, L.fe = Lp->fe;
+  const int act = ACT >= 0 ? ACT : Lp->act;
+  const bool next_ce = Lup && (Lup->flags & DPC_LAYER_SOFTMAX_CE);
+  const bool do_err = (P.flags & DPC_FWD_ERR_NEXT) && Lup && !next_ce;
+  const bool do_fe = (P.flags & DPC_FWD_FE) && Lup && !(next_ce && (P.flags & DPC_FWD_ERR_NEXT));
+  const bool do_copy = (P.flags & DPC_FWD_COPY_NEXT) && Lup;
+  const bool store = !(P.flags & DPC_FWD_TRANSIENT);
+  const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
+  float* up_z = Lup ? Lup->z : nullptr;
+  float* up_e = Lup ? Lup->e : nullptr;
+  // What the epilogue reads from the layer above: its belief (fresh error) or its stored
+  // error (feedback error from the error already in memory).
+  const float* up_src = (do_err && !do_copy) ? up_z : ((do_fe && !do_err) ? up_e : nullptr);
+  const size_t row = (size_t)m * P.N + n0;
+  constexpr int CW = 16; // columns per step
+  float up[CW], upn[CW];
+  if (up_src)
+  {
+#pragma unroll
+    for (int k = 0; k < CW; k += 8)
+      ld8(up_src + row + grp * CW + k, &up[k]);
+  }
+#pragma unroll 1
+  for (int c = grp; c < BN / CW; c += GROUPS)
+  {
+    const size_t o = row + c * CW;
+    float v[CW];
+    tc_ld16(taddr + c * CW, v);
+    if (PREFETCH && up_src && c + GROUPS < BN / CW)
+    {
+#pragma unroll
+      for (int k = 0; k < CW; k += 8)
+        ld8(up_src + o + GROUPS * CW + k, &upn[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < CW; k += 8)
+    {
+      float bb[8], pre[8], mu[8], d[8], e[8];
+      ld8(L.b + n0 + c * CW + k, bb);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+      {
+        pre[q] = L.a * v[k + q] + bb[q];
+        if (do_fe)
+          act_both(act, pre[q], mu[q], d[q]);
+        else
+          mu[q] = act_fwd(act, pre[q]), d[q] = 1.0f;
+      }
+      if (residual)
+      {
+        float zz[8];
+        ld8(L.z + o + k, zz);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          mu[q] += zz[q];
+      }
+      if (store)
+      {
+        st8(L.preact + o + k, pre);
+        st8(L.mu + o + k, mu);
+      }
+      if (do_copy)
+        st8(up_z + o + k, mu);
+      if (do_err)
+      {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+        {
+          e[q] = do_copy ? 0.0f : up[k + q] - mu[q];
+          esum += e[q] * e[q];
+        }
+        st8(up_e + o + k, e);
+      }
+      else if (do_fe)
+      {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          e[q] = up[k + q];
+      }
+      if (do_fe)
+      {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          e[q] *= d[q];
+        st8(L.fe + o + k, e);
+      }
+    }
+    if (up_src && c + GROUPS < BN / CW)
+    {
+      if (PREFETCH)
+      {
+#pragma unroll
+        for (int k = 0; k < CW; ++k)
+          up[k] = upn[k];
+      }
+      else
+      {
+#pragma unroll
+        for (int k = 0; k < CW; k += 8)
+          ld8(up_src + o + GROUPS * CW + k, &up[k]);
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------ kernel
@@ -244,6 +412,9 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_per_layer = P.tiles_m * P.tiles_n;
   const int total_tiles = P.count * tiles_per_layer;
+  const int t_begin = P.chain ? 0 : (int)blockIdx.x;
+  const int t_end = P.chain ? P.count : total_tiles;
+  const int t_step = P.chain ? 1 : (int)gridDim.x;
   const int kblocks = P.K / TBK;
 
   if (threadIdx.x == 0)
@@ -283,9 +454,10 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
     {
       int it = 0;
       bool alive = true;
-      for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x)
+      for (int t = t_begin; t < t_end && alive; t += t_step)
       {
-        const int lrel = t / tiles_per_layer, rem = t % tiles_per_layer;
+        const int lrel = P.chain ? t : t / tiles_per_layer;
+        const int rem = P.chain ? (int)blockIdx.x : t % tiles_per_layer;
         const int m0 = (rem / P.tiles_n) * TBM, n0 = (rem % P.tiles_n) * BN;
         const int lcoord = P.first + lrel - P.run_first;
         for (int kb = 0; kb < kblocks; ++kb, ++it)
@@ -300,16 +472,27 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
           uint8_t* b_dst = a_dst + C::A_BYTES;
           mbar_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
           const int k0 = kb * TBK;
-          if (!C::A_MN)
-            tma_load_3d(a_dst, &mapA, &full[s], k0, m0, lcoord);
-          else
-            for (int i = 0; i < TBM / 32; ++i)
-              tma_load_3d(a_dst + i * (TBK * 128), &mapA, &full[s], m0 + 32 * i, k0, lcoord);
           if (!C::B_MN)
             tma_load_3d(b_dst, &mapB, &full[s], k0, n0, lcoord);
           else
             for (int i = 0; i < BN / 32; ++i)
               tma_load_3d(b_dst + i * (TBK * 128), &mapB, &full[s], n0 + 32 * i, k0, lcoord);
+          if (P.chain && kb == 0 && t > 0)
+          {
+            // The rows of this layer's input are the previous layer's output: wait until every
+            // tile of that row block has been published (the weights above are already on
+            // their way).
+            if (!chain_wait(&P.chain_counters[(t - 1) * P.tiles_m + m0 / TBM], P.chain_target,
+                            abort_flag))
+              alive = false; // the A copy below still runs so the stage's byte count completes
+          }
+          if (!C::A_MN)
+            tma_load_3d(a_dst, &mapA, &full[s], k0, m0, lcoord);
+          else
+            for (int i = 0; i < TBM / 32; ++i)
+              tma_load_3d(a_dst + i * (TBK * 128), &mapA, &full[s], m0 + 32 * i, k0, lcoord);
+          if (!alive)
+            break;
         }
       }
       if (!alive)
@@ -338,7 +521,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
       // 32 columns TBK*128 bytes apart.  K-major tiles: 8 rows per atom (1024 B between groups).
       const uint32_t a_sbo = C::A_MN ? 512 : 1024, b_sbo = C::B_MN ? 512 : 1024;
       const uint32_t a_lay = C::A_MN ? 1 : 2, b_lay = C::B_MN ? 1 : 2;
-      for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++tile_iter)
+      for (int t = t_begin; t < t_end && alive; t += t_step, ++tile_iter)
       {
         const int acc = tile_iter & 1;
         if (!mbar_wait(&tempty[acc], ((tile_iter >> 1) & 1) ^ 1, abort_flag))
@@ -394,13 +577,13 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
     constexpr int GROUPS = C::EPI_WARPS / 4;
     float esum = 0.0f;
     int tile_iter = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter)
+    for (int t = t_begin; t < t_end; t += t_step, ++tile_iter)
     {
-      const int lrel = t / tiles_per_layer, rem = t % tiles_per_layer;
+      const int lrel = P.chain ? t : t / tiles_per_layer;
+        const int rem = P.chain ? (int)blockIdx.x : t % tiles_per_layer;
       const int m = (rem / P.tiles_n) * TBM + quarter * 32 + lane;
       const int n0 = (rem % P.tiles_n) * BN;
       const int li = P.first + lrel;
-      const dpc_layer L = P.layers[li];
       const dpc_layer* Lup = (li + 1 < P.n_layers) ? &P.layers[li + 1] : nullptr;
       const int acc = tile_iter & 1;
       if (!mbar_wait(&tfull[acc], (tile_iter >> 1) & 1, abort_flag))
@@ -410,83 +593,23 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
 
       if (OP == TC_FWD)
       {
-        const bool next_ce = Lup && (Lup->flags & DPC_LAYER_SOFTMAX_CE);
-        const bool do_err = (P.flags & DPC_FWD_ERR_NEXT) && Lup && !next_ce;
-        const bool do_fe = (P.flags & DPC_FWD_FE) && Lup && !(next_ce && (P.flags & DPC_FWD_ERR_NEXT));
-        const bool do_copy = (P.flags & DPC_FWD_COPY_NEXT) && Lup;
-        const bool store = !(P.flags & DPC_FWD_TRANSIENT);
-        const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
-        // What the epilogue reads from the layer above: its belief (fresh error) or its
-        // stored error (feedback error from the error already in memory).
-        const float* up_src = (do_err && !do_copy) ? Lup->z : ((do_fe && !do_err) ? Lup->e : nullptr);
-        for (int c = grp; c < BN / 32; c += GROUPS)
+        constexpr bool PF = !THREE_X;
+        const dpc_layer* Lp = &P.layers[li];
+        switch (Lp->act)
         {
-          const size_t o = (size_t)m * P.N + n0 + c * 32;
-          float up[32], v[32];
-          if (up_src)
-          {
-#pragma unroll
-            for (int k = 0; k < 32; k += 8)
-              ld8(up_src + o + k, &up[k]);
-          }
-          tc_ld32(taddr + c * 32, v);
-#pragma unroll
-          for (int k = 0; k < 32; k += 8)
-          {
-            float bb[8], pre[8], mu[8], d[8], e[8];
-            ld8(L.b + n0 + c * 32 + k, bb);
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-            {
-              pre[q] = L.a * v[k + q] + bb[q];
-              if (do_fe)
-                act_both(L.act, pre[q], mu[q], d[q]);
-              else
-                mu[q] = act_fwd(L.act, pre[q]), d[q] = 1.0f;
-            }
-            if (residual)
-            {
-              float zz[8];
-              ld8(L.z + o + k, zz);
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                mu[q] += zz[q];
-            }
-            if (store)
-            {
-              st8(L.preact + o + k, pre);
-              st8(L.mu + o + k, mu);
-            }
-            if (do_copy)
-              st8(Lup->z + o + k, mu);
-            if (do_err)
-            {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-              {
-                e[q] = do_copy ? 0.0f : up[k + q] - mu[q];
-                esum += e[q] * e[q];
-              }
-              st8(Lup->e + o + k, e);
-            }
-            else if (do_fe)
-            {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                e[q] = up[k + q];
-            }
-            if (do_fe)
-            {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                e[q] *= d[q];
-              st8(L.fe + o + k, e);
-            }
-          }
+        case DPC_ACT_TANH:
+          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF>(P, Lp, Lup, taddr, m, n0, grp, esum);
+          break;
+        case DPC_ACT_GELU:
+          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF>(P, Lp, Lup, taddr, m, n0, grp, esum);
+          break;
+        default:
+          fwd_epilogue_tile<-1, BN, GROUPS, false>(P, Lp, Lup, taddr, m, n0, grp, esum);
         }
       }
       else if (OP == TC_FB)
       {
+        const dpc_layer L = P.layers[li];
         const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
         for (int c = grp; c < BN / 32; c += GROUPS)
         {
@@ -538,6 +661,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
       }
       else
       {
+        const dpc_layer L = P.layers[li];
         const float Bf = (float)P.batch;
         float alpha, decay = 1.0f;
         if (P.mode == WG_DFA_MODE)
@@ -570,6 +694,16 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
           }
         }
       }
+      if (P.chain)
+      {
+        // Publish this warp's rows of the next layer's input: make the stores visible device
+        // wide (and to the TMA engine's proxy), then count the warp in.
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __syncwarp();
+        if (lane == 0)
+          atomicAdd(&P.chain_counters[lrel * P.tiles_m + rem / P.tiles_n], 1);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0)
@@ -593,7 +727,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
     const int tid = threadIdx.x - (2 + C::EPI_WARPS) * 32;
     int it = 0;
     bool alive = true;
-    for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x)
+    for (int t = t_begin; t < t_end && alive; t += t_step)
     {
       for (int kb = 0; kb < kblocks; ++kb, ++it)
       {
@@ -696,7 +830,7 @@ int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b,
     configured = true;
   }
   const int total = P.count * P.tiles_m * P.tiles_n;
-  const int grid = std::min(total, p->ctx->sm_count);
+  const int grid = P.chain ? P.tiles_m * P.tiles_n : std::min(total, p->ctx->sm_count);
   kern<<<grid, C::THREADS, C::SMEM_BYTES, p->ctx->stream>>>(a, b, P);
   p->ctx->launches += 1;
   cudaError_t e = cudaPeekAtLastError();
@@ -777,6 +911,7 @@ int tc_plan_init(dpc_plan* plan)
   bool ok = true;
   ok &= make_map(&st->z_km, L0.z, H, B, best_count, plan->run.z_stride, TBM, false);
   ok &= make_map(&st->fe_km, L0.fe, H, B, best_count, plan->run.out_stride, TBM, false);
+  ok &= make_map(&st->w_km64, L0.W, H, H, best_count, plan->run.w_stride, 64, false);
   ok &= make_map(&st->w_km128, L0.W, H, H, best_count, plan->run.w_stride, 128, false);
   ok &= make_map(&st->w_km256, L0.W, H, H, best_count, plan->run.w_stride, 256, false);
   ok &= make_map(&st->z_mn, L0.z, H, B, best_count, plan->run.z_stride, 32, true);
@@ -784,7 +919,8 @@ int tc_plan_init(dpc_plan* plan)
   ok &= make_map(&st->w_mn, L0.W, H, H, best_count, plan->run.w_stride, 32, true);
   if (!ok)
     return DPC_OK; // the driver refused a tensor map: stay on the CUDA-core path
-  if (cudaMalloc(&st->error_flag, sizeof(int)) != cudaSuccess ||
+  if (cudaMalloc(&st->chain_counters, sizeof(int) * (size_t)best_count * (B / TBM)) != cudaSuccess ||
+      cudaMalloc(&st->error_flag, sizeof(int)) != cudaSuccess ||
       cudaMemset(st->error_flag, 0, sizeof(int)) != cudaSuccess ||
       cudaMallocHost(&st->error_host, sizeof(int)) != cudaSuccess)
     return DPC_OK;
@@ -803,6 +939,8 @@ void tc_plan_free(dpc_plan* plan)
     return;
   if (st->error_flag)
     cudaFree(st->error_flag);
+  if (st->chain_counters)
+    cudaFree(st->chain_counters);
   if (st->error_host)
     cudaFreeHost(st->error_host);
   delete st;
@@ -844,6 +982,9 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
   P.mode = mode;
   P.energy = p->energy;
   P.error_flag = st->error_flag;
+  P.chain = 0;
+  P.chain_counters = nullptr;
+  P.chain_target = 0;
   return P;
 }
 
@@ -858,6 +999,33 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
                                       base_params(p, st, first, count, B, H, H, 256, flags, 0));
   return launch<TC_FWD, 128, true>(p, st, st->z_km, st->w_km128,
                                    base_params(p, st, first, count, B, H, H, 128, flags, 0));
+}
+
+// The sequential forward sweep over layers [first, first+count) of the run as ONE persistent
+// launch: 128 x 64 output tiles, one CTA per tile, every CTA walking all layers and
+// synchronising per row block through counters in global memory (no grid-wide barrier: a
+// row block of layer l+1 only needs the same row block of layer l).  All CTAs must be
+// resident at once, so the tile grid may not exceed the SM count.
+int tc_project_forward(dpc_plan* p, int first, int count, int flags)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (!st || !st->ok || !range_in_run(p, first, count) || count < 2)
+    return 1;
+  const int H = p->run.width, B = p->batch;
+  const int tiles = (B / TBM) * (H / 64);
+  if (tiles > p->ctx->sm_count)
+    return 1;
+  TcParams P = base_params(p, st, first, count, B, H, H, 64, flags, 0);
+  P.chain = 1;
+  P.chain_counters = st->chain_counters;
+  P.chain_target = (H / 64) * 8; // column tiles x epilogue warps
+  cudaError_t e = cudaMemsetAsync(st->chain_counters, 0, sizeof(int) * (size_t)count * (B / TBM),
+                                  p->ctx->stream);
+  if (e != cudaSuccess)
+    return cuda_fail(e, "cudaMemsetAsync(chain counters)");
+  if (p->ctx->precision == DPC_PRECISION_TF32)
+    return launch<TC_FWD, 64, false>(p, st, st->z_km, st->w_km64, P);
+  return launch<TC_FWD, 64, true>(p, st, st->z_km, st->w_km64, P);
 }
 
 int tc_update_state(dpc_plan* p, int first, int count)
