@@ -43,6 +43,7 @@ SIGNATURES = {
     "dpc_plan_create": (_i, [_vp, _vp, _i, _i, ctypes.POINTER(_vp)]),
     "dpc_plan_update": (_i, [_vp, _vp, _i]),
     "dpc_plan_destroy": (_i, [_vp]),
+    "dpc_plan_set_terminal_error": (_i, [_vp, _vp]),
     "dpc_plan_tensor_run": (_i, [_vp, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "dpc_forward": (_i, [_vp, _i, _i, _i]),
     "dpc_project_forward": (_i, [_vp, _i, _i, _i]),
@@ -69,6 +70,7 @@ SIGNATURES = {
     "dpcn_train_step_device": (_i, [_vp, _vp, _i64, _vp, _i64, _i, c_f32p]),
     "dpcn_train_step_mode": (_i, [_vp, _i, c_f32p, _i64, c_f32p, _i64, _i, c_f32p]),
     "dpcn_predict": (_i, [_vp, c_f32p, _i64, _i, _i, c_f32p, _i64]),
+    "dpcn_reset_state": (_i, [_vp]),
     "dpcn_context": (_vp, [_vp]),
     "dpcn_plan": (_vp, [_vp]),
     "dpcn_launch_count": (_i64, [_vp]),

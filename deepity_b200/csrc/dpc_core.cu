@@ -343,7 +343,7 @@ static int validate_layers(const dpc_layer* layers, int n, int batch)
                                          std::to_string(i));
     }
     else if (L.next_size != 0)
-      return fail(DPC_ERR_INVALID, "plan: the last layer must be the weight-less terminal layer");
+      return fail(DPC_ERR_INVALID, "plan: the last layer must be weight-less (next_size 0)");
   }
   return DPC_OK;
 }
@@ -361,6 +361,7 @@ int dpc_plan_create(dpc_ctx* ctx, const dpc_layer* layers, int n_layers, int bat
   p->n = n_layers;
   p->batch = batch;
   p->h.assign(layers, layers + n_layers);
+  p->e_terminal = layers[n_layers - 1].e;
   cudaError_t err = cudaMalloc(&p->d, sizeof(dpc_layer) * n_layers);
   if (err == cudaSuccess)
     err = cudaMalloc(&p->energy, sizeof(double));
@@ -393,6 +394,8 @@ int dpc_plan_update(dpc_plan* p, const dpc_layer* layers, int n_layers)
   if (rc != DPC_OK)
     return rc;
   DPC_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  if (p->e_terminal == p->h[p->n - 1].e)
+    p->e_terminal = layers[n_layers - 1].e;
   p->h.assign(layers, layers + n_layers);
   DPC_CUDA(cudaMemcpy(p->d, layers, sizeof(dpc_layer) * n_layers, cudaMemcpyHostToDevice));
   tc_plan_free(p);
@@ -412,6 +415,14 @@ int dpc_plan_destroy(dpc_plan* p)
   if (p->energy_host)
     cudaFreeHost(p->energy_host);
   delete p;
+  return DPC_OK;
+}
+
+int dpc_plan_set_terminal_error(dpc_plan* p, const float* e_terminal_dev)
+{
+  if (!p)
+    return fail(DPC_ERR_INVALID, "null plan");
+  p->e_terminal = e_terminal_dev ? e_terminal_dev : p->h[p->n - 1].e;
   return DPC_OK;
 }
 
@@ -666,7 +677,7 @@ int dpc_direct_feedback(dpc_plan* p, int first, int count, int decay_w)
     for (int i = f; i < f + c; ++i)
       mx = std::max(mx, (size_t)p->batch * std::max(p->h[i].next_size, 0));
     dim3 grid(elem_blocks(p, mx), c);
-    dfa_proj_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch);
+    dfa_proj_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal);
     if ((rc = check_launch(p->ctx, "dfa_proj kernel")) != DPC_OK)
       return rc;
   }
@@ -728,7 +739,7 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
     if (any_psi)
     {
       dim3 gp(std::max(1, cdiv(max_size, 128)), c);
-      psi_update_kernel<<<gp, 128, 0, st>>>(p->d, f, p->n, p->batch);
+      psi_update_kernel<<<gp, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal);
       if ((rc = check_launch(p->ctx, "psi_update kernel")) != DPC_OK)
         return rc;
     }

@@ -56,6 +56,7 @@ struct dpc_plan
   dpc_layer* d = nullptr;   // device copy
   double* energy = nullptr; // device accumulator
   double* energy_host = nullptr; // pinned
+  const float* e_terminal = nullptr; // terminal error the DFA / Psi kernels read
   dpc::TensorRun run;
   void* tc = nullptr; // tensor-core path state (tensor maps), owned by dpc_tc.cu
 };

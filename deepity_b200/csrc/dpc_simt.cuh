@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(NTHREADS)
   if (OP == OP_WG && mode == WG_DFA)
   {
     // DirectFeedbackUpdate is a no-op unless the layer above owns feedback weights.
-    if (li + 1 >= n_layers || layers[li + 1].Psi == nullptr || layers[li + 1].next_size <= 0)
+    if (li + 1 >= n_layers || layers[li + 1].Psi == nullptr)
       return;
   }
 
@@ -538,16 +538,15 @@ __global__ void relax_kernel(const dpc_layer* __restrict__ layers, int first, in
 
 // DFA projection: fe[l] = (e_T · Psi[l+1]^T) * f'(preact[l])   (K = terminal_size).
 __global__ void dfa_proj_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
-                                int batch)
+                                int batch, const float* __restrict__ eT)
 {
   const int li = first + blockIdx.y;
   if (li + 1 >= n_layers)
     return;
   const dpc_layer L = layers[li];
   const dpc_layer Lup = layers[li + 1];
-  if (L.next_size <= 0 || Lup.Psi == nullptr || Lup.next_size <= 0)
+  if (L.next_size <= 0 || Lup.Psi == nullptr)
     return;
-  const float* eT = layers[n_layers - 1].e;
   const int TS = L.terminal_size, n = L.next_size;
   const size_t total = (size_t)batch * n;
   for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
@@ -614,7 +613,7 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
 // Feedback-weight update Psi[l] (+)= (fl*a/B) z[l]^T e_T, one thread per row of Psi with the
 // terminal columns in registers (chunks of 16).
 __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
-                                  int batch)
+                                  int batch, const float* __restrict__ eT)
 {
   const int li = first + blockIdx.y;
   if (li + 1 >= n_layers)
@@ -622,7 +621,6 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
   const dpc_layer L = layers[li];
   if (L.next_size <= 0 || L.Psi == nullptr || (L.flags & DPC_LAYER_INPUT_ACT))
     return;
-  const float* eT = layers[n_layers - 1].e;
   const int TS = L.terminal_size, s = L.size;
   const bool full_kind = (L.flags & DPC_LAYER_FULLPC_PSI) != 0;
   const float rate = full_kind ? L.fl * L.a : L.fl;

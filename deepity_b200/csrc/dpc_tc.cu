@@ -1051,7 +1051,7 @@ int tc_weight_gemm(dpc_plan* p, int first, int count, int mode)
     const dpc_layer& L = p->h[i];
     if (mode == WG_LEARN_MODE && L.opt != DPC_OPT_SGD)
       return 1;
-    if (mode == WG_DFA_MODE && (i + 1 >= p->n || !p->h[i + 1].Psi || p->h[i + 1].next_size <= 0))
+    if (mode == WG_DFA_MODE && (i + 1 >= p->n || !p->h[i + 1].Psi))
       return 1;
   }
   const int H = p->run.width, B = p->batch;

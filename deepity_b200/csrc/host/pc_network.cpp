@@ -104,7 +104,7 @@ void PCNetwork::Compile()
     throw std::invalid_argument("deepity_b200: the last layer must have nextSize == 0");
   const int n = (int)layers.size();
   // Same check as DirectKPPCNetwork::Compile() (src/networks/DirectKPPCNetwork.cpp:677-684).
-  if (kind != NetworkKind::SIMPLE &&
+  if (kind != NetworkKind::SIMPLE && !ghostTop &&
       layers.back()->d.size != layers.back()->d.terminal_size)
     throw std::invalid_argument(
         "Compile(): terminalSize (" + std::to_string(layers.back()->d.terminal_size) +
@@ -157,6 +157,9 @@ void PCNetwork::Compile()
     A_Z, A_E, A_W, A_B, A_PRE, A_MU, A_FE, A_PSI, A_ZF, A_V, A_COUNT
   };
   size_t total[A_COUNT] = {};
+  if (ghostTop)
+    total[A_PSI] += Pad64((size_t)layers.back()->d.size * layers.back()->d.terminal_size) +
+                    Pad64(B * layers.back()->d.terminal_size);
   for (auto& l : layers)
   {
     const size_t s = l->d.size, nx = l->d.next_size, ts = l->d.terminal_size;
@@ -219,6 +222,12 @@ void PCNetwork::Compile()
       }
     }
   }
+  if (ghostTop)
+  {
+    PCLayer* g = layers.back().get();
+    g->d.Psi = take(A_PSI, (size_t)g->d.size * g->d.terminal_size);
+    ghostET = take(A_PSI, B * g->d.terminal_size);
+  }
   size_t inN = B * layers.front()->d.size, outN = B * layers.back()->d.size;
   void* p = nullptr;
   Check(dpc_alloc_host(ctx, inN * sizeof(float), &p));
@@ -233,6 +242,8 @@ void PCNetwork::Compile()
   for (auto& l : layers)
     table.push_back(l->d);
   Check(dpc_plan_create(ctx, table.data(), n, batchSize, &plan));
+  if (ghostTop)
+    Check(dpc_plan_set_terminal_error(plan, ghostET));
   Check(dpc_sync(ctx));
   dirty = false;
 }
@@ -903,6 +914,12 @@ void PCNetwork::SetPrecision(int precision)
   Check(dpc_set_precision(ctx, precision));
   Dirty();
 }
+void PCNetwork::SetGhostTop(bool enabled)
+{
+  if (plan)
+    throw std::logic_error("deepity_b200: SetGhostTop() must precede Compile()");
+  ghostTop = enabled;
+}
 void PCNetwork::SetUseGraph(bool enabled)
 {
   useGraph = enabled;
@@ -975,6 +992,10 @@ bool PCNetwork::FindTensor(int layer, const std::string& name, float** ptr, size
     p = d.v, r = B, c = s;
   else if (name == "zF")
     p = d.zF, r = B, c = s;
+  else if (name == "Psi" && n == 0 && d.Psi)
+    p = d.Psi, r = s, c = ts, st = d.psi_stride;
+  else if (name == "eT" && ghostET && layer == (int)layers.size() - 1)
+    p = ghostET, r = B, c = ts;
   else if (n > 0)
   {
     if (name == "mu")
@@ -1128,6 +1149,8 @@ int dpcn_set_option(dpcn_net* net, const char* name, int iv, float fv)
           n.SetUseMomentum(iv != 0, fv);
         else if (nm == "precision")
           n.SetPrecision(iv);
+        else if (nm == "ghost_top")
+          n.SetGhostTop(iv != 0);
         else if (nm == "use_graph")
           n.SetUseGraph(iv != 0);
         else
@@ -1278,6 +1301,13 @@ int dpcn_predict(dpcn_net* net, const float* x, int64_t nx, int steps, int with_
   return Guard([&] {
     net->net->PredictRaw(x, (size_t)nx, steps, with_projection != 0, host_out, (size_t)nout);
   });
+}
+
+int dpcn_reset_state(dpcn_net* net)
+{
+  if (!net)
+    return DPC_ERR_INVALID;
+  return Guard([&] { net->net->ResetState(); });
 }
 
 dpc_ctx* dpcn_context(dpcn_net* net)

@@ -142,6 +142,10 @@ public:
   void SetUseMomentum(bool enabled, float beta = 0.9f);
   void SetPrecision(int precision);
   void SetUseGraph(bool enabled);
+  // Layer sharding: the last layer is a copy of the neighbour rank's first layer (it owns no
+  // weights here but carries that layer's Psi); the terminal error arrives by broadcast.
+  void SetGhostTop(bool enabled);
+  float* TerminalErrorBuffer() noexcept { return ghostET; }
 
   std::vector<std::unique_ptr<PCLayer>>& GetLayers() noexcept { return layers; }
   PCLayer* GetTerminalLayer() noexcept { return layers.back().get(); }
@@ -184,6 +188,8 @@ private:
   bool useIPC = false, useMomentum = false, useGraph = true, dirty = false;
   bool adamAllocated = false, psiAdamAllocated = false, pendingAsync = false;
   float momentumBeta = 0.9f, psiDecay = -1.0f;
+  bool ghostTop = false;
+  float* ghostET = nullptr;
   int transientFlag = 0; // DPC_FWD_TRANSIENT while a whole train step is being issued
   // key of the graph captured in slot s: mode*1e6+steps (train) or steps (predict); -1 none
   long graphKey[4] = {-1, -1, -1, -1};

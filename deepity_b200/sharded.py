@@ -1,0 +1,365 @@
+"""Layer-sharded DKPPCN across the GPUs of one node.
+
+Deep stacks are split into contiguous blocks of layers, one block per rank (one process per
+GPU).  Every phase of the train step except the forward sweep is local to a layer and its
+two neighbours, so a rank only ever exchanges ONE boundary tensor with the rank above or
+below it per phase, plus a broadcast of the small terminal error:
+
+    forward sweep   rank r sends the prediction of its top layer to r+1          [B, H]
+    terminal error  last rank broadcasts e_T (after the sweep and after the last
+                    settling pass, which is the one the Psi update reads)         [B, TS]
+    settling pass   a) every rank computes errors/predictions of its block, then
+                       sends the error of the boundary layer UP (the rank above
+                       owns that layer's belief and needs e to update it)        [B, H]
+                    b) every rank updates its beliefs, then sends the boundary
+                       belief DOWN (the rank below needs it for its next error)  [B, H]
+    learn           the rank above sends Psi of its first layer DOWN once per step
+                    (the direct-feedback update of the layer below reads it)     [H, TS]
+    energy          one all-reduce of a scalar
+
+The local block of a rank is an ordinary network of this library whose last layer is a
+"ghost": a copy of the first layer of the rank above (its belief z, error e and Psi), so the
+single-GPU kernels run unchanged on it.  The reference has no multi-GPU code at all; the
+arithmetic per layer is exactly that of the single-GPU path, so results are identical to it
+up to the order of the energy sum.
+
+The schedule is written against a small engine interface so that the same code is tested on
+CPU ranks (gloo) with an engine backed by the numpy oracle (tests/test_sharded_cpu.py).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Sequence, Tuple
+
+import numpy as np
+
+
+def partition_layers(n_weight_layers: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous [begin, end) ranges of weight layers per rank, sizes differing by at most 1;
+    the remainder goes to the lowest ranks.  Every rank gets at least one layer."""
+    if world < 1 or n_weight_layers < world:
+        raise ValueError(f"cannot split {n_weight_layers} weight layers over {world} ranks")
+    base, rem = divmod(n_weight_layers, world)
+    out, b = [], 0
+    for r in range(world):
+        e = b + base + (1 if r < rem else 0)
+        out.append((b, e))
+        b = e
+    return out
+
+
+class GpuEngine:
+    """The local block on one GPU, driven phase by phase through the dpc_* C ABI."""
+
+    def __init__(self, sizes: Sequence[int], batch: int, hyper: dict, act: str, ghost_top: bool,
+                 terminal_size: int, device: int, precision: str = "fp32"):
+        import torch
+        from . import _lib
+        from .layer import ACT_IDS
+        self.torch = torch
+        self.lib = _lib.load()
+        self.check = _lib.check
+        self.batch, self.sizes, self.ts = batch, list(sizes), terminal_size
+        self.n = len(self.sizes)  # local layers incl. ghost / terminal
+        self.h = ctypes.c_void_p()
+        self.check(self.lib.dpcn_create(1, batch, device, ctypes.byref(self.h)))
+        for i in range(self.n - 1):
+            self.check(self.lib.dpcn_add_layer(self.h, self.sizes[i], self.sizes[i + 1],
+                                               terminal_size, hyper["lr"], hyper["ir"],
+                                               hyper["fl"], hyper["lmbda"], ACT_IDS[act]))
+        self.check(self.lib.dpcn_add_layer(self.h, self.sizes[-1], 0, terminal_size, hyper["lr"],
+                                           hyper["ir"], hyper["fl"], hyper["lmbda"],
+                                           ACT_IDS["linear"]))
+        self.check(self.lib.dpcn_set_option(self.h, b"ghost_top", int(ghost_top), 0.0))
+        self.check(self.lib.dpcn_set_option(self.h, b"precision", {"fp32": 0, "tf32": 1}[precision],
+                                            0.0))
+        self.check(self.lib.dpcn_compile(self.h))
+        self.ctx = self.lib.dpcn_context(self.h)
+        self.plan = self.lib.dpcn_plan(self.h)
+        self.stream = torch.cuda.ExternalStream(self.lib.dpc_stream(self.ctx),
+                                                device=torch.device("cuda", device))
+        self.ghost_top = ghost_top
+        self._views = {}
+
+    # -- tensors as torch views over the library's device memory (zero copy) ---------------
+    def tensor(self, layer: int, name: str):
+        key = (layer, name)
+        if key not in self._views:
+            p = ctypes.c_void_p()
+            stride = ctypes.c_int64()
+            n = self.lib.dpcn_tensor_size(self.h, layer, name.encode())
+            self.check(self.lib.dpcn_tensor_ptr(self.h, layer, name.encode(), ctypes.byref(p),
+                                                ctypes.byref(stride)))
+
+            class _View:
+                __cuda_array_interface__ = {"shape": (int(n),), "typestr": "<f4",
+                                            "data": (int(p.value), False), "version": 3}
+            self._views[key] = self.torch.as_tensor(_View(), device=self.stream.device)
+        return self._views[key]
+
+    def set_param(self, layer: int, name: str, value) -> None:
+        v = np.ascontiguousarray(value, dtype=np.float32).ravel()
+        from . import _lib
+        self.check(self.lib.dpcn_set_tensor(self.h, layer, name.encode(),
+                                            v.ctypes.data_as(_lib.c_f32p), v.size))
+
+    def get(self, layer: int, name: str) -> np.ndarray:
+        self.sync()
+        return self.tensor(layer, name).cpu().numpy()
+
+    def terminal_error_tensor(self):
+        return self.tensor(self.n - 1, "eT" if self.ghost_top else "e")
+
+    # -- phases ---------------------------------------------------------------------------
+    def reset(self):
+        self.check(self.lib.dpcn_reset_state(self.h))
+
+    def project_forward(self, skip_last_copy: bool):
+        self.check(self.lib.dpc_project_forward(self.plan, 0, self.n - 1, int(skip_last_copy)))
+
+    def terminal_error(self):
+        self.check(self.lib.dpc_error(self.plan, self.n - 1, 0))
+
+    def dfa(self):
+        self.check(self.lib.dpc_direct_feedback(self.plan, 0, self.n - 1, 0))
+
+    def forward_state(self, first_cached: bool, flags: int):
+        """ComputeMuOnly + error of the layer above for every local weight layer."""
+        start = 0
+        if first_cached:
+            self.check(self.lib.dpc_forward(self.plan, 0, 1, (flags | 16) & ~256))  # CACHED
+            start = 1
+        if self.n - 1 - start > 0:
+            self.check(self.lib.dpc_forward(self.plan, start, self.n - 1 - start, flags))
+
+    def update_state(self, first: int, count: int):
+        if count > 0:
+            self.check(self.lib.dpc_update_state(self.plan, first, count))
+
+    def update_weights(self):
+        self.check(self.lib.dpc_update_weights(self.plan, 0, self.n - 1, 0))
+
+    def energy_reset(self):
+        self.check(self.lib.dpc_energy_reset(self.plan))
+
+    def energy_read(self) -> float:
+        e = ctypes.c_double()
+        self.check(self.lib.dpc_energy_read(self.plan, ctypes.byref(e)))
+        return e.value
+
+    def sync(self):
+        self.check(self.lib.dpc_sync(self.ctx))
+
+    def mark_clamped(self, layer: int):
+        """The kernels take clamping from the ranges the schedule passes; nothing to record."""
+
+    def comm_stream(self):
+        return self.torch.cuda.stream(self.stream)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.dpc_launch_count(self.ctx))
+
+
+FWD_COPY, FWD_ERR, FWD_ENERGY, FWD_FE, FWD_TRANSIENT = 1, 2, 4, 8, 256
+
+
+class ShardedDKPPCN:
+    """DKPPCN whose weight layers are split over the ranks of a torch.distributed group."""
+
+    def __init__(self, sizes: Sequence[int], batch: int, hyper: dict, act: str = "tanh",
+                 engine_factory=None, group=None, precision: str = "fp32"):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.sizes, self.batch = list(sizes), batch
+        self.ts = self.sizes[-1]
+        n_weight = len(self.sizes) - 1
+        self.ranges = partition_layers(n_weight, self.world)
+        self.begin, self.end = self.ranges[self.rank]
+        self.is_first, self.is_last = self.rank == 0, self.rank == self.world - 1
+        # local widths: own layers' inputs + the input width of the layer above (ghost), or the
+        # real terminal on the last rank
+        local = self.sizes[self.begin:self.end + 1]
+        if engine_factory is None:
+            device = int(os.environ.get("LOCAL_RANK", self.rank))
+            engine_factory = lambda **kw: GpuEngine(device=device, precision=precision, **kw)  # noqa: E731
+        self.eng = engine_factory(sizes=local, batch=batch, hyper=hyper, act=act,
+                                  ghost_top=not self.is_last, terminal_size=self.ts)
+        self.n = len(local)
+
+    # ---- parameter placement: global layer index -> local ---------------------------------
+    def owns(self, layer: int) -> bool:
+        return self.begin <= layer < self.end
+
+    def set_param(self, layer: int, name: str, value) -> None:
+        if self.owns(layer):
+            self.eng.set_param(layer - self.begin, name, value)
+
+    def get_local(self, layer: int, name: str):
+        return self.eng.get(layer - self.begin, name)
+
+    # ---- communication helpers -------------------------------------------------------------
+    def _exchange(self, send=None, recv=None):
+        """send/recv: (tensor, peer rank) or None; both are posted before either is waited on."""
+        ops = []
+        with self.eng.comm_stream():
+            if send is not None:
+                ops.append(self.dist.isend(send[0], send[1], group=self.group))
+            if recv is not None:
+                ops.append(self.dist.irecv(recv[0], recv[1], group=self.group))
+            for op in ops:
+                op.wait()
+
+    def _broadcast_terminal_error(self):
+        with self.eng.comm_stream():
+            self.dist.broadcast(self.eng.terminal_error_tensor(), self.world - 1, group=self.group)
+
+    # ---- one train step ---------------------------------------------------------------------
+    def train_step(self, x, y, steps: int, read_energy: bool = True):
+        eng, n = self.eng, self.n
+        up, down = self.rank + 1, self.rank - 1
+        eng.reset()
+        if self.is_first:
+            self._load(0, "z", x)
+            eng.mark_clamped(0)
+        if self.is_last:
+            self._load(n - 1, "z", y)
+            eng.mark_clamped(n - 1)
+        # Psi of the first layer of the rank above, for this step's direct-feedback update.
+        if self.world > 1:
+            self._exchange(send=None if self.is_first else (eng.tensor(0, "Psi"), down),
+                           recv=None if self.is_last else (eng.tensor(n - 1, "Psi"), up))
+        # forward sweep, rank after rank
+        if not self.is_first:
+            self._exchange(recv=(eng.tensor(0, "z"), down))
+        eng.project_forward(skip_last_copy=self.is_last)
+        if not self.is_last:
+            self._exchange(send=(eng.tensor(n - 1, "z"), up))
+        if self.is_last:
+            eng.terminal_error()
+        if self.world > 1:
+            self._broadcast_terminal_error()
+        eng.dfa()
+        first_unclamped = 1 if self.is_first else 0
+        for t in range(steps):
+            eng.forward_state(self.is_first, FWD_ERR | FWD_FE | FWD_TRANSIENT)
+            if self.world > 1:
+                self._exchange(send=None if self.is_last else (eng.tensor(n - 1, "e"), up),
+                               recv=None if self.is_first else (eng.tensor(0, "e"), down))
+                if t == steps - 1:
+                    self._broadcast_terminal_error()
+            eng.update_state(first_unclamped, n - 1 - first_unclamped)
+            if self.world > 1:
+                self._exchange(send=None if self.is_first else (eng.tensor(0, "z"), down),
+                               recv=None if self.is_last else (eng.tensor(n - 1, "z"), up))
+        eng.forward_state(self.is_first, FWD_FE | FWD_TRANSIENT)
+        eng.update_weights()
+        eng.energy_reset()
+        eng.forward_state(self.is_first, FWD_ERR | FWD_ENERGY | FWD_FE)
+        if self.world > 1:
+            # leave the boundary error where a reader of the rank above expects it
+            self._exchange(send=None if self.is_last else (eng.tensor(n - 1, "e"), up),
+                           recv=None if self.is_first else (eng.tensor(0, "e"), down))
+        if not read_energy:
+            return None
+        energy = eng.energy_read()
+        if self.world > 1:
+            import torch
+            t = torch.tensor([energy], dtype=torch.float64)
+            if self.dist.get_backend(self.group) == "nccl":
+                t = t.cuda()
+            self.dist.all_reduce(t, group=self.group)
+            energy = float(t.item())
+        return energy
+
+    def _load(self, layer: int, name: str, value):
+        import torch
+        t = self.eng.tensor(layer, name)
+        src = value if isinstance(value, torch.Tensor) else torch.from_numpy(
+            np.ascontiguousarray(value, dtype=np.float32))
+        with self.eng.comm_stream():
+            t.copy_(src.reshape(-1).to(t.device, non_blocking=True))
+
+    def train_step_flops(self, steps: int) -> float:
+        from bench import algorithmic_flops  # the same formula the benchmark reports
+        return algorithmic_flops("dkp", self.sizes, self.batch, steps)
+
+
+# ------------------------------------------------------------------------------------------
+def bench_main(args, w, sizes, config):
+    """The N>1 arm of bench.py: layer-sharded C3, strong scaling (the same network and batch
+    at every N), timed on the device with CUDA events, max over ranks."""
+    import json
+    import time
+
+    import torch
+    import torch.distributed as dist
+
+    from bench import HYPER, ClockSampler, synth
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    net = ShardedDKPPCN(sizes, w["batch"], HYPER, act=w["act"], precision=args.precision)
+    x, y, params = synth(w, sizes)
+    for l, p in enumerate(params):
+        for nm, v in p.items():
+            net.set_param(l, nm, v)
+    xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+    xh, yh = torch.from_numpy(x).pin_memory(), torch.from_numpy(y).pin_memory()
+    T, B = w["T"], w["batch"]
+    for _ in range(args.warmup):
+        energy = net.train_step(xd, yd, T)
+
+    def timed(fn, steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(net.eng.stream)
+        for _ in range(steps):
+            fn()
+        b.record(net.eng.stream)
+        b.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b) / steps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    with ClockSampler(local) as clk:
+        n0 = net.eng.launch_count
+        ms = timed(lambda: net.train_step(xd, yd, T, read_energy=False), args.steps)
+        launches = net.eng.launch_count - n0
+        energy = net.train_step(xd, yd, T)
+        e2e_ms = timed(lambda: net.train_step(xh, yh, T), args.steps)
+    lc = torch.tensor([launches], device="cuda", dtype=torch.int64)
+    dist.all_reduce(lc)
+    if rank == 0:
+        flops = net.train_step_flops(T)
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(os.path.dirname(os.path.dirname(
+                os.path.abspath(__file__))), "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = (peaks.get("bf16_tflops_sustained") or 1590.0) * world
+        config = dict(config, parallelism=f"layer-sharded x{world}",
+                      layers_per_rank=[e - b for b, e in net.ranges])
+        line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
+                "config": config, "energy": energy, "algorithmic_flops_per_step": flops,
+                "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
+                "frac_of_gemm_peak_step": flops / (ms * 1e-3) / 1e12 / peak,
+                "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8},
+                "gpu_launches": int(lc.item()), "clocks": clk.summary(),
+                "roofline": None, "cpu_baseline": None}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()

@@ -167,6 +167,11 @@ DPC_API int dpc_plan_create(dpc_ctx* ctx, const dpc_layer* layers, int n_layers,
 /* Re-upload after a hyper-parameter / optimizer / pointer change (same layer count). */
 DPC_API int dpc_plan_update(dpc_plan* plan, const dpc_layer* layers, int n_layers);
 DPC_API int dpc_plan_destroy(dpc_plan* plan);
+/* Terminal error used by dpc_direct_feedback and the Psi update.  NULL (default): the e
+ * buffer of the plan's last layer.  A layer-sharded network whose last local layer is only a
+ * copy of the neighbour rank's first layer points this at the buffer that receives the
+ * broadcast terminal error [batch, terminal_size]. */
+DPC_API int dpc_plan_set_terminal_error(dpc_plan* plan, const float* e_terminal_dev);
 /* Layers [first, first+count) that the tensor-core path covers (0 if none). */
 DPC_API int dpc_plan_tensor_run(dpc_plan* plan, int* first, int* count);
 
@@ -238,7 +243,8 @@ DPC_API int dpcn_add_layer(dpcn_net* net, int size, int next_size, int terminal_
 /* Options by name, before or after compile as the reference allows: "optimizer",
  * "psi_optimizer" (ivalue = dpc_opt), "center_weights", "psi_decay" (fvalue),
  * "learning_rate", "feedback_rate", "inference_rate" (fvalue), "cross_entropy", "mupc",
- * "residual", "ipc", "momentum" (ivalue on/off, fvalue beta), "precision" (dpc_precision),
+ * "residual", "ipc", "momentum" (ivalue on/off, fvalue beta), "precision" (dpc_precision), "ghost_top" (before
+ * compile: the last layer is a copy of a neighbour rank's layer, see deepity_b200/sharded.py),
  * "use_graph" (capture the step into a CUDA graph, default on). */
 DPC_API int dpcn_set_option(dpcn_net* net, const char* name, int ivalue, float fvalue);
 DPC_API int dpcn_compile(dpcn_net* net);
@@ -274,6 +280,8 @@ DPC_API int dpcn_train_step_mode(dpcn_net* net, int mode, const float* x, int64_
 /* Predict(x, T) -> terminal beliefs [B, terminal] into host_out. */
 DPC_API int dpcn_predict(dpcn_net* net, const float* x, int64_t nx, int steps,
                          int with_projection, float* host_out, int64_t nout);
+/* ResetState(): zero every belief (FullPC: also errors and momentum). Stream-ordered. */
+DPC_API int dpcn_reset_state(dpcn_net* net);
 /* The network's context and plan, for callers that drive single phases themselves
  * (layer-sharded multi-GPU stepping, per-kernel timing).  Valid after dpcn_compile;
  * owned by the network. */

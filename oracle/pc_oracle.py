@@ -128,16 +128,19 @@ class PCOracle:
     def __init__(self, kind, sizes, batch, *, lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.0, act="tanh",
                  last_act=None, optimizer="SGD", psi_optimizer="SGD", psi_decay=-1.0,
                  center_weights=False, cross_entropy=False, mupc=False, residual=False,
-                 ipc=False, epc=False, momentum=None):
+                 ipc=False, epc=False, momentum=None, terminal_size=None):
         self.kind, self.B, self.sizes = kind, batch, list(sizes)
-        ts = self.sizes[-1]
+        # terminal_size differs from sizes[-1] only for one block of a layer-sharded network,
+        # whose last layer is a copy of the next block's first layer (tests/test_sharded_cpu.py).
+        ts = self.sizes[-1] if terminal_size is None else terminal_size
+        self.e_terminal = None  # override of the terminal error for such a block
         nw = len(self.sizes) - 1
         self.layers = []
         for i in range(nw):
             a = act if (i + 1 < nw or last_act is None) else last_act
             self.layers.append(_Layer(self.sizes[i], self.sizes[i + 1], ts, batch, lr, ir, fl,
                                       lmbda, a))
-        self.layers.append(_Layer(ts, 0, ts, batch, lr, ir, fl, lmbda, "linear"))
+        self.layers.append(_Layer(self.sizes[-1], 0, ts, batch, lr, ir, fl, lmbda, "linear"))
         self.opt, self.opt_psi = optimizer, psi_optimizer
         self.psi_decay, self.center = F(psi_decay), center_weights
         self.ipc, self.epc = ipc, epc
@@ -245,7 +248,8 @@ class PCOracle:
         L = self.layers[i]
         if i + 1 >= len(self.layers) or L.n == 0:
             return
-        above, term = self.layers[i + 1], self.layers[-1]
+        above = self.layers[i + 1]
+        term_e = self.layers[-1].e if self.e_terminal is None else self.e_terminal
         B = F(self.B)
         if self.kind == "simple":
             g, zin, a = above.e, L.zF, F(1)
@@ -269,10 +273,10 @@ class PCOracle:
         if self.opt_psi == "SGD":
             if self.kind == "dkp" and self.psi_decay > 0:
                 L.Psi *= F(1) - self.psi_decay
-            L.Psi += F(flr / B) * (L.z.T @ term.e)
+            L.Psi += F(flr / B) * (L.z.T @ term_e)
         else:
             L.tP += 1
-            gP = F(-1) * (L.z.T @ term.e)
+            gP = F(-1) * (L.z.T @ term_e)
             wd = None
             if self.opt_psi == "ADAMW":
                 dec = self.psi_decay if (self.kind == "dkp" and self.psi_decay >= 0) else L.lmbda
@@ -282,10 +286,11 @@ class PCOracle:
     def dfa(self, i):
         """DirectKPPCLayer.cpp:503-549, FullPCLayer.cpp:514-572."""
         L = self.layers[i]
-        if i + 1 >= len(self.layers) or self.layers[i + 1].n == 0:
+        if i + 1 >= len(self.layers) or getattr(self.layers[i + 1], "Psi", None) is None:
             return
-        above, term = self.layers[i + 1], self.layers[-1]
-        proj = (term.e @ above.Psi.T) * dact(L.act, L.preact)
+        above = self.layers[i + 1]
+        term_e = self.layers[-1].e if self.e_terminal is None else self.e_terminal
+        proj = (term_e @ above.Psi.T) * dact(L.act, L.preact)
         if self.kind == "full" and L.lmbda > 0 and L.fl != 0:
             L.W *= F(1) - L.lmbda
         L.W += F(L.fl * L.a / F(self.B)) * (proj.T @ L.z)
