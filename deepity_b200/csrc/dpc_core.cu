@@ -673,11 +673,11 @@ int dpc_direct_feedback(dpc_plan* p, int first, int count, int decay_w)
   for (int f = first; f < first + count; f += kMaxZ)
   {
     const int c = std::min(kMaxZ, first + count - f);
-    size_t mx = 0;
+    int mxn = 1;
     for (int i = f; i < f + c; ++i)
-      mx = std::max(mx, (size_t)p->batch * std::max(p->h[i].next_size, 0));
-    dim3 grid(elem_blocks(p, mx), c);
-    dfa_proj_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal);
+      mxn = std::max(mxn, p->h[i].next_size);
+    dim3 grid(cdiv(mxn, 128), cdiv(p->batch, DFA_ROWS), c);
+    dfa_proj_kernel<<<grid, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal);
     if ((rc = check_launch(p->ctx, "dfa_proj kernel")) != DPC_OK)
       return rc;
   }

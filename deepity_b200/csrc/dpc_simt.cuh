@@ -537,10 +537,13 @@ __global__ void relax_kernel(const dpc_layer* __restrict__ layers, int first, in
 }
 
 // DFA projection: fe[l] = (e_T · Psi[l+1]^T) * f'(preact[l])   (K = terminal_size).
+// One thread per output unit j with its Psi row in registers; a block covers DFA_ROWS batch
+// rows whose terminal errors sit in shared memory, so preact/fe stream through coalesced.
+constexpr int DFA_ROWS = 32;
 __global__ void dfa_proj_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
                                 int batch, const float* __restrict__ eT)
 {
-  const int li = first + blockIdx.y;
+  const int li = first + blockIdx.z;
   if (li + 1 >= n_layers)
     return;
   const dpc_layer L = layers[li];
@@ -548,17 +551,52 @@ __global__ void dfa_proj_kernel(const dpc_layer* __restrict__ layers, int first,
   if (L.next_size <= 0 || Lup.Psi == nullptr)
     return;
   const int TS = L.terminal_size, n = L.next_size;
-  const size_t total = (size_t)batch * n;
-  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
-       o += (size_t)gridDim.x * blockDim.x)
+  const int b0 = blockIdx.y * DFA_ROWS;
+  if (b0 >= batch || (int)(blockIdx.x * blockDim.x) >= n)
+    return;
+  __shared__ __align__(16) float es[DFA_ROWS][16];
+  for (int kc = 0; kc < TS; kc += 16)
   {
-    const int b = (int)(o / n), j = (int)(o % n);
-    const float* er = eT + (size_t)b * TS;
-    const float* pr = Lup.Psi + (size_t)j * Lup.psi_stride;
-    float s = 0.0f;
-    for (int k = 0; k < TS; ++k)
-      s = fmaf(er[k], pr[k], s);
-    L.fe[o] = s * act_deriv(L.act, L.preact[o]);
+    const int kn = min(16, TS - kc);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < DFA_ROWS * 16; idx += blockDim.x)
+    {
+      const int r = idx >> 4, k = idx & 15;
+      es[r][k] = (b0 + r < batch && k < kn) ? eT[(size_t)(b0 + r) * TS + kc + k] : 0.0f;
+    }
+    __syncthreads();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n)
+    {
+      float psi[16];
+      const float* pr = Lup.Psi + (size_t)j * Lup.psi_stride + kc;
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        psi[k] = k < kn ? pr[k] : 0.0f;
+      const bool last = kc + 16 >= TS;
+#pragma unroll 4
+      for (int r = 0; r < DFA_ROWS; ++r)
+      {
+        if (b0 + r >= batch)
+          break;
+        float acc = 0.0f;
+#pragma unroll
+        for (int k4 = 0; k4 < 16; k4 += 4)
+        {
+          const float4 e4 = *reinterpret_cast<const float4*>(&es[r][k4]);
+          acc = fmaf(e4.x, psi[k4], acc);
+          acc = fmaf(e4.y, psi[k4 + 1], acc);
+          acc = fmaf(e4.z, psi[k4 + 2], acc);
+          acc = fmaf(e4.w, psi[k4 + 3], acc);
+        }
+        const size_t o = (size_t)(b0 + r) * n + j;
+        if (kc > 0)
+          acc += L.fe[o];
+        if (last)
+          acc *= act_deriv(L.act, L.preact[o]);
+        L.fe[o] = acc;
+      }
+    }
   }
 }
 
@@ -624,8 +662,11 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
   const int TS = L.terminal_size, s = L.size;
   const bool full_kind = (L.flags & DPC_LAYER_FULLPC_PSI) != 0;
   const float rate = full_kind ? L.fl * L.a : L.fl;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < s; i += gridDim.x * blockDim.x)
+  constexpr int PSI_ROWS = 64;
+  __shared__ __align__(16) float es[PSI_ROWS][16];
+  for (int i0 = blockIdx.x * blockDim.x; i0 < s; i0 += gridDim.x * blockDim.x)
   {
+    const int i = i0 + threadIdx.x;
     for (int kc = 0; kc < TS; kc += 16)
     {
       float acc[16];
@@ -633,15 +674,38 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
       for (int k = 0; k < 16; ++k)
         acc[k] = 0.0f;
       const int kn = min(16, TS - kc);
-      for (int b = 0; b < batch; ++b)
+      // The terminal errors of PSI_ROWS batch rows at a time go through shared memory (zero
+      // padded to 16 columns), so each thread issues one global load per row.
+      for (int b0 = 0; b0 < batch; b0 += PSI_ROWS)
       {
-        const float zv = L.z[(size_t)b * s + i];
-        const float* er = eT + (size_t)b * TS + kc;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < PSI_ROWS * 16; idx += blockDim.x)
+        {
+          const int r = idx >> 4, k = idx & 15;
+          es[r][k] = (b0 + r < batch && k < kn) ? eT[(size_t)(b0 + r) * TS + kc + k] : 0.0f;
+        }
+        __syncthreads();
+        if (i < s)
+        {
+          const int rows = min(PSI_ROWS, batch - b0);
+#pragma unroll 8
+          for (int r = 0; r < rows; ++r)
+          {
+            const float zv = L.z[(size_t)(b0 + r) * s + i];
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
-          if (k < kn)
-            acc[k] = fmaf(zv, er[k], acc[k]);
+            for (int k4 = 0; k4 < 16; k4 += 4)
+            {
+              const float4 e4 = *reinterpret_cast<const float4*>(&es[r][k4]);
+              acc[k4] = fmaf(zv, e4.x, acc[k4]);
+              acc[k4 + 1] = fmaf(zv, e4.y, acc[k4 + 1]);
+              acc[k4 + 2] = fmaf(zv, e4.z, acc[k4 + 2]);
+              acc[k4 + 3] = fmaf(zv, e4.w, acc[k4 + 3]);
+            }
+          }
+        }
       }
+      if (i >= s)
+        continue;
       float* prow = L.Psi + (size_t)i * L.psi_stride + kc;
       if (L.opt_psi == DPC_OPT_SGD)
       {

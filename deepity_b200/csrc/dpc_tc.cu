@@ -249,31 +249,46 @@ __device__ __forceinline__ void st8(float* p, const float* r)
 // Forward epilogue of one 128 x BN tile for the 32 rows of one warp.  ACT >= 0 fixes the
 // activation at compile time (the per-element switch disappears), ACT < 0 reads it from the
 // layer.  The operand read from the layer above is fetched one chunk ahead when PREFETCH.
+// The fields of the layer table the forward epilogue needs, fetched BEFORE the warp waits for
+// the accumulator so their latency overlaps the main loop (registers are scarce: only these).
+struct FwdMeta
+{
+  float a;
+  int flags, act, up_flags;
+  const float* b;
+  const float* z;
+  float *preact, *mu, *fe, *up_z, *up_e;
+};
+
+__device__ __forceinline__ void load_fwd_meta(const TcParams& P, int li, FwdMeta& M)
+{
+  const dpc_layer* Lp = &P.layers[li];
+  M.a = Lp->a, M.flags = Lp->flags, M.act = Lp->act, M.b = Lp->b, M.z = Lp->z;
+  M.preact = Lp->preact, M.mu = Lp->mu, M.fe = Lp->fe;
+  if (li + 1 < P.n_layers)
+  {
+    const dpc_layer* Lup = Lp + 1;
+    M.up_z = Lup->z, M.up_e = Lup->e, M.up_flags = Lup->flags;
+  }
+  else
+    M.up_z = M.up_e = nullptr, M.up_flags = 0;
+}
+
 template <int ACT, int BN, int GROUPS, bool PREFETCH>
-__device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const dpc_layer* Lp,
-                                                  const dpc_layer* Lup, uint32_t taddr, int m,
+__device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMeta& L,
+                                                  const float* bias_pre, uint32_t taddr, int m,
                                                   int n0, int grp, float& esum)
 {
-  // Only the fields this pass needs are pulled out of the layer table (registers are scarce).
-  struct
-  {
-    float a;
-    int flags;
-    const float* b;
-    const float* z;
-    float *preact, *mu, *fe;
-  } L;
-  L.a = Lp->a, L.flags = Lp->flags, L.b = Lp->b, L.z = Lp->z;
-  L.preact = Lp->preact, L.mu = Lp->mu, L.fe = Lp->fe;
-  const int act = ACT >= 0 ? ACT : Lp->act;
-  const bool next_ce = Lup && (Lup->flags & DPC_LAYER_SOFTMAX_CE);
+  const int act = ACT >= 0 ? ACT : L.act;
+  const bool Lup = L.up_z != nullptr;
+  const bool next_ce = Lup && (L.up_flags & DPC_LAYER_SOFTMAX_CE);
   const bool do_err = (P.flags & DPC_FWD_ERR_NEXT) && Lup && !next_ce;
   const bool do_fe = (P.flags & DPC_FWD_FE) && Lup && !(next_ce && (P.flags & DPC_FWD_ERR_NEXT));
   const bool do_copy = (P.flags & DPC_FWD_COPY_NEXT) && Lup;
   const bool store = !(P.flags & DPC_FWD_TRANSIENT);
   const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
-  float* up_z = Lup ? Lup->z : nullptr;
-  float* up_e = Lup ? Lup->e : nullptr;
+  float* up_z = L.up_z;
+  float* up_e = L.up_e;
   // What the epilogue reads from the layer above: its belief (fresh error) or its stored
   // error (feedback error from the error already in memory).
   const float* up_src = (do_err && !do_copy) ? up_z : ((do_fe && !do_err) ? up_e : nullptr);
@@ -302,7 +317,14 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const dpc_l
     for (int k = 0; k < CW; k += 8)
     {
       float bb[8], pre[8], mu[8], d[8], e[8];
-      ld8(L.b + n0 + c * CW + k, bb);
+      if (BN / GROUPS <= 32)
+      {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          bb[q] = bias_pre[((c - grp) / GROUPS) * CW + k + q];
+      }
+      else
+        ld8(L.b + n0 + c * CW + k, bb);
 #pragma unroll
       for (int q = 0; q < 8; ++q)
       {
@@ -586,6 +608,21 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
       const int li = P.first + lrel;
       const dpc_layer* Lup = (li + 1 < P.n_layers) ? &P.layers[li + 1] : nullptr;
       const int acc = tile_iter & 1;
+      FwdMeta meta;
+      float bias_pre[32];
+      if (OP == TC_FWD)
+      {
+        load_fwd_meta(P, li, meta);
+        if (BN / GROUPS <= 32)
+        {
+          // Narrow tiles (the sequential sweep): this warp's bias values are fetched now too.
+#pragma unroll
+          for (int i = 0; i < (BN / GROUPS) / 16; ++i)
+#pragma unroll
+            for (int k = 0; k < 16; k += 8)
+              ld8(meta.b + n0 + (grp + GROUPS * i) * 16 + k, &bias_pre[i * 16 + k]);
+        }
+      }
       if (!mbar_wait(&tfull[acc], (tile_iter >> 1) & 1, abort_flag))
         break;
       tc_fence_after();
@@ -594,17 +631,16 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
       if (OP == TC_FWD)
       {
         constexpr bool PF = !THREE_X;
-        const dpc_layer* Lp = &P.layers[li];
-        switch (Lp->act)
+        switch (meta.act)
         {
         case DPC_ACT_TANH:
-          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF>(P, Lp, Lup, taddr, m, n0, grp, esum);
+          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum);
           break;
         case DPC_ACT_GELU:
-          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF>(P, Lp, Lup, taddr, m, n0, grp, esum);
+          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum);
           break;
         default:
-          fwd_epilogue_tile<-1, BN, GROUPS, false>(P, Lp, Lup, taddr, m, n0, grp, esum);
+          fwd_epilogue_tile<-1, BN, GROUPS, false>(P, meta, bias_pre, taddr, m, n0, grp, esum);
         }
       }
       else if (OP == TC_FB)
