@@ -53,6 +53,7 @@ SIGNATURES = {
     "dpc_relax": (_i, [_vp, _i]),
     "dpc_direct_feedback": (_i, [_vp, _i, _i, _i]),
     "dpc_update_weights": (_i, [_vp, _i, _i, _i]),
+    "dpc_error_energy_static": (_i, [_vp, _vp, _vp, _vp, _i64, _vp]),
     "dpc_energy_reset": (_i, [_vp]),
     "dpc_energy_read": (_i, [_vp, ctypes.POINTER(ctypes.c_double)]),
     "dpcn_create": (_i, [_i, _i, _i, ctypes.POINTER(_vp)]),

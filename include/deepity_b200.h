@@ -223,6 +223,20 @@ DPC_API int dpc_direct_feedback(dpc_plan* plan, int first, int count, int decay_
  * (DirectKPPCLayer.cpp:361-501, FullPCLayer.cpp:382-512, SimplePCLayer.cpp:259-350,
  * CPUBackend.cpp:250-272, 721-772). */
 DPC_API int dpc_update_weights(dpc_plan* plan, int first, int count, int center_rows);
+/* The error/energy kernel for callers that must not allocate device memory (code between
+ * graph captures, hosts whose framework owns every byte of the GPU, loops that forbid
+ * allocation once running).  It has no counterpart in the reference.  e = z - mu over
+ * `count` floats and *energy_dev = 0.5*sum(e^2), all four pointers device memory the caller
+ * provides, work ordered on `stream` (a cudaStream_t; NULL = the default stream) of the
+ * device that is current on the calling thread.  Nothing is allocated or freed: the
+ * reduction scratch is a static device array of 1025 doubles that every GPU loading this
+ * library holds until exit.  count may not exceed 2^26 (DPC_ERR_TOO_LARGE otherwise).  The
+ * first call on a device looks up the array's address; make that call before any stream
+ * capture.  All calls share the one array, which keeps what the last call left in it (the
+ * entry clears the part that must start at zero): two calls whose kernels overlap on the GPU
+ * race, so order them on one stream or with events. */
+DPC_API int dpc_error_energy_static(void* stream, const float* z_dev, const float* mu_dev,
+                                    float* e_dev, int64_t count, float* energy_dev);
 /* Energy accumulator of the plan (device-resident double). */
 DPC_API int dpc_energy_reset(dpc_plan* plan);
 DPC_API int dpc_energy_read(dpc_plan* plan, double* out); /* synchronous */
