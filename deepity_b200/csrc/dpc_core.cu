@@ -338,7 +338,8 @@ static int validate_layers(const dpc_layer* layers, int n, int batch)
         return fail(DPC_ERR_INVALID, "plan: Adam state missing on layer " + std::to_string(i));
       if (L.Psi && L.opt_psi != DPC_OPT_SGD && (!L.m_Psi || !L.v_Psi || !L.t_Psi))
         return fail(DPC_ERR_INVALID, "plan: Psi Adam state missing on layer " + std::to_string(i));
-      if (L.Psi && (L.psi_stride < L.terminal_size || L.terminal_size != layers[n - 1].size))
+      // (the last layer of a layer-sharded block is not the terminal: only the stride is checked)
+      if (L.Psi && (L.psi_stride < L.terminal_size || L.terminal_size <= 0))
         return fail(DPC_ERR_INVALID, "plan: terminal_size / psi_stride mismatch on layer " +
                                          std::to_string(i));
     }
