@@ -47,6 +47,7 @@ SIGNATURES = {
     "dpc_plan_tensor_run": (_i, [_vp, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "dpc_forward": (_i, [_vp, _i, _i, _i]),
     "dpc_project_forward": (_i, [_vp, _i, _i, _i]),
+    "dpc_project_forward_ex": (_i, [_vp, _i, _i, _i, _i]),
     "dpc_error": (_i, [_vp, _i, _i]),
     "dpc_feedback_error": (_i, [_vp, _i, _i]),
     "dpc_update_state": (_i, [_vp, _i, _i]),

@@ -509,6 +509,12 @@ int dpc_forward(dpc_plan* p, int first, int count, int flags)
 
 int dpc_project_forward(dpc_plan* p, int first, int count, int skip_last_copy)
 {
+  return dpc_project_forward_ex(p, first, count, skip_last_copy, 0);
+}
+
+int dpc_project_forward_ex(dpc_plan* p, int first, int count, int skip_last_copy, int extra)
+{
+  extra &= DPC_FWD_NO_MU;
   int rc = check_range(p, first, count);
   if (rc != DPC_OK)
     return rc;
@@ -518,9 +524,11 @@ int dpc_project_forward(dpc_plan* p, int first, int count, int skip_last_copy)
       !(skip_last_copy && p->run.first + p->run.count + 1 == p->n))
   {
     for (int i = first; i < p->run.first; ++i)
-      if ((rc = dpc_forward(p, i, 1, DPC_FWD_COPY_NEXT)) != DPC_OK)
+      if ((rc = dpc_forward(p, i, 1, DPC_FWD_COPY_NEXT | (i == first ? 0 : extra))) != DPC_OK)
         return rc;
-    rc = tc_project_forward(p, p->run.first, p->run.count, DPC_FWD_COPY_NEXT);
+    // (the chain kernel itself keeps mu of the sweep's very first layer when it starts there)
+    rc = tc_project_forward(p, p->run.first, p->run.count,
+                            DPC_FWD_COPY_NEXT | extra | (p->run.first == first ? (1 << 10) : 0));
     if (rc < 0)
       return rc;
     i0 = rc == DPC_OK ? p->run.first + p->run.count : p->run.first;
@@ -529,7 +537,7 @@ int dpc_project_forward(dpc_plan* p, int first, int count, int skip_last_copy)
   {
     if (p->h[i].next_size <= 0)
       continue;
-    int flags = DPC_FWD_COPY_NEXT;
+    int flags = DPC_FWD_COPY_NEXT | (i == first ? 0 : extra);
     if (skip_last_copy && i + 2 == p->n)
       flags = 0;
     rc = dpc_forward(p, i, 1, flags);

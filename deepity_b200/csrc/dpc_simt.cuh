@@ -285,7 +285,8 @@ __global__ void __launch_bounds__(NTHREADS)
         {
           if (L.preact)
             L.preact[o] = pre;
-          L.mu[o] = mu;
+          if (!(do_copy && (flags & DPC_FWD_NO_MU)))
+            L.mu[o] = mu;
         }
         if (do_copy)
           Lup->z[o] = mu;

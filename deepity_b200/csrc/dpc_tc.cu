@@ -51,7 +51,7 @@ constexpr int WG_LEARN_MODE = 0, WG_DFA_MODE = 1;
 struct TcState
 {
   bool ok = false;
-  CUtensorMap z_km, fe_km, w_km64, w_km128, w_km256, z_mn, fe_mn, w_mn;
+  CUtensorMap z_km, fe_km, w_km32, w_km64, w_km128, w_km256, z_mn, fe_mn, w_mn;
   int* chain_counters = nullptr; // device: [layers of the run][row blocks]
   int* error_flag = nullptr; // device
   int* error_host = nullptr; // pinned
@@ -74,6 +74,10 @@ struct TcParams
   int chain;
   int* chain_counters;
   int chain_target;
+  // Optional timing trace of the chain kernel (NULL in normal use): for CTA 0 and the first
+  // 256 layers, globaltimer stamps of [dependency seen, first operands landed, accumulator
+  // complete, epilogue stores issued, published].
+  unsigned long long* trace;
 };
 
 // ------------------------------------------------------------------------------ PTX
@@ -231,6 +235,16 @@ __device__ __forceinline__ bool chain_wait(const int* ctr, int target, volatile 
   return true;
 }
 
+__device__ __forceinline__ void trace_stamp(const TcParams& P, int layer, int slot)
+{
+  if (P.trace && blockIdx.x == 0 && layer < 256)
+  {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    P.trace[layer * 8 + slot] = t;
+  }
+}
+
 // 256-bit global accesses: eight consecutive floats, 32-byte aligned (one full sector).
 __device__ __forceinline__ void ld8(const float* p, float* r)
 {
@@ -277,7 +291,7 @@ __device__ __forceinline__ void load_fwd_meta(const TcParams& P, int li, FwdMeta
 template <int ACT, int BN, int GROUPS, bool PREFETCH>
 __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMeta& L,
                                                   const float* bias_pre, uint32_t taddr, int m,
-                                                  int n0, int grp, float& esum)
+                                                  int n0, int grp, float& esum, int tl)
 {
   const int act = ACT >= 0 ? ACT : L.act;
   const bool Lup = L.up_z != nullptr;
@@ -286,6 +300,8 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
   const bool do_fe = (P.flags & DPC_FWD_FE) && Lup && !(next_ce && (P.flags & DPC_FWD_ERR_NEXT));
   const bool do_copy = (P.flags & DPC_FWD_COPY_NEXT) && Lup;
   const bool store = !(P.flags & DPC_FWD_TRANSIENT);
+  // bit 10 (internal): the launch starts at the first layer of the sweep, whose mu is kept
+  const bool no_mu = do_copy && (P.flags & DPC_FWD_NO_MU) && !((P.flags & (1 << 10)) && tl == 0);
   const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
   float* up_z = L.up_z;
   float* up_e = L.up_e;
@@ -307,6 +323,8 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
     const size_t o = row + c * CW;
     float v[CW];
     tc_ld16(taddr + c * CW, v);
+    if (tl >= 0 && c == grp && threadIdx.x == 64)
+      trace_stamp(P, tl, 5);
     if (PREFETCH && up_src && c + GROUPS < BN / CW)
     {
 #pragma unroll
@@ -345,7 +363,8 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
       if (store)
       {
         st8(L.preact + o + k, pre);
-        st8(L.mu + o + k, mu);
+        if (!no_mu)
+          st8(L.mu + o + k, mu);
       }
       if (do_copy)
         st8(up_z + o + k, mu);
@@ -372,6 +391,8 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
           e[q] *= d[q];
         st8(L.fe + o + k, e);
       }
+      if (tl >= 0 && c == grp && k == 0 && threadIdx.x == 64)
+        trace_stamp(P, tl, 6);
     }
     if (up_src && c + GROUPS < BN / CW)
     {
@@ -507,6 +528,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
             if (!chain_wait(&P.chain_counters[(t - 1) * P.tiles_m + m0 / TBM], P.chain_target,
                             abort_flag))
               alive = false; // the A copy below still runs so the stage's byte count completes
+            trace_stamp(P, t, 0);
           }
           if (!C::A_MN)
             tma_load_3d(a_dst, &mapA, &full[s], k0, m0, lcoord);
@@ -560,6 +582,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
             break;
           }
           tc_fence_after();
+          if (P.chain && kb == 0)
+            trace_stamp(P, t, 1);
           const uint32_t a_addr = smem_u32(stage_base + s * C::STAGE_BYTES);
           const uint32_t b_addr = a_addr + C::A_BYTES;
           const uint32_t alo_addr = b_addr + C::B_BYTES;
@@ -626,6 +650,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
       if (!mbar_wait(&tfull[acc], (tile_iter >> 1) & 1, abort_flag))
         break;
       tc_fence_after();
+      if (P.chain && warp == 2 && lane == 0)
+        trace_stamp(P, t, 2);
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 
       if (OP == TC_FWD)
@@ -634,13 +660,13 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
         switch (meta.act)
         {
         case DPC_ACT_TANH:
-          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum);
+          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1);
           break;
         case DPC_ACT_GELU:
-          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum);
+          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1);
           break;
         default:
-          fwd_epilogue_tile<-1, BN, GROUPS, false>(P, meta, bias_pre, taddr, m, n0, grp, esum);
+          fwd_epilogue_tile<-1, BN, GROUPS, false>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1);
         }
       }
       else if (OP == TC_FB)
@@ -730,6 +756,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
           }
         }
       }
+      if (P.chain && warp == 2 && lane == 0)
+        trace_stamp(P, t, 3);
       if (P.chain)
       {
         // Publish this warp's rows of the next layer's input: make the stores visible device
@@ -739,6 +767,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
         __syncwarp();
         if (lane == 0)
           atomicAdd(&P.chain_counters[lrel * P.tiles_m + rem / P.tiles_n], 1);
+        if (warp == 2 && lane == 0)
+          trace_stamp(P, t, 4);
       }
       tc_fence_before();
       __syncwarp();
@@ -947,6 +977,7 @@ int tc_plan_init(dpc_plan* plan)
   bool ok = true;
   ok &= make_map(&st->z_km, L0.z, H, B, best_count, plan->run.z_stride, TBM, false);
   ok &= make_map(&st->fe_km, L0.fe, H, B, best_count, plan->run.out_stride, TBM, false);
+  ok &= make_map(&st->w_km32, L0.W, H, H, best_count, plan->run.w_stride, 32, false);
   ok &= make_map(&st->w_km64, L0.W, H, H, best_count, plan->run.w_stride, 64, false);
   ok &= make_map(&st->w_km128, L0.W, H, H, best_count, plan->run.w_stride, 128, false);
   ok &= make_map(&st->w_km256, L0.W, H, H, best_count, plan->run.w_stride, 256, false);
@@ -1021,6 +1052,7 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
   P.chain = 0;
   P.chain_counters = nullptr;
   P.chain_target = 0;
+  P.trace = nullptr;
   return P;
 }
 
@@ -1048,20 +1080,27 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   if (!st || !st->ok || !range_in_run(p, first, count) || count < 2)
     return 1;
   const int H = p->run.width, B = p->batch;
-  const int tiles = (B / TBM) * (H / 64);
+  // Narrow tiles: more CTAs in flight and less epilogue per CTA on the dependent path.
+  const int BNC = ((B / TBM) * (H / 32) <= p->ctx->sm_count) ? 32 : 64;
+  const int tiles = (B / TBM) * (H / BNC);
   if (tiles > p->ctx->sm_count)
     return 1;
-  TcParams P = base_params(p, st, first, count, B, H, H, 64, flags, 0);
+  TcParams P = base_params(p, st, first, count, B, H, H, BNC, flags, 0);
   P.chain = 1;
   P.chain_counters = st->chain_counters;
-  P.chain_target = (H / 64) * 8; // column tiles x epilogue warps
+  P.chain_target = (H / BNC) * 8; // column tiles x epilogue warps
+  if (const char* tp = getenv("DPC_CHAIN_TRACE_PTR"))
+    P.trace = reinterpret_cast<unsigned long long*>(strtoull(tp, nullptr, 0));
   cudaError_t e = cudaMemsetAsync(st->chain_counters, 0, sizeof(int) * (size_t)count * (B / TBM),
                                   p->ctx->stream);
   if (e != cudaSuccess)
     return cuda_fail(e, "cudaMemsetAsync(chain counters)");
-  if (p->ctx->precision == DPC_PRECISION_TF32)
-    return launch<TC_FWD, 64, false>(p, st, st->z_km, st->w_km64, P);
-  return launch<TC_FWD, 64, true>(p, st, st->z_km, st->w_km64, P);
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  if (BNC == 32)
+    return tf32 ? launch<TC_FWD, 32, false>(p, st, st->z_km, st->w_km32, P)
+                : launch<TC_FWD, 32, true>(p, st, st->z_km, st->w_km32, P);
+  return tf32 ? launch<TC_FWD, 64, false>(p, st, st->z_km, st->w_km64, P)
+              : launch<TC_FWD, 64, true>(p, st, st->z_km, st->w_km64, P);
 }
 
 int tc_update_state(dpc_plan* p, int first, int count)

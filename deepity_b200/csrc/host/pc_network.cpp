@@ -488,7 +488,10 @@ void PCNetwork::ProjectForward()
   }
   if (plain)
   {
-    Check(dpc_project_forward(plan, 0, n - 1, layers.back()->clamped ? 1 : 0));
+    // Inside a whole train step only the clamped input layer's mu is read again before it is
+    // recomputed (its cached prediction); the others skip the store.
+    Check(dpc_project_forward_ex(plan, 0, n - 1, layers.back()->clamped ? 1 : 0,
+                                 transientFlag ? DPC_FWD_NO_MU : 0));
     for (int i = 0; i < n - 1; ++i)
       if (layers[i]->clamped)
         layers[i]->cacheValid = true;

@@ -185,6 +185,8 @@ enum
                                  computed with ERR_NEXT, else the one in memory            */
   DPC_FWD_CACHED = 1 << 4,    /* skip the GEMM, reuse preact/mu in memory (a clamped layer's
                                  cached prediction, DirectKPPCLayer.cpp:275-280)          */
+  DPC_FWD_NO_MU = 1 << 9,     /* with COPY_NEXT: mu[l] itself is not written (z[l+1] holds the
+                                 same values and mu is recomputed before anyone reads it)  */
   DPC_FWD_TRANSIENT = 1 << 8  /* preact/mu of this pass are consumed only through the fused
                                  e/fe outputs and recomputed before anyone reads them: do
                                  not write them to memory                                  */
@@ -198,6 +200,10 @@ DPC_API int dpc_forward(dpc_plan* plan, int first, int count, int flags);
  * l+1 is the last layer and skip_last_copy != 0 (a clamped target)
  * (DirectKPPCNetwork::ProjectForward, src/networks/DirectKPPCNetwork.cpp:349-371). */
 DPC_API int dpc_project_forward(dpc_plan* plan, int first, int count, int skip_last_copy);
+/* Same, with extra DPC_FWD_* flags (DPC_FWD_NO_MU) applied to every layer of the sweep but its
+ * first (a clamped input layer's prediction is cached and read again). */
+DPC_API int dpc_project_forward_ex(dpc_plan* plan, int first, int count, int skip_last_copy,
+                                   int extra_flags);
 /* Error of one layer against the prediction below: Gaussian e = z - mu, or softmax
  * cross-entropy when the layer has DPC_LAYER_SOFTMAX_CE.  with_energy accumulates into the
  * plan's energy accumulator (CPUBackend.cpp:602-629, 658-714). */
