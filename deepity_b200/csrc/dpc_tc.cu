@@ -51,7 +51,7 @@ constexpr int WG_LEARN_MODE = 0, WG_DFA_MODE = 1;
 struct TcState
 {
   bool ok = false;
-  CUtensorMap z_km, fe_km, w_km32, w_km64, w_km128, w_km256, z_mn, fe_mn, w_mn;
+  CUtensorMap z_km, z_km64, fe_km, w_km32, w_km64, w_km128, w_km256, z_mn, fe_mn, w_mn;
   int* chain_counters = nullptr; // device: [layers of the run][row blocks]
   int* error_flag = nullptr; // device
   int* error_host = nullptr; // pinned
@@ -291,7 +291,8 @@ __device__ __forceinline__ void load_fwd_meta(const TcParams& P, int li, FwdMeta
 template <int ACT, int BN, int GROUPS, bool PREFETCH>
 __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMeta& L,
                                                   const float* bias_pre, uint32_t taddr, int m,
-                                                  int n0, int grp, float& esum, int tl)
+                                                  int n0, int grp, float& esum, int tl,
+                                                  bool active)
 {
   const int act = ACT >= 0 ? ACT : L.act;
   const bool Lup = L.up_z != nullptr;
@@ -307,10 +308,13 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
   float* up_e = L.up_e;
   // What the epilogue reads from the layer above: its belief (fresh error) or its stored
   // error (feedback error from the error already in memory).
-  const float* up_src = (do_err && !do_copy) ? up_z : ((do_fe && !do_err) ? up_e : nullptr);
+  const float* up_src_all = (do_err && !do_copy) ? up_z : ((do_fe && !do_err) ? up_e : nullptr);
+  const float* up_src = up_src_all;
   const size_t row = (size_t)m * P.N + n0;
   constexpr int CW = 16; // columns per step
   float up[CW], upn[CW];
+  if (!active)
+    up_src = nullptr; // lanes that hold no accumulator row touch no memory
   if (up_src)
   {
 #pragma unroll
@@ -352,7 +356,7 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
         else
           mu[q] = act_fwd(act, pre[q]), d[q] = 1.0f;
       }
-      if (residual)
+      if (residual && active)
       {
         float zz[8];
         ld8(L.z + o + k, zz);
@@ -360,36 +364,38 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
         for (int q = 0; q < 8; ++q)
           mu[q] += zz[q];
       }
-      if (store)
+      if (store && active)
       {
         st8(L.preact + o + k, pre);
         if (!no_mu)
           st8(L.mu + o + k, mu);
       }
-      if (do_copy)
+      if (do_copy && active)
         st8(up_z + o + k, mu);
       if (do_err)
       {
 #pragma unroll
         for (int q = 0; q < 8; ++q)
         {
-          e[q] = do_copy ? 0.0f : up[k + q] - mu[q];
+          e[q] = (do_copy || !active) ? 0.0f : up[k + q] - mu[q];
           esum += e[q] * e[q];
         }
-        st8(up_e + o + k, e);
+        if (active)
+          st8(up_e + o + k, e);
       }
       else if (do_fe)
       {
 #pragma unroll
         for (int q = 0; q < 8; ++q)
-          e[q] = up[k + q];
+          e[q] = active ? up[k + q] : 0.0f;
       }
       if (do_fe)
       {
 #pragma unroll
         for (int q = 0; q < 8; ++q)
           e[q] *= d[q];
-        st8(L.fe + o + k, e);
+        if (active)
+          st8(L.fe + o + k, e);
       }
       if (tl >= 0 && c == grp && k == 0 && threadIdx.x == 64)
         trace_stamp(P, tl, 6);
@@ -415,30 +421,35 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
 // ------------------------------------------------------------------------------ kernel
 // Warp roles: 0 TMA producer, 1 MMA issuer (+ tensor-memory owner), 2..9 epilogue,
 // 10..13 remainder ("lo") transform (3xTF32 only).
-template <int OP, int BN, bool THREE_X>
+template <int OP, int BN, bool THREE_X, int BM = 128>
 struct Cfg
 {
   static constexpr bool A_MN = (OP == TC_WG);
   static constexpr bool B_MN = (OP != TC_FWD);
-  static constexpr int A_BYTES = TBM * TBK * 4;
+  static constexpr int A_BYTES = BM * TBK * 4;
   static constexpr int B_BYTES = BN * TBK * 4;
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (THREE_X ? 2 : 1);
-  static constexpr int STAGES = (196608 / STAGE_BYTES) < 2 ? 2 : (196608 / STAGE_BYTES);
+  // at most 8 stages: the barrier block after the ring is sized for that
+  static constexpr int STAGES_RAW = 196608 / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW);
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS = (2 + EPI_WARPS + (THREE_X ? 4 : 0)) * 32;
-  static constexpr int TMEM_COLS = 2 * BN;
+  // (Spreading the k-steps of a narrow tile over several accumulators was measured: it does not
+  // shorten the main loop, whose per-k-block cost is the barrier/TMA handshake.)
+  static constexpr int KSPLIT = 1;
+  static constexpr int TMEM_COLS = 2 * BN * KSPLIT;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
                                     ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
-                                    ((uint32_t)(TBM >> 4) << 24);
+                                    ((uint32_t)(BM >> 4) << 24);
 };
 
-template <int OP, int BN, bool THREE_X>
-__global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
+template <int OP, int BN, bool THREE_X, int BM = 128>
+__global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
     pc_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const TcParams P)
 {
-  using C = Cfg<OP, BN, THREE_X>;
+  using C = Cfg<OP, BN, THREE_X, BM>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -495,18 +506,20 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0)
     {
-      int it = 0;
+      int s = 0;
+      uint32_t phase = 1; // parity to wait for on empty[s]; flips each time the ring wraps
       bool alive = true;
       for (int t = t_begin; t < t_end && alive; t += t_step)
       {
         const int lrel = P.chain ? t : t / tiles_per_layer;
         const int rem = P.chain ? (int)blockIdx.x : t % tiles_per_layer;
-        const int m0 = (rem / P.tiles_n) * TBM, n0 = (rem % P.tiles_n) * BN;
+        const int m0 = (rem / P.tiles_n) * BM, n0 = (rem % P.tiles_n) * BN;
         const int lcoord = P.first + lrel - P.run_first;
-        for (int kb = 0; kb < kblocks; ++kb, ++it)
+        for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == C::STAGES ? 0 : s + 1))
         {
-          const int s = it % C::STAGES;
-          if (!mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag))
+          if (s == 0 && !(t == t_begin && kb == 0))
+            phase ^= 1;
+          if (!mbar_wait(&empty[s], phase, abort_flag))
           {
             alive = false;
             break;
@@ -525,7 +538,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
             // The rows of this layer's input are the previous layer's output: wait until every
             // tile of that row block has been published (the weights above are already on
             // their way).
-            if (!chain_wait(&P.chain_counters[(t - 1) * P.tiles_m + m0 / TBM], P.chain_target,
+            if (!chain_wait(&P.chain_counters[(t - 1) * P.tiles_m + m0 / BM], P.chain_target,
                             abort_flag))
               alive = false; // the A copy below still runs so the stage's byte count completes
             trace_stamp(P, t, 0);
@@ -533,7 +546,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
           if (!C::A_MN)
             tma_load_3d(a_dst, &mapA, &full[s], k0, m0, lcoord);
           else
-            for (int i = 0; i < TBM / 32; ++i)
+            for (int i = 0; i < BM / 32; ++i)
               tma_load_3d(a_dst + i * (TBK * 128), &mapA, &full[s], m0 + 32 * i, k0, lcoord);
           if (!alive)
             break;
@@ -557,7 +570,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0)
     {
-      int it = 0, tile_iter = 0;
+      int s = 0, tile_iter = 0;
+      uint32_t phase = 0; // parity to wait for on full[s] / xf[s]
       bool alive = true;
       const uint32_t a_lbo = C::A_MN ? TBK * 128 : 16, b_lbo = C::B_MN ? TBK * 128 : 16;
       const uint32_t a_adv = C::A_MN ? 1024 : UMMA_K * 4, b_adv = C::B_MN ? 1024 : UMMA_K * 4;
@@ -565,18 +579,19 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
       // 32 columns TBK*128 bytes apart.  K-major tiles: 8 rows per atom (1024 B between groups).
       const uint32_t a_sbo = C::A_MN ? 512 : 1024, b_sbo = C::B_MN ? 512 : 1024;
       const uint32_t a_lay = C::A_MN ? 1 : 2, b_lay = C::B_MN ? 1 : 2;
+      const uint64_t da0 = make_desc(smem_u32(stage_base), a_lbo, a_sbo, a_lay);
+      const uint64_t db0 = make_desc(smem_u32(stage_base) + C::A_BYTES, b_lbo, b_sbo, b_lay);
       for (int t = t_begin; t < t_end && alive; t += t_step, ++tile_iter)
       {
         const int acc = tile_iter & 1;
         if (!mbar_wait(&tempty[acc], ((tile_iter >> 1) & 1) ^ 1, abort_flag))
           break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it)
+        const uint32_t d_tmem0 = tmem_base + acc * (BN * C::KSPLIT);
+        for (int kb = 0; kb < kblocks; ++kb)
         {
-          const int s = it % C::STAGES;
           uint64_t* ready = THREE_X ? &xf[s] : &full[s];
-          if (!mbar_wait(ready, (it / C::STAGES) & 1, abort_flag))
+          if (!mbar_wait(ready, phase, abort_flag))
           {
             alive = false;
             break;
@@ -584,20 +599,21 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
           tc_fence_after();
           if (P.chain && kb == 0)
             trace_stamp(P, t, 1);
-          const uint32_t a_addr = smem_u32(stage_base + s * C::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + C::A_BYTES;
-          const uint32_t alo_addr = b_addr + C::B_BYTES;
-          const uint32_t blo_addr = alo_addr + C::A_BYTES;
+          // Descriptors differ between stages and k-steps only in the 14-bit start-address
+          // field (units of 16 bytes): one add per operand per instruction.
+          const uint64_t sa = da0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
+          const uint64_t sb = db0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
 #pragma unroll
           for (int ks = 0; ks < TBK / UMMA_K; ++ks)
           {
-            const uint64_t da = make_desc(a_addr + ks * a_adv, a_lbo, a_sbo, a_lay);
-            const uint64_t db = make_desc(b_addr + ks * b_adv, b_lbo, b_sbo, b_lay);
-            const uint32_t first = (kb | ks) != 0;
+            const uint64_t da = sa + (uint64_t)(ks * (a_adv >> 4));
+            const uint64_t db = sb + (uint64_t)(ks * (b_adv >> 4));
+            const uint32_t d_tmem = d_tmem0 + (ks % C::KSPLIT) * BN;
+            const uint32_t first = C::KSPLIT > 1 ? (kb != 0) : ((kb | ks) != 0);
             if (THREE_X)
             {
-              const uint64_t dal = make_desc(alo_addr + ks * a_adv, a_lbo, a_sbo, a_lay);
-              const uint64_t dbl = make_desc(blo_addr + ks * b_adv, b_lbo, b_sbo, b_lay);
+              const uint64_t dal = da + (uint64_t)((C::A_BYTES + C::B_BYTES) >> 4);
+              const uint64_t dbl = db + (uint64_t)((C::A_BYTES + C::B_BYTES) >> 4);
               tc_mma_tf32(d_tmem, da, dbl, C::IDESC, first);
               tc_mma_tf32(d_tmem, dal, db, C::IDESC, 1);
               tc_mma_tf32(d_tmem, da, db, C::IDESC, 1);
@@ -606,6 +622,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
               tc_mma_tf32(d_tmem, da, db, C::IDESC, first);
           }
           tc_commit(&empty[s]);
+          if (++s == C::STAGES)
+            s = 0, phase ^= 1;
         }
         if (alive)
           tc_commit(&tfull[acc]);
@@ -627,7 +645,10 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
     {
       const int lrel = P.chain ? t : t / tiles_per_layer;
         const int rem = P.chain ? (int)blockIdx.x : t % tiles_per_layer;
-      const int m = (rem / P.tiles_n) * TBM + quarter * 32 + lane;
+      // M=128: lane i of quarter q holds row 32q+i.  M=64: rows 16q..16q+15 sit in lanes 0..15 of
+      // quarter q and the upper 16 lanes hold nothing.
+      const bool active = BM == 128 || lane < 16;
+      const int m = (rem / P.tiles_n) * BM + (BM == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15));
       const int n0 = (rem % P.tiles_n) * BN;
       const int li = P.first + lrel;
       const dpc_layer* Lup = (li + 1 < P.n_layers) ? &P.layers[li + 1] : nullptr;
@@ -652,7 +673,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
       tc_fence_after();
       if (P.chain && warp == 2 && lane == 0)
         trace_stamp(P, t, 2);
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (BN * C::KSPLIT);
 
       if (OP == TC_FWD)
       {
@@ -660,13 +681,13 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
         switch (meta.act)
         {
         case DPC_ACT_TANH:
-          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1);
+          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active);
           break;
         case DPC_ACT_GELU:
-          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1);
+          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active);
           break;
         default:
-          fwd_epilogue_tile<-1, BN, GROUPS, false>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1);
+          fwd_epilogue_tile<-1, BN, GROUPS, false>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active);
         }
       }
       else if (OP == TC_FB)
@@ -791,14 +812,14 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X>::THREADS, 1)
     // when it reads the raw tile as TF32.  Elementwise on identical offsets, so the swizzled
     // layout of the tile carries over unchanged.
     const int tid = threadIdx.x - (2 + C::EPI_WARPS) * 32;
-    int it = 0;
+    int s = 0;
+    uint32_t phase = 0;
     bool alive = true;
     for (int t = t_begin; t < t_end && alive; t += t_step)
     {
-      for (int kb = 0; kb < kblocks; ++kb, ++it)
+      for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == C::STAGES ? 0 : s + 1), phase ^= (s == 0))
       {
-        const int s = it % C::STAGES;
-        if (!mbar_wait(&full[s], (it / C::STAGES) & 1, abort_flag))
+        if (!mbar_wait(&full[s], phase, abort_flag))
         {
           alive = false;
           break;
@@ -879,12 +900,12 @@ bool make_map(CUtensorMap* map, const float* base, int cols, int rows, int layer
   return r == CUDA_SUCCESS;
 }
 
-template <int OP, int BN, bool THREE_X>
+template <int OP, int BN, bool THREE_X, int BM = 128>
 int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P)
 {
-  using C = Cfg<OP, BN, THREE_X>;
+  using C = Cfg<OP, BN, THREE_X, BM>;
   static bool configured = false;
-  auto kern = pc_tc_kernel<OP, BN, THREE_X>;
+  auto kern = pc_tc_kernel<OP, BN, THREE_X, BM>;
   if (!configured)
   {
     if (C::SMEM_BYTES > st->max_smem)
@@ -976,6 +997,7 @@ int tc_plan_init(dpc_plan* plan)
   const int H = L0.size;
   bool ok = true;
   ok &= make_map(&st->z_km, L0.z, H, B, best_count, plan->run.z_stride, TBM, false);
+  ok &= make_map(&st->z_km64, L0.z, H, B, best_count, plan->run.z_stride, 64, false);
   ok &= make_map(&st->fe_km, L0.fe, H, B, best_count, plan->run.out_stride, TBM, false);
   ok &= make_map(&st->w_km32, L0.W, H, H, best_count, plan->run.w_stride, 32, false);
   ok &= make_map(&st->w_km64, L0.W, H, H, best_count, plan->run.w_stride, 64, false);
@@ -986,7 +1008,7 @@ int tc_plan_init(dpc_plan* plan)
   ok &= make_map(&st->w_mn, L0.W, H, H, best_count, plan->run.w_stride, 32, true);
   if (!ok)
     return DPC_OK; // the driver refused a tensor map: stay on the CUDA-core path
-  if (cudaMalloc(&st->chain_counters, sizeof(int) * (size_t)best_count * (B / TBM)) != cudaSuccess ||
+  if (cudaMalloc(&st->chain_counters, sizeof(int) * (size_t)best_count * (B / 64)) != cudaSuccess ||
       cudaMalloc(&st->error_flag, sizeof(int)) != cudaSuccess ||
       cudaMemset(st->error_flag, 0, sizeof(int)) != cudaSuccess ||
       cudaMallocHost(&st->error_host, sizeof(int)) != cudaSuccess)
@@ -1033,7 +1055,7 @@ int tc_check_error(dpc_plan* plan)
 }
 
 static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int M, int N, int K,
-                            int BN, int flags, int mode)
+                            int BN, int flags, int mode, int BM = TBM)
 {
   TcParams P;
   P.layers = p->d;
@@ -1043,7 +1065,7 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
   P.batch = p->batch;
   P.run_first = p->run.first;
   P.M = M, P.N = N, P.K = K;
-  P.tiles_m = M / TBM;
+  P.tiles_m = M / BM;
   P.tiles_n = N / BN;
   P.flags = flags;
   P.mode = mode;
@@ -1080,7 +1102,10 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   if (!st || !st->ok || !range_in_run(p, first, count) || count < 2)
     return 1;
   const int H = p->run.width, B = p->batch;
-  // Narrow tiles: more CTAs in flight and less epilogue per CTA on the dependent path.
+  // Narrow 128 x 32 tiles: B/128 * H/32 CTAs (128 for the 1024 x 512 layers of the deep-stack
+  // benchmark) keep the epilogue and the publish step on the dependent path short.  (Tiles of
+  // 64 rows were measured too: a tcgen05.mma costs about the same whatever M and N are, so
+  // they do not shorten the chain.)
   const int BNC = ((B / TBM) * (H / 32) <= p->ctx->sm_count) ? 32 : 64;
   const int tiles = (B / TBM) * (H / BNC);
   if (tiles > p->ctx->sm_count)

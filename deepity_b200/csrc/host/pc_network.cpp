@@ -541,7 +541,11 @@ float PCNetwork::CalculateState(bool needEnergy)
   RequireCompiled();
   const int n = (int)layers.size();
   Check(dpc_zero(ctx, layers[0]->d.e, (size_t)batchSize * layers[0]->d.size * sizeof(float)));
-  ForwardRange(0, n - 1, StateFlags(kind, needEnergy) | (needEnergy ? 0 : transientFlag));
+  int flags = StateFlags(kind, needEnergy) | (needEnergy ? 0 : transientFlag);
+  // The energy pass that closes a train step is followed by no state update: nobody reads fe.
+  if (needEnergy && transientFlag)
+    flags &= ~DPC_FWD_FE;
+  ForwardRange(0, n - 1, flags);
   if (layers.back()->d.flags & DPC_LAYER_SOFTMAX_CE)
   {
     Check(dpc_error(plan, n - 1, needEnergy ? 1 : 0));
