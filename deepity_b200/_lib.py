@@ -44,6 +44,7 @@ SIGNATURES = {
     "dpc_plan_update": (_i, [_vp, _vp, _i]),
     "dpc_plan_destroy": (_i, [_vp]),
     "dpc_plan_set_terminal_error": (_i, [_vp, _vp]),
+    "dpc_plan_set_chain_trace": (_i, [_vp, _vp]),
     "dpc_plan_tensor_run": (_i, [_vp, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "dpc_forward": (_i, [_vp, _i, _i, _i]),
     "dpc_project_forward": (_i, [_vp, _i, _i, _i]),
@@ -51,6 +52,8 @@ SIGNATURES = {
     "dpc_error": (_i, [_vp, _i, _i]),
     "dpc_feedback_error": (_i, [_vp, _i, _i]),
     "dpc_update_state": (_i, [_vp, _i, _i]),
+    "dpc_epc_reconstruct": (_i, [_vp, _i]),
+    "dpc_epc_adjoint": (_i, [_vp, _i, _i, _f, _i]),
     "dpc_relax": (_i, [_vp, _i]),
     "dpc_direct_feedback": (_i, [_vp, _i, _i, _i]),
     "dpc_update_weights": (_i, [_vp, _i, _i, _i]),

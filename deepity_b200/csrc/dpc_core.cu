@@ -427,6 +427,14 @@ int dpc_plan_set_terminal_error(dpc_plan* p, const float* e_terminal_dev)
   return DPC_OK;
 }
 
+int dpc_plan_set_chain_trace(dpc_plan* p, void* trace_dev)
+{
+  if (!p)
+    return fail(DPC_ERR_INVALID, "null plan");
+  tc_set_chain_trace(p, static_cast<unsigned long long*>(trace_dev));
+  return DPC_OK;
+}
+
 int dpc_plan_tensor_run(dpc_plan* p, int* first, int* count)
 {
   if (!p)
@@ -637,6 +645,50 @@ int dpc_update_state(dpc_plan* p, int first, int count)
   return dispatch_range(
       p, first, count, [&](int f, int c) { return tc_update_state(p, f, c); },
       [&](int f, int c) { return update_state_simt(p, f, c); });
+}
+
+int dpc_epc_reconstruct(dpc_plan* p, int layer)
+{
+  int rc = check_range(p, layer, 1);
+  if (rc != DPC_OK)
+    return rc;
+  if (layer == 0)
+    return fail(DPC_ERR_INVALID, "dpc_epc_reconstruct: the input layer has nothing below it");
+  epc_reconstruct_kernel<<<elem_blocks(p, (size_t)p->batch * p->h[layer].size), NTHREADS, 0,
+                           p->ctx->stream>>>(p->d, layer, p->batch);
+  return check_launch(p->ctx, "epc_reconstruct kernel");
+}
+
+int dpc_epc_adjoint(dpc_plan* p, int layer, int from_terminal, float scale, int clamped)
+{
+  int rc = check_range(p, layer, 1);
+  if (rc != DPC_OK)
+    return rc;
+  const dpc_layer& L = p->h[layer];
+  if (layer + 1 >= p->n || L.next_size <= 0 || !L.adj || !L.fe || !L.preact)
+    return fail(DPC_ERR_INVALID, "dpc_epc_adjoint: layer has no weights, no adjoint buffer or no "
+                                 "upper neighbour");
+  const float* src = from_terminal ? p->h[p->n - 1].e : p->h[layer + 1].adj;
+  if (!src)
+    return fail(DPC_ERR_INVALID, "dpc_epc_adjoint: the layer above has no adjoint buffer");
+  cudaStream_t st = p->ctx->stream;
+  epc_source_kernel<<<elem_blocks(p, (size_t)p->batch * L.next_size), NTHREADS, 0, st>>>(
+      p->d, layer, p->batch, src);
+  if ((rc = check_launch(p->ctx, "epc_source kernel")) != DPC_OK)
+    return rc;
+  // hop scale travels as float bits with the lowest mantissa bit replaced by the clamp flag
+  // (scale is +1 or -1, whose lowest mantissa bit is zero)
+  union
+  {
+    float f;
+    int i;
+  } u;
+  u.f = scale;
+  const int packed = (u.i & ~1) | (clamped ? 1 : 0);
+  dim3 grid(cdiv(L.size, BN), cdiv(p->batch, BM), 1);
+  pc_gemm_kernel<OP_FB><<<grid, NTHREADS, 0, st>>>(p->d, layer, p->n, p->batch, packed, FB_ADJOINT,
+                                                  p->energy, src);
+  return check_launch(p->ctx, "epc_adjoint kernel");
 }
 
 int dpc_relax(dpc_plan* p, int layer)

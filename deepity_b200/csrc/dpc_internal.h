@@ -75,4 +75,5 @@ int tc_weight_gemm(dpc_plan* plan, int first, int count, int mode);
 // Synchronous: reads the device-side status flag the kernels raise when a bounded wait runs
 // out; DPC_ERR_TIMEOUT if it was raised.
 int tc_check_error(dpc_plan* plan);
+void tc_set_chain_trace(dpc_plan* plan, unsigned long long* buf);
 } // namespace dpc

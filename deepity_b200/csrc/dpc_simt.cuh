@@ -23,6 +23,12 @@ enum
   WG_LEARN = 0, // UpdateWeights: g = fe (or e_above for Simple), rate lr, optimizer
   WG_DFA = 1    // DirectFeedbackUpdate: g = fe (holds proj), rate fl, plain accumulate
 };
+// mode of OP_FB
+enum
+{
+  FB_STATE = 0,  // UpdateState
+  FB_ADJOINT = 1 // ePC ComputeAdjoint + UpdateErrorEPC (fe holds src * f'(preact))
+};
 
 struct Tile
 {
@@ -124,7 +130,7 @@ __device__ __forceinline__ void block_energy_add(float local, double* energy)
 template <int OP>
 __global__ void __launch_bounds__(NTHREADS)
     pc_gemm_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
-                   int flags, int mode, double* energy)
+                   int flags, int mode, double* energy, const float* __restrict__ epc_src = nullptr)
 {
   const int li = first + blockIdx.z;
   const dpc_layer L = layers[li];
@@ -156,7 +162,7 @@ __global__ void __launch_bounds__(NTHREADS)
   if (OP == OP_FWD)
     A = L.z, lda = L.size, Bm = L.W, ldb = L.size;
   else if (OP == OP_FB)
-    A = simple ? Lup->e : L.fe, lda = L.next_size, Bm = L.W, ldb = L.size;
+    A = (simple && mode == FB_STATE) ? Lup->e : L.fe, lda = L.next_size, Bm = L.W, ldb = L.size;
   else
     A = (simple && mode == WG_LEARN) ? Lup->e : L.fe, lda = L.next_size,
     Bm = simple ? L.zF : L.z, ldb = L.size;
@@ -321,6 +327,20 @@ __global__ void __launch_bounds__(NTHREADS)
         if (n >= N)
           continue;
         const size_t o = (size_t)m * N + n;
+        if (mode == FB_ADJOINT)
+        {
+          // ePC: adjoint of this layer and the error update driven by it.  `flags` carries the
+          // hop scale (+1 or -1) as float bits with bit 0 replaced by the clamp flag.
+          const float scale = __int_as_float(flags & ~1);
+          const bool clamped = flags & 1;
+          float adj = (L.a * scale) * acc[i][j];
+          if (L.flags & DPC_LAYER_RESIDUAL)
+            adj += scale * epc_src[o];
+          L.adj[o] = adj;
+          if (!clamped)
+            L.e[o] = (1.0f - L.ir) * L.e[o] - L.ir * adj;
+          continue;
+        }
         float z = L.z[o];
         if (simple)
         {
@@ -521,6 +541,28 @@ __global__ void feedback_error_kernel(const dpc_layer* __restrict__ layers, int 
   for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
        o += (size_t)gridDim.x * blockDim.x)
     L.fe[o] = e_up[o] * act_deriv(L.act, L.preact[o]);
+}
+
+// ePC: fe[l] = src * f'(preact[l]) with an explicit source (terminal error or adj[l+1]).
+__global__ void epc_source_kernel(const dpc_layer* __restrict__ layers, int li, int batch,
+                                  const float* __restrict__ src)
+{
+  const dpc_layer L = layers[li];
+  const size_t total = (size_t)batch * L.next_size;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+       o += (size_t)gridDim.x * blockDim.x)
+    L.fe[o] = src[o] * act_deriv(L.act, L.preact[o]);
+}
+
+// ePC: z[l] = mu[l-1] + e[l]   (src/layers/FullPCLayer.cpp:574-582)
+__global__ void epc_reconstruct_kernel(const dpc_layer* __restrict__ layers, int li, int batch)
+{
+  const dpc_layer L = layers[li];
+  const float* mu = layers[li - 1].mu;
+  const size_t total = (size_t)batch * L.size;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+       o += (size_t)gridDim.x * blockDim.x)
+    L.z[o] = mu[o] + L.e[o];
 }
 
 // z -= ir*e for layers of the range that have no weights or no upper neighbour.

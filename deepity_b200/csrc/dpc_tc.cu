@@ -53,6 +53,7 @@ struct TcState
   bool ok = false;
   CUtensorMap z_km, z_km64, fe_km, w_km32, w_km64, w_km128, w_km256, z_mn, fe_mn, w_mn;
   int* chain_counters = nullptr; // device: [layers of the run][row blocks]
+  unsigned long long* trace = nullptr; // optional timing trace buffer of the chain kernel
   int* error_flag = nullptr; // device
   int* error_host = nullptr; // pinned
   int max_smem = 0;
@@ -1037,6 +1038,13 @@ void tc_plan_free(dpc_plan* plan)
   plan->run = TensorRun();
 }
 
+void tc_set_chain_trace(dpc_plan* plan, unsigned long long* buf)
+{
+  auto* st = static_cast<TcState*>(plan->tc);
+  if (st)
+    st->trace = buf;
+}
+
 int tc_check_error(dpc_plan* plan)
 {
   auto* st = static_cast<TcState*>(plan->tc);
@@ -1114,8 +1122,7 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   P.chain = 1;
   P.chain_counters = st->chain_counters;
   P.chain_target = (H / BNC) * 8; // column tiles x epilogue warps
-  if (const char* tp = getenv("DPC_CHAIN_TRACE_PTR"))
-    P.trace = reinterpret_cast<unsigned long long*>(strtoull(tp, nullptr, 0));
+  P.trace = st->trace;
   cudaError_t e = cudaMemsetAsync(st->chain_counters, 0, sizeof(int) * (size_t)count * (B / TBM),
                                   p->ctx->stream);
   if (e != cudaSuccess)

@@ -154,7 +154,7 @@ void PCNetwork::Compile()
   const size_t B = (size_t)batchSize;
   enum
   {
-    A_Z, A_E, A_W, A_B, A_PRE, A_MU, A_FE, A_PSI, A_ZF, A_V, A_COUNT
+    A_Z, A_E, A_W, A_B, A_PRE, A_MU, A_FE, A_PSI, A_ZF, A_V, A_ADJ, A_COUNT
   };
   size_t total[A_COUNT] = {};
   if (ghostTop)
@@ -167,6 +167,8 @@ void PCNetwork::Compile()
     total[A_E] += Pad64(B * s);
     if (useMomentum)
       total[A_V] += Pad64(B * s);
+    if (useEPC && nx > 0)
+      total[A_ADJ] += Pad64(B * s);
     if (nx > 0)
     {
       total[A_W] += Pad64(nx * s);
@@ -207,6 +209,8 @@ void PCNetwork::Compile()
     l->d.e = take(A_E, B * s);
     if (useMomentum)
       l->d.v = take(A_V, B * s);
+    if (useEPC && nx > 0)
+      l->d.adj = take(A_ADJ, B * s);
     if (nx > 0)
     {
       l->d.W = take(A_W, nx * s);
@@ -586,6 +590,29 @@ void PCNetwork::UpdateState()
   }
 }
 
+// ePC settling step, src/networks/FullPCNetwork.cpp:99-131: a forward sweep that rebuilds each
+// hidden belief from the prediction below plus its error, then a top-down sweep that chains the
+// adjoint through every layer and moves the errors.
+void PCNetwork::EPCStep()
+{
+  RequireCompiled();
+  const int n = (int)layers.size();
+  ForwardRange(0, 1, 0);
+  for (int i = 1; i + 1 < n; ++i)
+  {
+    Check(dpc_epc_reconstruct(plan, i));
+    ForwardRange(i, 1, 0);
+  }
+  Check(dpc_error(plan, n - 1, 0));
+  bool firstHop = true;
+  for (int i = n - 2; i >= 1; --i)
+  {
+    Check(dpc_epc_adjoint(plan, i, firstHop ? 1 : 0, firstHop ? -1.0f : 1.0f,
+                          layers[i]->clamped ? 1 : 0));
+    firstHop = false;
+  }
+}
+
 float PCNetwork::Step(bool computeEnergy)
 {
   double e = 0.0;
@@ -650,7 +677,10 @@ void PCNetwork::RunTrainPhases(int mode, int steps)
     CalculateTerminalError();
     for (int t = 0; t < steps; ++t)
     {
-      settle(false);
+      if (useEPC)
+        EPCStep();
+      else
+        settle(false);
       if (useIPC)
       {
         UpdateWeights();
@@ -767,8 +797,13 @@ void PCNetwork::RunPredictPhases(int steps, bool withProjection)
     ProjectForward();
   for (int t = 0; t < steps; ++t)
   {
-    CalculateState(false);
-    UpdateState();
+    if (useEPC)
+      EPCStep();
+    else
+    {
+      CalculateState(false);
+      UpdateState();
+    }
   }
   if (kind == NetworkKind::FULL && (layers.back()->d.flags & DPC_LAYER_SOFTMAX_CE))
   {
@@ -902,6 +937,14 @@ void PCNetwork::SetUseResidualConnections(bool enabled)
     throw std::logic_error("deepity_b200: SetUseResidualConnections() must precede Compile()");
   useResidual = enabled;
 }
+void PCNetwork::SetUseEPC(bool enabled)
+{
+  if (plan)
+    throw std::logic_error("deepity_b200: SetUseEPC() must precede Compile()");
+  if (kind != NetworkKind::FULL)
+    throw std::invalid_argument("deepity_b200: ePC exists for FullPCNetwork only");
+  useEPC = enabled;
+}
 void PCNetwork::SetUseIPC(bool enabled)
 {
   useIPC = enabled;
@@ -999,6 +1042,8 @@ bool PCNetwork::FindTensor(int layer, const std::string& name, float** ptr, size
     p = d.v, r = B, c = s;
   else if (name == "zF")
     p = d.zF, r = B, c = s;
+  else if (name == "adj")
+    p = d.adj, r = B, c = s;
   else if (name == "Psi" && n == 0 && d.Psi)
     p = d.Psi, r = s, c = ts, st = d.psi_stride;
   else if (name == "eT" && ghostET && layer == (int)layers.size() - 1)
@@ -1152,6 +1197,8 @@ int dpcn_set_option(dpcn_net* net, const char* name, int iv, float fv)
           n.SetUseResidualConnections(iv != 0);
         else if (nm == "ipc")
           n.SetUseIPC(iv != 0);
+        else if (nm == "epc")
+          n.SetUseEPC(iv != 0);
         else if (nm == "momentum")
           n.SetUseMomentum(iv != 0, fv);
         else if (nm == "precision")

@@ -139,6 +139,8 @@ public:
   void SetUseMuPCScaling(bool enabled);
   void SetUseResidualConnections(bool enabled);
   void SetUseIPC(bool enabled);
+  void SetUseEPC(bool enabled);
+  void EPCStep();
   void SetUseMomentum(bool enabled, float beta = 0.9f);
   void SetPrecision(int precision);
   void SetUseGraph(bool enabled);
@@ -185,7 +187,7 @@ private:
 
   OptimizerType opt = OptimizerType::SGD, optPsi = OptimizerType::SGD;
   bool centerWeights = false, crossEntropy = false, useMuPC = false, useResidual = false;
-  bool useIPC = false, useMomentum = false, useGraph = true, dirty = false;
+  bool useEPC = false, useIPC = false, useMomentum = false, useGraph = true, dirty = false;
   bool adamAllocated = false, psiAdamAllocated = false, pendingAsync = false;
   float momentumBeta = 0.9f, psiDecay = -1.0f;
   bool ghostTop = false;

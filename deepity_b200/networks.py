@@ -323,14 +323,13 @@ class FullPCN(DKPPCN):
                   use_cross_entropy: bool = False, seed: Optional[int] = None,
                   dist: str = "normal", center_weights: bool = False,
                   precision: str = "fp32") -> "FullPCN":
-        if use_epc:
-            raise NotImplementedError("FullPCN: the ePC settling mode is not built on this backend")
         self._learning_rate, self._inference_rate = learning_rate, inference_rate
         self._feedback_rate, self._lambda = feedback_rate, lmbda
         self._build_backend(learning_rate, inference_rate, feedback_rate, lmbda)
         self._option("mupc", int(use_mu_pc_scaling))
         self._option("residual", int(use_residual_connections))
         self._option("ipc", int(use_ipc))
+        self._option("epc", int(use_epc))
         self._option("momentum", int(use_momentum), momentum_beta)
         self._option("cross_entropy", int(use_cross_entropy))
         self.set_optimizer(optimizer)

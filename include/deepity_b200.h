@@ -154,6 +154,7 @@ typedef struct dpc_layer
   float* Psi;
   float* zF; /* DPC_LAYER_INPUT_ACT only: f(z) as last fed to the GEMM */
   float* v;  /* state momentum or NULL */
+  float* adj; /* ePC adjoint [B,size] or NULL (FullPCLayer::ComputeAdjoint) */
   float *m_W, *v_W, *m_b, *v_b, *m_Psi, *v_Psi; /* Adam moments or NULL */
   int32_t *t, *t_Psi;                           /* Adam step counters on the device or NULL */
 } dpc_layer;
@@ -172,6 +173,10 @@ DPC_API int dpc_plan_destroy(dpc_plan* plan);
  * copy of the neighbour rank's first layer points this at the buffer that receives the
  * broadcast terminal error [batch, terminal_size]. */
 DPC_API int dpc_plan_set_terminal_error(dpc_plan* plan, const float* e_terminal_dev);
+/* Profiling aid: a device buffer of 256*8 uint64 in which CTA 0 of the forward-sweep kernel
+ * records globaltimer stamps per layer (dependency seen, first operands landed, accumulator
+ * complete, stores issued, published, ...).  NULL switches it off (default). */
+DPC_API int dpc_plan_set_chain_trace(dpc_plan* plan, void* trace_dev);
 /* Layers [first, first+count) that the tensor-core path covers (0 if none). */
 DPC_API int dpc_plan_tensor_run(dpc_plan* plan, int* first, int* count);
 
@@ -217,6 +222,15 @@ DPC_API int dpc_feedback_error(dpc_plan* plan, int first, int count);
  * (DirectKPPCLayer.cpp:318-359, FullPCLayer.cpp:300-380, SimplePCLayer.cpp:185-257).
  * Layers listed as clamped by the caller must simply be left out of the range. */
 DPC_API int dpc_update_state(dpc_plan* plan, int first, int count);
+/* ePC settling (FullPCNetwork::EPCStep, src/networks/FullPCNetwork.cpp:99-131):
+ * dpc_epc_reconstruct: z[l] = mu[l-1] + e[l]  (FullPCLayer::ReconstructBelief);
+ * dpc_epc_adjoint: adj[l] = a*scale*((src * f'(preact[l]))·W[l]) (+ scale*src with residual),
+ * then e[l] = (1-ir)*e[l] - ir*adj[l] unless `clamped` (ComputeAdjoint + UpdateErrorEPC,
+ * src/layers/FullPCLayer.cpp:584-640).  src is the terminal error (from_terminal != 0,
+ * scale -1 on that first hop) or adj[l+1]. */
+DPC_API int dpc_epc_reconstruct(dpc_plan* plan, int layer);
+DPC_API int dpc_epc_adjoint(dpc_plan* plan, int layer, int from_terminal, float scale,
+                            int clamped);
 /* z -= ir*e for one layer (the "output layer" branch of UpdateState). */
 DPC_API int dpc_relax(dpc_plan* plan, int layer);
 /* DirectFeedbackUpdate for every layer of the range whose upper neighbour has Psi:
@@ -263,7 +277,7 @@ DPC_API int dpcn_add_layer(dpcn_net* net, int size, int next_size, int terminal_
 /* Options by name, before or after compile as the reference allows: "optimizer",
  * "psi_optimizer" (ivalue = dpc_opt), "center_weights", "psi_decay" (fvalue),
  * "learning_rate", "feedback_rate", "inference_rate" (fvalue), "cross_entropy", "mupc",
- * "residual", "ipc", "momentum" (ivalue on/off, fvalue beta), "precision" (dpc_precision), "ghost_top" (before
+ * "residual", "ipc", "epc", "momentum" (ivalue on/off, fvalue beta), "precision" (dpc_precision), "ghost_top" (before
  * compile: the last layer is a copy of a neighbour rank's layer, see deepity_b200/sharded.py),
  * "use_graph" (capture the step into a CUDA graph, default on). */
 DPC_API int dpcn_set_option(dpcn_net* net, const char* name, int ivalue, float fvalue);

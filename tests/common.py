@@ -70,7 +70,7 @@ def state_names(kind):
 def _oracle_kwargs(case):
     kw = dict(case["hyper"])
     for k, v in case.get("options", {}).items():
-        kw[k] = bool(v) if k in ("center_weights", "cross_entropy", "mupc", "residual", "ipc") else v
+        kw[k] = bool(v) if k in ("center_weights", "cross_entropy", "mupc", "residual", "ipc", "epc") else v
     return kw
 
 
@@ -124,7 +124,7 @@ def build_gpu_net(case, precision="fp32", use_graph=True):
     if kind == "full":
         kw.update(use_mu_pc_scaling=bool(opts.get("mupc", 0)),
                   use_residual_connections=bool(opts.get("residual", 0)),
-                  use_ipc=bool(opts.get("ipc", 0)), use_momentum="momentum" in opts,
+                  use_ipc=bool(opts.get("ipc", 0)), use_epc=bool(opts.get("epc", 0)), use_momentum="momentum" in opts,
                   momentum_beta=opts.get("momentum", 0.9),
                   use_cross_entropy=bool(opts.get("cross_entropy", 0)))
     if kind == "simple":

@@ -61,6 +61,12 @@ EXTRA = {
                            options=dict(cross_entropy=1)),
     "full_plain": dict(kind="full", sizes=[30, 40, 40, 10], batch=16, T=4, steps=3,
                        hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="gelu")),
+    "full_epc_residual": dict(kind="full", sizes=[30, 40, 40, 40, 10], batch=16, T=4, steps=3,
+                              hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="tanh"),
+                              options=dict(epc=1, residual=1)),
+    "full_epc_ce": dict(kind="full", sizes=[30, 40, 40, 10], batch=16, T=3, steps=2,
+                        hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="gelu"),
+                        options=dict(epc=1, cross_entropy=1)),
     "full_adamw": dict(kind="full", sizes=[33, 40, 40, 10], batch=24, T=3, steps=3,
                        hyper=dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.01, act="tanh"),
                        options=dict(optimizer="ADAMW", psi_optimizer="ADAMW")),
