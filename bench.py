@@ -258,7 +258,11 @@ def main():
 
     if world > 1:
         from deepity_b200 import sharded
-        sharded.bench_main(args, w, sizes, config)
+        # deep stacks shard by layers; wide, shallow networks by batch rows
+        if w["kind"] == "dkp" and len(sizes) - 1 >= world:
+            sharded.bench_main(args, w, sizes, config)
+        else:
+            sharded.batch_bench_main(args, w, sizes, config)
         return
 
     torch.cuda.set_device(0)

@@ -57,6 +57,8 @@ SIGNATURES = {
     "dpc_relax": (_i, [_vp, _i]),
     "dpc_direct_feedback": (_i, [_vp, _i, _i, _i]),
     "dpc_update_weights": (_i, [_vp, _i, _i, _i]),
+    "dpc_weight_gradients": (_i, [_vp, _i, _i, _i]),
+    "dpc_apply_gradients": (_i, [_vp, _i, _i, _i, _i, _i]),
     "dpc_error_energy_static": (_i, [_vp, _vp, _vp, _vp, _i64, _vp]),
     "dpc_energy_reset": (_i, [_vp]),
     "dpc_energy_read": (_i, [_vp, ctypes.POINTER(ctypes.c_double)]),
@@ -78,6 +80,7 @@ SIGNATURES = {
     "dpcn_reset_state": (_i, [_vp]),
     "dpcn_context": (_vp, [_vp]),
     "dpcn_plan": (_vp, [_vp]),
+    "dpcn_set_gradient_sync": (_i, [_vp, _vp, _vp, _i]),
     "dpcn_launch_count": (_i64, [_vp]),
     "dpcn_train_step_flops": (ctypes.c_double, [_vp, _i]),
 }

@@ -794,17 +794,136 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
   {
     const int c = std::min(kMaxZ, first + count - f);
     dim3 gb(std::max(1, cdiv(max_next, 128)), c);
-    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch);
+    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch, 0);
     if ((rc = check_launch(p->ctx, "bias_update kernel")) != DPC_OK)
       return rc;
     if (any_psi)
     {
       dim3 gp(std::max(1, cdiv(max_size, 128)), c);
-      psi_update_kernel<<<gp, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal);
+      psi_update_kernel<<<gp, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, 0);
       if ((rc = check_launch(p->ctx, "psi_update kernel")) != DPC_OK)
         return rc;
     }
     if (center_rows)
+    {
+      dim3 gc(std::min(max_next, 1024), c);
+      center_rows_kernel<<<gc, 256, 0, st>>>(p->d, f, p->n);
+      if ((rc = check_launch(p->ctx, "center_rows kernel")) != DPC_OK)
+        return rc;
+    }
+  }
+  return DPC_OK;
+}
+
+static int staging_ready(dpc_plan* p, int first, int count, int which)
+{
+  for (int i = first; i < first + count; ++i)
+  {
+    const dpc_layer& L = p->h[i];
+    if (L.next_size <= 0)
+      continue;
+    if (!L.g_W || (which == 0 && (!L.g_b || (L.Psi && !(L.flags & DPC_LAYER_INPUT_ACT) && !L.g_Psi))))
+      return fail(DPC_ERR_INVALID, "layer has no gradient staging buffers");
+  }
+  return DPC_OK;
+}
+
+int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK || count == 0)
+    return rc;
+  if (which != 0 && which != 1)
+    return fail(DPC_ERR_INVALID, "which must be 0 (learn) or 1 (direct feedback)");
+  if (first + count == p->n)
+    count -= 1;
+  if (count <= 0)
+    return DPC_OK;
+  if ((rc = staging_ready(p, first, count, which)) != DPC_OK)
+    return rc;
+  cudaStream_t st = p->ctx->stream;
+  if (which == 1)
+  {
+    for (int f = first; f < first + count; f += kMaxZ)
+    {
+      const int c = std::min(kMaxZ, first + count - f);
+      int mxn = 1;
+      for (int i = f; i < f + c; ++i)
+        mxn = std::max(mxn, p->h[i].next_size);
+      dim3 grid(cdiv(mxn, 128), cdiv(p->batch, DFA_ROWS), c);
+      dfa_proj_kernel<<<grid, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal);
+      if ((rc = check_launch(p->ctx, "dfa_proj kernel")) != DPC_OK)
+        return rc;
+    }
+    return weight_gemm_simt(p, first, count, WG_DFA | WG_GRAD_ONLY, 0);
+  }
+  if ((rc = weight_gemm_simt(p, first, count, WG_LEARN | WG_GRAD_ONLY, 0)) != DPC_OK)
+    return rc;
+  bool any_psi = false;
+  int max_next = 0, max_size = 0;
+  for (int i = first; i < first + count; ++i)
+  {
+    const dpc_layer& L = p->h[i];
+    any_psi |= L.Psi != nullptr && !(L.flags & DPC_LAYER_INPUT_ACT);
+    max_next = std::max(max_next, L.next_size);
+    max_size = std::max(max_size, L.size);
+  }
+  for (int f = first; f < first + count; f += kMaxZ)
+  {
+    const int c = std::min(kMaxZ, first + count - f);
+    dim3 gb(std::max(1, cdiv(max_next, 128)), c);
+    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch, 1);
+    if ((rc = check_launch(p->ctx, "bias gradient kernel")) != DPC_OK)
+      return rc;
+    if (any_psi)
+    {
+      dim3 gp(std::max(1, cdiv(max_size, 128)), c);
+      psi_update_kernel<<<gp, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, 1);
+      if ((rc = check_launch(p->ctx, "psi gradient kernel")) != DPC_OK)
+        return rc;
+    }
+  }
+  return DPC_OK;
+}
+
+int dpc_apply_gradients(dpc_plan* p, int first, int count, int which, int global_batch, int option)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK || count == 0)
+    return rc;
+  if ((which != 0 && which != 1) || global_batch <= 0)
+    return fail(DPC_ERR_INVALID, "bad which / global_batch");
+  if (first + count == p->n)
+    count -= 1;
+  if (count <= 0)
+    return DPC_OK;
+  if ((rc = staging_ready(p, first, count, which)) != DPC_OK)
+    return rc;
+  cudaStream_t st = p->ctx->stream;
+  bool any_adam = false;
+  int max_next = 0;
+  size_t max_w = 1;
+  for (int i = first; i < first + count; ++i)
+  {
+    const dpc_layer& L = p->h[i];
+    any_adam |= L.opt != DPC_OPT_SGD || (L.Psi && L.opt_psi != DPC_OPT_SGD);
+    max_next = std::max(max_next, L.next_size);
+    max_w = std::max(max_w, (size_t)std::max(L.next_size, 0) * L.size);
+  }
+  if (which == 0 && any_adam)
+  {
+    bump_counters_kernel<<<cdiv(count, 256), 256, 0, st>>>(p->d, first, count, p->n);
+    if ((rc = check_launch(p->ctx, "bump_counters kernel")) != DPC_OK)
+      return rc;
+  }
+  for (int f = first; f < first + count; f += kMaxZ)
+  {
+    const int c = std::min(kMaxZ, first + count - f);
+    dim3 grid(elem_blocks(p, max_w), c);
+    apply_gradients_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, global_batch, which, option ? 1 : 0);
+    if ((rc = check_launch(p->ctx, "apply_gradients kernel")) != DPC_OK)
+      return rc;
+    if (which == 0 && option)
     {
       dim3 gc(std::min(max_next, 1024), c);
       center_rows_kernel<<<gc, 256, 0, st>>>(p->d, f, p->n);

@@ -21,7 +21,10 @@ enum GemmOp
 enum
 {
   WG_LEARN = 0, // UpdateWeights: g = fe (or e_above for Simple), rate lr, optimizer
-  WG_DFA = 1    // DirectFeedbackUpdate: g = fe (holds proj), rate fl, plain accumulate
+  WG_DFA = 1,   // DirectFeedbackUpdate: g = fe (holds proj), rate fl, plain accumulate
+  // or-ed in: only store the raw sum g^T zin in the layer's gradient staging buffer g_W; the
+  // update is applied later by apply_gradients_kernel (after a sum over batch shards)
+  WG_GRAD_ONLY = 2
 };
 // mode of OP_FB
 enum
@@ -148,6 +151,9 @@ __global__ void __launch_bounds__(NTHREADS)
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   if (m0 >= M || n0 >= N)
     return;
+  const bool wg_stage = OP == OP_WG && (mode & WG_GRAD_ONLY);
+  if (OP == OP_WG)
+    mode &= ~WG_GRAD_ONLY;
   if (OP == OP_WG && mode == WG_DFA)
   {
     // DirectFeedbackUpdate is a no-op unless the layer above owns feedback weights.
@@ -366,6 +372,22 @@ __global__ void __launch_bounds__(NTHREADS)
   }
   else
   {
+    if (wg_stage)
+    {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+      {
+        const int m = m0 + ty * 4 + i;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+          const int n = n0 + tx * 4 + j;
+          if (m < M && n < N)
+            L.g_W[(size_t)m * N + n] = acc[i][j];
+        }
+      }
+      return;
+    }
     const float Bf = (float)batch;
     const bool adam = (mode == WG_LEARN) && (L.opt != DPC_OPT_SGD);
     float alpha, decay = 1.0f, step = 0.0f, lr_wd = -1.0f;
@@ -663,7 +685,7 @@ __global__ void bump_counters_kernel(const dpc_layer* __restrict__ layers, int f
 // Bias update from the column sums of the local gradient: one thread per output unit,
 // summing the batch in row order like CPUBackend::SumRows (CPUBackend.cpp:243-248).
 __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
-                                   int batch)
+                                   int batch, int grad_only)
 {
   const int li = first + blockIdx.y;
   if (li + 1 >= n_layers)
@@ -679,7 +701,9 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
     float s = 0.0f;
     for (int b = 0; b < batch; ++b)
       s += g[(size_t)b * n + j];
-    if (L.opt == DPC_OPT_SGD)
+    if (grad_only)
+      L.g_b[j] = s;
+    else if (L.opt == DPC_OPT_SGD)
       L.b[j] += (L.lr / (float)batch) * s;
     else
     {
@@ -694,7 +718,7 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
 // Feedback-weight update Psi[l] (+)= (fl*a/B) z[l]^T e_T, one thread per row of Psi with the
 // terminal columns in registers (chunks of 16).
 __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
-                                  int batch, const float* __restrict__ eT)
+                                  int batch, const float* __restrict__ eT, int grad_only)
 {
   const int li = first + blockIdx.y;
   if (li + 1 >= n_layers)
@@ -750,7 +774,15 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
       if (i >= s)
         continue;
       float* prow = L.Psi + (size_t)i * L.psi_stride + kc;
-      if (L.opt_psi == DPC_OPT_SGD)
+      if (grad_only)
+      {
+        float* grow = L.g_Psi + (size_t)i * L.psi_stride + kc;
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if (k < kn)
+            grow[k] = acc[k];
+      }
+      else if (L.opt_psi == DPC_OPT_SGD)
       {
         const float decay = (!full_kind && L.psi_decay > 0.0f) ? 1.0f - L.psi_decay : 1.0f;
         const float alpha = rate / (float)batch;
@@ -782,6 +814,109 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
             vrow[k] = v;
           }
       }
+    }
+  }
+}
+
+// Applies staged gradients (the raw sums that the WG_GRAD_ONLY weight kernel and the grad_only
+// bias / Psi kernels left in g_W, g_b, g_Psi, possibly summed over batch shards since) with
+// exactly the formulas of the fused updates above; `batch` is the batch the sums cover (the
+// global one).  which = WG_LEARN: W, b and Psi; WG_DFA: W only (DirectFeedbackUpdate).
+__global__ void apply_gradients_kernel(const dpc_layer* __restrict__ layers, int first,
+                                       int n_layers, int batch, int which, int flags)
+{
+  const int li = first + blockIdx.y;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0)
+    return;
+  const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+  const float Bf = (float)batch;
+  const size_t nW = (size_t)L.next_size * L.size;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t nthr = (size_t)gridDim.x * blockDim.x;
+  if (which == WG_DFA)
+  {
+    if (layers[li + 1].Psi == nullptr)
+      return;
+    const float alpha = L.fl * L.a / Bf;
+    const float decay = ((flags & 1) && L.lmbda > 0.0f && L.fl != 0.0f) ? 1.0f - L.lmbda : 1.0f;
+    for (size_t o = tid; o < nW; o += nthr)
+    {
+      float w = L.W[o];
+      if (decay != 1.0f)
+        w *= decay;
+      L.W[o] = fmaf(alpha, L.g_W[o], w);
+    }
+    return;
+  }
+  if (L.opt == DPC_OPT_SGD)
+  {
+    const float alpha = simple ? (L.lr / Bf) : (L.a * L.lr / Bf);
+    const float decay = L.lmbda > 0.0f ? 1.0f - L.lmbda : 1.0f;
+    for (size_t o = tid; o < nW; o += nthr)
+    {
+      float w = L.W[o];
+      if (decay != 1.0f)
+        w *= decay;
+      L.W[o] = fmaf(alpha, L.g_W[o], w);
+    }
+    for (size_t j = tid; j < (size_t)L.next_size; j += nthr)
+      L.b[j] += (L.lr / Bf) * L.g_b[j];
+  }
+  else
+  {
+    const float step = adam_step_size(L.lr, *L.t);
+    const float lr_wd = L.opt == DPC_OPT_ADAMW ? L.lr * L.lmbda : -1.0f;
+    const float alpha = -1.0f * L.a;
+    for (size_t o = tid; o < nW; o += nthr)
+    {
+      float mm = L.m_W[o], vv = L.v_W[o];
+      L.W[o] = adam_update(L.W[o], alpha * L.g_W[o], mm, vv, step, lr_wd);
+      L.m_W[o] = mm;
+      L.v_W[o] = vv;
+    }
+    for (size_t j = tid; j < (size_t)L.next_size; j += nthr)
+    {
+      float m = L.m_b[j], v = L.v_b[j];
+      L.b[j] = adam_update(L.b[j], -L.g_b[j], m, v, step, -1.0f);
+      L.m_b[j] = m;
+      L.v_b[j] = v;
+    }
+  }
+  if (L.Psi == nullptr || simple)
+    return;
+  const bool full_kind = (L.flags & DPC_LAYER_FULLPC_PSI) != 0;
+  const float rate = full_kind ? L.fl * L.a : L.fl;
+  const int TS = L.terminal_size;
+  const size_t nP = (size_t)L.size * TS;
+  if (L.opt_psi == DPC_OPT_SGD)
+  {
+    const float decay = (!full_kind && L.psi_decay > 0.0f) ? 1.0f - L.psi_decay : 1.0f;
+    const float alpha = rate / Bf;
+    for (size_t q = tid; q < nP; q += nthr)
+    {
+      const size_t o = (q / TS) * L.psi_stride + q % TS;
+      float p = L.Psi[o];
+      if (decay != 1.0f)
+        p *= decay;
+      L.Psi[o] = fmaf(alpha, L.g_Psi[o], p);
+    }
+  }
+  else
+  {
+    const float step = adam_step_size(rate, *L.t_Psi);
+    float lr_wd = -1.0f;
+    if (L.opt_psi == DPC_OPT_ADAMW)
+      lr_wd = rate * ((!full_kind && L.psi_decay >= 0.0f) ? L.psi_decay : L.lmbda);
+    for (size_t q = tid; q < nP; q += nthr)
+    {
+      const size_t o = (q / TS) * L.psi_stride + q % TS;
+      float m = L.m_Psi[o], v = L.v_Psi[o];
+      L.Psi[o] = adam_update(L.Psi[o], -L.g_Psi[o], m, v, step, lr_wd);
+      L.m_Psi[o] = m;
+      L.v_Psi[o] = v;
     }
   }
 }

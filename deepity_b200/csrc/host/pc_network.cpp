@@ -242,6 +242,7 @@ void PCNetwork::Compile()
   pinnedOut = static_cast<float*>(p);
 
   EnsureOptimizerState();
+  EnsureGradientStaging();
   std::vector<dpc_layer> table;
   for (auto& l : layers)
     table.push_back(l->d);
@@ -308,6 +309,58 @@ void PCNetwork::EnsureOptimizerState()
   }
 }
 
+void PCNetwork::EnsureGradientStaging()
+{
+  if (!gradSync || gradBuffer)
+    return;
+  size_t tw = 0, tb = 0, tp = 0;
+  for (auto& l : layers)
+    if (l->d.next_size > 0)
+    {
+      tw += Pad64((size_t)l->d.next_size * l->d.size);
+      tb += Pad64(l->d.next_size);
+      if (l->d.Psi)
+        tp += Pad64((size_t)l->d.size * l->d.psi_stride);
+    }
+  void* p = nullptr;
+  gradCount = tw + tb + tp;
+  gradWCount = tw;
+  Check(dpc_alloc(ctx, gradCount * sizeof(float), &p));
+  allocations.push_back(p);
+  Check(dpc_zero(ctx, p, gradCount * sizeof(float)));
+  gradBuffer = static_cast<float*>(p);
+  size_t ow = 0, ob = tw, op = tw + tb;
+  for (auto& l : layers)
+    if (l->d.next_size > 0)
+    {
+      l->d.g_W = gradBuffer + ow;
+      l->d.g_b = gradBuffer + ob;
+      ow += Pad64((size_t)l->d.next_size * l->d.size);
+      ob += Pad64(l->d.next_size);
+      if (l->d.Psi)
+      {
+        l->d.g_Psi = gradBuffer + op;
+        op += Pad64((size_t)l->d.size * l->d.psi_stride);
+      }
+    }
+}
+
+void PCNetwork::SetGradientSync(GradientSyncFn sync, void* user, int global)
+{
+  if (sync && (global < batchSize || global % batchSize != 0))
+    throw std::invalid_argument("deepity_b200: global batch must be a multiple of the local batch");
+  gradSync = sync;
+  gradUser = user;
+  globalBatch = sync ? global : 0;
+  Dirty();
+}
+
+void PCNetwork::SyncGradients(size_t count)
+{
+  if (gradSync(gradUser, gradBuffer, (int64_t)count, dpc_stream(ctx)) != 0)
+    throw std::runtime_error("deepity_b200: the gradient sync function reported a failure");
+}
+
 void PCNetwork::Dirty()
 {
   dirty = true;
@@ -318,6 +371,7 @@ void PCNetwork::SyncPlan()
   if (!dirty || !plan)
     return;
   EnsureOptimizerState();
+  EnsureGradientStaging();
   std::vector<dpc_layer> table;
   for (auto& l : layers)
     table.push_back(l->d);
@@ -467,13 +521,19 @@ void PCNetwork::ForwardRange(int first, int count, int flags)
       ++i;
       continue;
     }
+    if (l->clamped)
+    {
+      // This pass fills the clamped layer's cache (first use in a step, or after iPC
+      // invalidated it): its preact/mu must reach memory whatever the caller elides.
+      Check(dpc_forward(plan, i, 1, flags & ~(DPC_FWD_TRANSIENT | DPC_FWD_NO_MU)));
+      l->cacheValid = true;
+      ++i;
+      continue;
+    }
     int j = i;
-    while (j < end && layers[j]->d.next_size > 0 && !(layers[j]->clamped && layers[j]->cacheValid))
+    while (j < end && layers[j]->d.next_size > 0 && !layers[j]->clamped)
       ++j;
     Check(dpc_forward(plan, i, j - i, flags));
-    for (int k = i; k < j; ++k)
-      if (layers[k]->clamped)
-        layers[k]->cacheValid = true;
     i = j;
   }
 }
@@ -522,10 +582,16 @@ void PCNetwork::DirectFeedbackUpdate()
   {
     // Refresh preact against the settled z first (src/networks/FullPCNetwork.cpp:72-82).
     ForwardRange(0, n - 1, 0);
-    Check(dpc_direct_feedback(plan, 0, n - 1, 1));
+  }
+  const int decayW = kind == NetworkKind::FULL ? 1 : 0;
+  if (gradSync)
+  {
+    Check(dpc_weight_gradients(plan, 0, n - 1, 1));
+    SyncGradients(gradWCount);
+    Check(dpc_apply_gradients(plan, 0, n - 1, 1, globalBatch, decayW));
   }
   else
-    Check(dpc_direct_feedback(plan, 0, n - 1, 0));
+    Check(dpc_direct_feedback(plan, 0, n - 1, decayW));
 }
 
 // CalculateState for every layer, in the reference's order: each layer's error uses the
@@ -636,7 +702,14 @@ void PCNetwork::UpdateWeights()
     // gradient fe = e_above * f'(preact) (src/networks/DirectKPPCNetwork.cpp:481-495).
     ForwardRange(0, n - 1, DPC_FWD_FE | transientFlag);
   }
-  Check(dpc_update_weights(plan, 0, n - 1, centerWeights ? 1 : 0));
+  if (gradSync)
+  {
+    Check(dpc_weight_gradients(plan, 0, n - 1, 0));
+    SyncGradients(gradCount);
+    Check(dpc_apply_gradients(plan, 0, n - 1, 0, globalBatch, centerWeights ? 1 : 0));
+  }
+  else
+    Check(dpc_update_weights(plan, 0, n - 1, centerWeights ? 1 : 0));
 }
 
 // Inside a whole train step the predictions of the settling passes and of the pre-update
@@ -745,7 +818,7 @@ float PCNetwork::TrainStepRaw(int mode, const float* x, size_t nx, const float* 
   for (int i = 1; i + 1 < n; ++i)
     layers[i]->clamped = false;
 
-  if (useGraph)
+  if (useGraph && !gradSync)
   {
     const long key = (long)mode * 1000000L + steps;
     if (graphKey[0] != key)
@@ -1375,6 +1448,13 @@ dpc_plan* dpcn_plan(dpcn_net* net)
     return nullptr;
   net->net->FlushSettings();
   return net->net->Plan();
+}
+
+int dpcn_set_gradient_sync(dpcn_net* net, dpcn_sync_fn sync, void* user, int global_batch)
+{
+  if (!net)
+    return DPC_ERR_INVALID;
+  return Guard([&] { net->net->SetGradientSync(sync, user, global_batch); });
 }
 
 int64_t dpcn_launch_count(dpcn_net* net)

@@ -148,6 +148,18 @@ public:
   // weights here but carries that layer's Psi); the terminal error arrives by broadcast.
   void SetGhostTop(bool enabled);
   float* TerminalErrorBuffer() noexcept { return ghostET; }
+  // Batch sharding: this network holds batchSize of globalBatch rows; every weight-shaped
+  // update is split into "stage raw gradient sums", a call of `sync` (which sums `count`
+  // floats at `dev` over the shards, ordered on `stream`) and "apply with globalBatch".
+  // sync == nullptr returns to the fused updates.  Steps are not captured into a graph
+  // while a sync function is set.
+  using GradientSyncFn = int (*)(void* user, float* dev, int64_t count, void* stream);
+  void SetGradientSync(GradientSyncFn sync, void* user, int globalBatch);
+  float* GradientBuffer(size_t* count) noexcept
+  {
+    *count = gradCount;
+    return gradBuffer;
+  }
 
   std::vector<std::unique_ptr<PCLayer>>& GetLayers() noexcept { return layers; }
   PCLayer* GetTerminalLayer() noexcept { return layers.back().get(); }
@@ -171,6 +183,8 @@ private:
   void Dirty(); // hyper-parameters changed: re-upload the plan, drop captured graphs
   void SyncPlan();
   void EnsureOptimizerState();
+  void EnsureGradientStaging();
+  void SyncGradients(size_t count);
   void ForwardRange(int first, int count, int flags);
   void RunTrainPhases(int mode, int steps);
   void RunPredictPhases(int steps, bool withProjection);
@@ -192,6 +206,11 @@ private:
   float momentumBeta = 0.9f, psiDecay = -1.0f;
   bool ghostTop = false;
   float* ghostET = nullptr;
+  GradientSyncFn gradSync = nullptr;
+  void* gradUser = nullptr;
+  int globalBatch = 0;
+  float* gradBuffer = nullptr; // [g_W of every layer | g_b | g_Psi], each padded to 64 floats
+  size_t gradCount = 0, gradWCount = 0;
   int transientFlag = 0; // DPC_FWD_TRANSIENT while a whole train step is being issued
   // key of the graph captured in slot s: mode*1e6+steps (train) or steps (predict); -1 none
   long graphKey[4] = {-1, -1, -1, -1};

@@ -94,6 +94,7 @@ class _Network:
             raise ValueError(f"{self.NAME}: device {device!r} is not supported; this build runs on "
                              "CUDA devices only (no CPU backend)")
         self._lib = _lib.load()
+        self._device_index = dev
         _lib.check(self._lib.dpcn_create(self.KIND, self.batch_size, dev, ctypes.byref(self._h)))
         self.layers: list[LayerView] = []
 
@@ -268,6 +269,39 @@ class _Network:
             if verbose:
                 print(f"epoch {epoch + 1} avg energy = {total / (n // bsz):.4f}")
         return self
+
+    def set_gradient_sync(self, reduce_fn, global_batch: int) -> None:
+        """Batch sharding: this network holds ``batch_size`` of ``global_batch`` rows.
+        ``reduce_fn(t)`` gets a CUDA torch view of the staged gradient sums and must sum it in
+        place over all shards (``torch.distributed.all_reduce``); it runs with the library's
+        stream current.  ``None`` switches back to the fused single-process updates."""
+        self._require_configured()
+        if reduce_fn is None:
+            _lib.check(self._lib.dpcn_set_gradient_sync(self._h, None, None, 0))
+            self._sync_cb = None
+            return
+        import torch
+        lib = self._lib
+        device = torch.device("cuda", self._device_index)
+
+        def trampoline(user, dev, count, stream):
+            try:
+                class _View:
+                    __cuda_array_interface__ = {"shape": (int(count),), "typestr": "<f4",
+                                                "data": (int(dev), False), "version": 3}
+                t = torch.as_tensor(_View(), device=device)
+                with torch.cuda.stream(torch.cuda.ExternalStream(int(stream), device=device)):
+                    reduce_fn(t)
+                return 0
+            except Exception as exc:  # noqa: BLE001 - reported through the status code
+                self._sync_error = exc
+                return 1
+
+        proto = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                 ctypes.c_void_p)
+        self._sync_cb = proto(trampoline)  # keep the thunk alive as long as it is installed
+        _lib.check(lib.dpcn_set_gradient_sync(self._h, ctypes.cast(self._sync_cb, ctypes.c_void_p),
+                                              None, int(global_batch)))
 
     @property
     def launch_count(self) -> int:

@@ -289,6 +289,65 @@ class ShardedDKPPCN:
 
 
 # ------------------------------------------------------------------------------------------
+class BatchSharded:
+    """Wide, shallow networks split over the ranks by batch rows.
+
+    Every rank holds the full W, b, Psi (and optimizer moments) and ``global_batch / world``
+    rows of every belief, error and prediction.  Settling, the softmax head and momentum are
+    row-local and need no communication; only the weight-shaped sums couple rows:
+
+        direct-feedback update   one all-reduce of the staged  proj^T z  of all layers
+        learn                    one all-reduce of the staged  fe^T z, column sums of fe and
+                                 z^T e_T  of all layers (a single contiguous buffer)
+        energy                   one all-reduce of a scalar
+
+    The sums are raw (no 1/B, no learning rate), so SGD, Adam and AdamW all apply them with
+    the global batch exactly as a single process would; iPC mode all-reduces in every
+    settling step because it learns in every step.  ``build_local(local_batch)`` returns the
+    rank's network: a configured deepity_b200 network, or anything with the same
+    ``set_gradient_sync(reduce_fn, global_batch)`` / ``train_step`` pair (the CPU tests use
+    the numpy oracle).  Parameters must be set identically on every rank.
+    """
+
+    def __init__(self, build_local, global_batch: int, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if global_batch % self.world != 0:
+            raise ValueError(f"global batch {global_batch} does not split over {self.world} ranks")
+        self.global_batch, self.local_batch = global_batch, global_batch // self.world
+        self.net = build_local(self.local_batch)
+        self.net.set_gradient_sync(self._reduce, global_batch)
+
+    def _reduce(self, t):
+        if self.world > 1:
+            self.dist.all_reduce(t, group=self.group)
+
+    def rows(self, a):
+        """This rank's rows of a [global_batch, ...] array."""
+        return a[self.rank * self.local_batch:(self.rank + 1) * self.local_batch]
+
+    def _energy(self, local):
+        import torch
+        if self.world == 1 or local is None:
+            return local
+        t = torch.tensor([local], dtype=torch.float64)
+        if self.dist.get_backend(self.group) == "nccl":
+            t = t.cuda()
+        self.dist.all_reduce(t, group=self.group)
+        return float(t.item())
+
+    def train_step(self, X, Y, inference_steps: int = 1) -> float:
+        """X, Y: the GLOBAL batch on the host; every rank takes its rows."""
+        return self._energy(self.net.train_step(self.rows(X), self.rows(Y), inference_steps))
+
+    def train_step_device(self, x_local, y_local, inference_steps: int = 1, read_energy=True):
+        """x_local, y_local: this rank's rows, already on its GPU."""
+        return self._energy(self.net.train_step_device(x_local, y_local, inference_steps,
+                                                       read_energy))
+
+
+# ------------------------------------------------------------------------------------------
 def bench_main(args, w, sizes, config):
     """The N>1 arm of bench.py: layer-sharded C3, strong scaling (the same network and batch
     at every N), timed on the device with CUDA events, max over ranks."""
@@ -358,6 +417,81 @@ def bench_main(args, w, sizes, config):
                 "frac_of_gemm_peak_step": flops / (ms * 1e-3) / 1e12 / peak,
                 "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8},
+                "gpu_launches": int(lc.item()), "clocks": clk.summary(),
+                "roofline": None, "cpu_baseline": None}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def batch_bench_main(args, w, sizes, config):
+    """The N>1 arm of bench.py for the wide, shallow workloads: batch-sharded, strong scaling
+    (the same network and GLOBAL batch at every N), CUDA events on the library's stream, max
+    over ranks."""
+    import json
+
+    import torch
+    import torch.distributed as dist
+
+    from bench import ClockSampler, build_net, synth
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    x, y, params = synth(w, sizes)
+    T, B = w["T"], w["batch"]
+
+    def build(local_batch):
+        net = build_net(dict(w, batch=local_batch), sizes, args.precision)
+        for l, p in enumerate(params):
+            for nm, v in p.items():
+                net.set_tensor(l, nm, v)
+        return net
+    net = BatchSharded(build, B)
+    lib = net.net._lib
+    stream = torch.cuda.ExternalStream(lib.dpc_stream(lib.dpcn_context(net.net._h)))
+    xd = torch.from_numpy(np.ascontiguousarray(net.rows(x))).cuda()
+    yd = torch.from_numpy(np.ascontiguousarray(net.rows(y))).cuda()
+    for _ in range(args.warmup):
+        energy = net.train_step_device(xd, yd, T)
+
+    def timed(fn, steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            fn()
+        b.record(stream)
+        b.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b) / steps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    with ClockSampler(local) as clk:
+        n0 = net.net.launch_count
+        ms = timed(lambda: net.train_step_device(xd, yd, T, read_energy=False), args.steps)
+        launches = net.net.launch_count - n0
+        energy = net.train_step_device(xd, yd, T)
+        e2e_ms = timed(lambda: net.train_step(x, y, T), args.steps)
+    lc = torch.tensor([launches], device="cuda", dtype=torch.int64)
+    dist.all_reduce(lc)
+    if rank == 0:
+        from bench import algorithmic_flops
+        flops = algorithmic_flops(w["kind"], sizes, B, T)
+        config = dict(config, parallelism=f"batch-sharded x{world}", rows_per_rank=B // world)
+        line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
+                "config": config, "energy": energy, "algorithmic_flops_per_step": flops,
+                "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
+                "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": int((x.nbytes + y.nbytes) // world),
+                        "d2h_bytes_per_step": 8},
                 "gpu_launches": int(lc.item()), "clocks": clk.summary(),
                 "roofline": None, "cpu_baseline": None}
         print(json.dumps(line))

@@ -157,6 +157,10 @@ typedef struct dpc_layer
   float* adj; /* ePC adjoint [B,size] or NULL (FullPCLayer::ComputeAdjoint) */
   float *m_W, *v_W, *m_b, *v_b, *m_Psi, *v_Psi; /* Adam moments or NULL */
   int32_t *t, *t_Psi;                           /* Adam step counters on the device or NULL */
+  /* Gradient staging (batch-sharded training) or NULL: raw sums fe^T z [next,size],
+   * column sums of fe [next] and z^T e_T [size,psi_stride], written by
+   * dpc_weight_gradients and consumed by dpc_apply_gradients. */
+  float *g_W, *g_b, *g_Psi;
 } dpc_layer;
 
 /* A plan = the layer table uploaded once, plus whatever the kernels precompute for it
@@ -243,6 +247,17 @@ DPC_API int dpc_direct_feedback(dpc_plan* plan, int first, int count, int decay_
  * (DirectKPPCLayer.cpp:361-501, FullPCLayer.cpp:382-512, SimplePCLayer.cpp:259-350,
  * CPUBackend.cpp:250-272, 721-772). */
 DPC_API int dpc_update_weights(dpc_plan* plan, int first, int count, int center_rows);
+/* The two halves of dpc_direct_feedback (which = 1) and dpc_update_weights (which = 0) for
+ * batch-sharded training: the first leaves the raw gradient sums of this process's batch rows
+ * in the layers' staging buffers (g_W only for which = 1); the caller sums the buffers over
+ * the shards (an all-reduce); the second applies them with the reference's update formulas
+ * (DirectKPPCLayer.cpp:361-549, FullPCLayer.cpp:382-572, SimplePCLayer.cpp:259-350,
+ * CPUBackendHighway.cpp:779-840), `global_batch` taking the place of the batch size in every
+ * 1/B factor.  option: decay_w (which = 1) or center_rows (which = 0).  The reference has no
+ * multi-GPU code; with one shard the pair computes what the fused call computes. */
+DPC_API int dpc_weight_gradients(dpc_plan* plan, int first, int count, int which);
+DPC_API int dpc_apply_gradients(dpc_plan* plan, int first, int count, int which,
+                                int global_batch, int option);
 /* The error/energy kernel for callers that must not allocate device memory (code between
  * graph captures, hosts whose framework owns every byte of the GPU, loops that forbid
  * allocation once running).  It has no counterpart in the reference.  e = z - mu over
@@ -321,6 +336,16 @@ DPC_API int dpcn_reset_state(dpcn_net* net);
  * owned by the network. */
 DPC_API dpc_ctx* dpcn_context(dpcn_net* net);
 DPC_API dpc_plan* dpcn_plan(dpcn_net* net);
+/* Batch sharding (the reference has no multi-GPU code; this is the "wide, shallow nets"
+ * regime): this network holds `batch` of `global_batch` rows.  From now on every
+ * DirectFeedbackUpdate / UpdateWeights inside a train step stages raw gradient sums, calls
+ * sync(user, dev, count, stream) -- which must leave in dev[0..count) the sum over all
+ * shards, ordered on `stream` (an NCCL all-reduce); non-zero return aborts the step -- and
+ * applies them with global_batch in the 1/B factors.  sync = NULL switches back.  Steps are
+ * not captured into a CUDA graph while a sync function is set. */
+typedef int (*dpcn_sync_fn)(void* user, float* dev, int64_t count, void* stream);
+DPC_API int dpcn_set_gradient_sync(dpcn_net* net, dpcn_sync_fn sync, void* user,
+                                   int global_batch);
 /* Kernel launches issued by the network's context so far. */
 DPC_API int64_t dpcn_launch_count(dpcn_net* net);
 /* Algorithmic FLOPs of one train step with `steps` settling steps (GEMM terms only). */

@@ -134,6 +134,10 @@ class PCOracle:
         # whose last layer is a copy of the next block's first layer (tests/test_sharded_cpu.py).
         ts = self.sizes[-1] if terminal_size is None else terminal_size
         self.e_terminal = None  # override of the terminal error for such a block
+        # Batch sharding: grad_sync(phase, layer, [arrays]) returns the arrays summed over the
+        # shards, global_B the batch those sums cover (no counterpart in the reference).
+        self.grad_sync = None
+        self.global_B = None
         nw = len(self.sizes) - 1
         self.layers = []
         for i in range(nw):
@@ -250,20 +254,25 @@ class PCOracle:
             return
         above = self.layers[i + 1]
         term_e = self.layers[-1].e if self.e_terminal is None else self.e_terminal
-        B = F(self.B)
+        B = F(self.global_B or self.B)
         if self.kind == "simple":
             g, zin, a = above.e, L.zF, F(1)
         else:
             g, zin, a = above.e * dact(L.act, L.preact), L.z, L.a
+        # raw sums over the batch rows held here; a batch-sharded run sums them over the shards
+        G, Gb = g.T @ zin, g.sum(axis=0, dtype=F)
+        GP = None if self.kind == "simple" else L.z.T @ term_e
+        if self.grad_sync is not None:
+            G, Gb, GP = self.grad_sync("learn", i, [G, Gb, GP])
         if self.opt == "SGD":
             if L.lmbda > 0:
                 L.W *= F(1) - L.lmbda
-            L.W += F(a * L.lr / B) * (g.T @ zin)
-            L.b += F(L.lr / B) * g.sum(axis=0, dtype=F)
+            L.W += F(a * L.lr / B) * G
+            L.b += F(L.lr / B) * Gb
         else:
             L.t += 1
-            gW = (F(-1) * a) * (g.T @ zin)
-            gb = F(-1) * g.sum(axis=0, dtype=F)
+            gW = (F(-1) * a) * G
+            gb = F(-1) * Gb
             adam_step(L.W, gW, L.mW, L.vW, L.t, L.lr,
                       wd=(L.lr * L.lmbda) if self.opt == "ADAMW" else None)
             adam_step(L.b, gb, L.mb, L.vb, L.t, L.lr)
@@ -273,10 +282,10 @@ class PCOracle:
         if self.opt_psi == "SGD":
             if self.kind == "dkp" and self.psi_decay > 0:
                 L.Psi *= F(1) - self.psi_decay
-            L.Psi += F(flr / B) * (L.z.T @ term_e)
+            L.Psi += F(flr / B) * GP
         else:
             L.tP += 1
-            gP = F(-1) * (L.z.T @ term_e)
+            gP = F(-1) * GP
             wd = None
             if self.opt_psi == "ADAMW":
                 dec = self.psi_decay if (self.kind == "dkp" and self.psi_decay >= 0) else L.lmbda
@@ -291,9 +300,12 @@ class PCOracle:
         above = self.layers[i + 1]
         term_e = self.layers[-1].e if self.e_terminal is None else self.e_terminal
         proj = (term_e @ above.Psi.T) * dact(L.act, L.preact)
+        G = proj.T @ L.z
+        if self.grad_sync is not None:
+            G, = self.grad_sync("dfa", i, [G])
         if self.kind == "full" and L.lmbda > 0 and L.fl != 0:
             L.W *= F(1) - L.lmbda
-        L.W += F(L.fl * L.a / F(self.B)) * (proj.T @ L.z)
+        L.W += F(L.fl * L.a / F(self.global_B or self.B)) * G
 
     # ---------------------------------------------------------------- network phases
     def reset(self):

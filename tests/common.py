@@ -98,7 +98,7 @@ def run_oracle(case):
     return out
 
 
-def build_gpu_net(case, precision="fp32", use_graph=True):
+def build_gpu_net(case, precision="fp32", use_graph=True, device="cuda"):
     """A deepity_b200 network for a golden-style case, with the case's seeded parameters."""
     import deepity_b200 as dp
     from deepity_b200.layer import Activation
@@ -113,7 +113,7 @@ def build_gpu_net(case, precision="fp32", use_graph=True):
         if hy["act"] != "linear":
             arch.append(acts[hy["act"]]())
     cls = {"simple": dp.SimplePCN, "dkp": dp.DKPPCN, "full": dp.FullPCN}[kind]
-    net = cls(*arch, batch_size=B)
+    net = cls(*arch, batch_size=B, device=device)
     kw = dict(learning_rate=hy["lr"], inference_rate=hy["ir"], lmbda=hy["lmbda"],
               optimizer=opts.get("optimizer", "SGD"), seed=1,
               center_weights=bool(opts.get("center_weights", 0)), precision=precision)
@@ -139,9 +139,12 @@ def build_gpu_net(case, precision="fp32", use_graph=True):
     return net, x, y
 
 
-def run_gpu(case, precision="fp32", use_graph=True):
+def run_gpu(case, precision="fp32", use_graph=True, staged_gradients=False):
     kind, T = case["kind"], case["T"]
     net, x, y = build_gpu_net(case, precision, use_graph)
+    if staged_gradients:
+        # the batch-sharded update path with a single shard: stage, "all-reduce", apply
+        net.set_gradient_sync(lambda t: None, case["batch"])
     mode = case.get("mode", "train_step")
     energies = []
     for _ in range(case["steps"]):

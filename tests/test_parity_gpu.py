@@ -79,6 +79,24 @@ def test_gpu_matches_live_oracle(name, built_library):
     compare_outputs(run_oracle(case), run_gpu(case), case_tol(case), name)
 
 
+STAGED = ["dkp_ragged", "full_adamw", "full_epc_ce", "simple_relu_ce", "dkp_wide_uniform"]
+
+
+@pytest.mark.parametrize("name", STAGED)
+def test_staged_gradient_updates_match_oracle(name, built_library):
+    """The stage / sum-over-shards / apply form of the weight updates (batch sharding) with one
+    shard must give what the fused updates give."""
+    case = EXTRA[name]
+    compare_outputs(run_oracle(case), run_gpu(case, staged_gradients=True), case_tol(case), name)
+
+
+def test_staged_gradients_ipc_and_center(built_library):
+    case = dict(kind="full", sizes=[30, 40, 40, 10], batch=16, T=3, steps=2,
+                hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="tanh"),
+                options=dict(ipc=1, center_weights=1))
+    compare_outputs(run_oracle(case), run_gpu(case, staged_gradients=True), TOL, "ipc staged")
+
+
 # Shapes the tensor-core (tcgen05) kernels take: square layers, width a multiple of 256,
 # batch a multiple of 128, with ordinary CUDA-core layers on both sides of the run.
 TENSOR = {
