@@ -7,10 +7,11 @@
 Everything computes in hand-written CUDA behind the C ABI of ``libdeepity_b200.so``
 (``include/deepity_b200.h``); build it with ``python -m deepity_b200.build``.
 """
-from .layer import (Activation, ESigmoid, GeLU, HardTanH, Layer, Linear, ReLU, Sigmoid,  # noqa: F401
-                    TanH)
+from .layer import (Activation, Convolution, ESigmoid, GeLU, HardTanH, Layer, Linear,  # noqa: F401
+                    ReLU, Sigmoid, TanH)
 from .networks import DKPPCN, FullPCN, SimplePCN  # noqa: F401
+from .conv import SimpleConvolutionalPCN  # noqa: F401
 from ._lib import DeepityError  # noqa: F401
 
-__all__ = ["DKPPCN", "FullPCN", "SimplePCN", "Linear", "Sigmoid", "TanH", "ReLU", "GeLU",
+__all__ = ["DKPPCN", "FullPCN", "SimplePCN", "SimpleConvolutionalPCN", "Convolution", "Linear", "Sigmoid", "TanH", "ReLU", "GeLU",
            "ESigmoid", "HardTanH", "DeepityError"]

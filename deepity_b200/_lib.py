@@ -83,6 +83,31 @@ SIGNATURES = {
     "dpcn_set_gradient_sync": (_i, [_vp, _vp, _vp, _i]),
     "dpcn_launch_count": (_i64, [_vp]),
     "dpcn_train_step_flops": (ctypes.c_double, [_vp, _i]),
+    "dpc_conv_plan_create": (_i, [_vp, _vp, _i, _i, ctypes.POINTER(_vp)]),
+    "dpc_conv_plan_update": (_i, [_vp, _vp, _i]),
+    "dpc_conv_plan_destroy": (_i, [_vp]),
+    "dpc_conv_forward": (_i, [_vp, _i, _i]),
+    "dpc_conv_update_state": (_i, [_vp, _i]),
+    "dpc_conv_gate_with_prediction": (_i, [_vp, _i]),
+    "dpc_conv_update_weights": (_i, [_vp, _i, _i]),
+    "dpc_conv_energy_reset": (_i, [_vp]),
+    "dpc_conv_energy_read": (_i, [_vp, ctypes.POINTER(ctypes.c_double)]),
+    "dpcn_conv_create": (_i, [_i, _i, ctypes.POINTER(_vp)]),
+    "dpcn_conv_destroy": (_i, [_vp]),
+    "dpcn_conv_add_layer": (_i, [_vp] + [_i] * 10 + [_f] * 3 + [_i]),
+    "dpcn_conv_set_option": (_i, [_vp, _cp, _i, _f]),
+    "dpcn_conv_compile": (_i, [_vp]),
+    "dpcn_conv_num_layers": (_i, [_vp]),
+    "dpcn_conv_layer_shape": (_i, [_vp, _i, ctypes.POINTER(_i)]),
+    "dpcn_conv_tensor_size": (_i64, [_vp, _i, _cp]),
+    "dpcn_conv_get_tensor": (_i, [_vp, _i, _cp, c_f32p, _i64]),
+    "dpcn_conv_set_tensor": (_i, [_vp, _i, _cp, c_f32p, _i64]),
+    "dpcn_conv_randomize": (_i, [_vp, ctypes.c_uint32]),
+    "dpcn_conv_train_step": (_i, [_vp, _vp, _i64, _vp, _i64, _i, _i, _i, c_f32p]),
+    "dpcn_conv_predict": (_i, [_vp, c_f32p, _i64, _i, _i, c_f32p, _i64]),
+    "dpcn_conv_context": (_vp, [_vp]),
+    "dpcn_conv_plan": (_vp, [_vp]),
+    "dpcn_conv_launch_count": (_i64, [_vp]),
 }
 
 _lib = None

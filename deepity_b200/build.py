@@ -17,8 +17,10 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 OUT = os.path.join(PKG, "libdeepity_b200.so")
 
-SOURCES = ["dpc_core.cu", "dpc_tc.cu", "dpc_static.cu", os.path.join("host", "pc_network.cpp")]
+SOURCES = ["dpc_core.cu", "dpc_tc.cu", "dpc_static.cu", "dpc_conv.cu",
+           os.path.join("host", "pc_network.cpp"), os.path.join("host", "conv_network.cpp")]
 HEADERS = ["dpc_internal.h", "dpc_math.cuh", "dpc_simt.cuh", os.path.join("host", "pc_network.h"),
+           os.path.join("host", "conv_network.h"),
            os.path.join(ROOT, "include", "deepity_b200.h")]
 
 

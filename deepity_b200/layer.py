@@ -19,6 +19,21 @@ class Linear(Layer):
         return "linear"
 
 
+class Convolution(Layer):
+    """A 2-D convolutional layer (``deepity/layer.py:26-48``); ``out_channels = 0`` closes the
+    architecture with the terminal layer, which has no weights."""
+
+    def __init__(self, out_channels: int, kernel_h: int, kernel_w: int, stride_h: int = 1,
+                 stride_w: int = 1, pad_h: int = 0, pad_w: int = 0):
+        self.out_channels = int(out_channels)
+        self.kernel_h, self.kernel_w = int(kernel_h), int(kernel_w)
+        self.stride_h, self.stride_w = int(stride_h), int(stride_w)
+        self.pad_h, self.pad_w = int(pad_h), int(pad_w)
+
+    def to_string(self) -> str:
+        return "convolution"
+
+
 class Activation:
     def to_string(self) -> str:
         raise NotImplementedError

@@ -351,6 +351,91 @@ DPC_API int64_t dpcn_launch_count(dpcn_net* net);
 /* Algorithmic FLOPs of one train step with `steps` settling steps (GEMM terms only). */
 DPC_API double dpcn_train_step_flops(dpcn_net* net, int steps);
 
+/* ------------------------------------------------------------------------------------
+ * Convolutional predictive coding: SimpleConvPCLayer / SimpleConvPCNetwork
+ * (include/deepity/layers/SimpleConvPCLayer.h, src/layers/SimpleConvPCLayer.cpp,
+ * src/networks/SimpleConvPCNetwork.cpp).  Layouts are the reference's: z, e [B,C,H,W];
+ * W [O, C*kH*kW]; b [O]; preact, mu [B,O,oH,oW].  The gathers the reference materialises
+ * (Im2Col / Col2Im, include/deepity/utils/Im2Col.h:78-259, RepackForBatchedGemm,
+ * CPUBackend.cpp:869-892) are done on the fly by implicit-GEMM kernels.
+ * ---------------------------------------------------------------------------------- */
+typedef struct dpc_conv_layer
+{
+  int32_t in_c, out_c, in_h, in_w; /* out_c = 0: the terminal layer (no weights) */
+  int32_t k_h, k_w, s_h, s_w, p_h, p_w;
+  int32_t out_h, out_w; /* ConvOutDim, Im2Col.h:47-50 */
+  int32_t act, opt;     /* dpc_act, dpc_opt */
+  float lr, ir, lmbda;
+  float *z, *e;
+  float *W, *b;
+  float *preact, *mu;
+  float* g;         /* gated error e_above * f'(preact) ("bottom_up_cols") [B,O,oH,oW] */
+  float *g_W, *g_b; /* raw gradient sums [O, C*kH*kW], [O] */
+  float *m_W, *v_W, *m_b, *v_b;
+  int32_t* t;
+} dpc_conv_layer;
+
+typedef struct dpc_conv_plan dpc_conv_plan;
+enum
+{
+  DPC_CONV_COPY_NEXT = 1 << 0, /* z[l+1] = mu[l] (ProjectForward)                          */
+  DPC_CONV_ERR_NEXT = 1 << 1,  /* e[l+1] = z[l+1] - mu[l], g[l] = e[l+1] * f'(preact[l])   */
+  DPC_CONV_ENERGY = 1 << 2,    /* with ERR_NEXT: energy += 0.5*sum e[l+1]^2                */
+  DPC_CONV_CACHED = 1 << 4     /* clamped layer with a valid cache: reuse preact/mu        */
+};
+DPC_API int dpc_conv_plan_create(dpc_ctx* ctx, const dpc_conv_layer* layers, int n_layers,
+                                 int batch, dpc_conv_plan** out);
+DPC_API int dpc_conv_plan_update(dpc_conv_plan* plan, const dpc_conv_layer* layers, int n_layers);
+DPC_API int dpc_conv_plan_destroy(dpc_conv_plan* plan);
+/* ComputeMuOnly of one layer (SimpleConvPCLayer.cpp:214-300) with the error of the layer above
+ * (CalculateState, :188-212) and the gated error fused in on request. */
+DPC_API int dpc_conv_forward(dpc_conv_plan* plan, int layer, int flags);
+/* UpdateState (SimpleConvPCLayer.cpp:302-400): z += ir*(W^T (*) g - e), the transposed
+ * convolution written as a gather; a layer without weights relaxes, z -= ir*e. */
+DPC_API int dpc_conv_update_state(dpc_conv_plan* plan, int layer);
+/* g = e_above * mu: the gate the reference's UpdateWeights sees when no UpdateState ran since
+ * the last CalculateState (its mu buffer then still holds the prediction, :414). */
+DPC_API int dpc_conv_gate_with_prediction(dpc_conv_plan* plan, int layer);
+/* UpdateWeights (SimpleConvPCLayer.cpp:402-556) + optional CenterWeights. */
+DPC_API int dpc_conv_update_weights(dpc_conv_plan* plan, int layer, int center_rows);
+DPC_API int dpc_conv_energy_reset(dpc_conv_plan* plan);
+DPC_API int dpc_conv_energy_read(dpc_conv_plan* plan, double* out); /* synchronous */
+
+/* The network with host buffers (include/deepity/networks/SimpleConvPCNetwork.h:30-131,
+ * bindings/NetworkBindings.cpp:1850-2000). */
+typedef struct dpcn_conv_net dpcn_conv_net;
+DPC_API int dpcn_conv_create(int batch, int device, dpcn_conv_net** out);
+DPC_API int dpcn_conv_destroy(dpcn_conv_net* net);
+/* AddLayer(inChannels, outChannels, inHeight, inWidth, kernelH, kernelW, strideH, strideW,
+ * padH, padW, lr, ir, lmbda, aType, dType). */
+DPC_API int dpcn_conv_add_layer(dpcn_conv_net* net, int in_c, int out_c, int in_h, int in_w,
+                                int k_h, int k_w, int s_h, int s_w, int p_h, int p_w, float lr,
+                                float ir, float lmbda, int act);
+/* "optimizer" (before compile), "center_weights", "learning_rate", "inference_rate",
+ * "lambda", "use_graph". */
+DPC_API int dpcn_conv_set_option(dpcn_conv_net* net, const char* name, int ivalue, float fvalue);
+DPC_API int dpcn_conv_compile(dpcn_conv_net* net);
+DPC_API int dpcn_conv_num_layers(dpcn_conv_net* net);
+/* Per-layer geometry after compile: out[0..3] = out_c, out_h, out_w, in_c*k_h*k_w. */
+DPC_API int dpcn_conv_layer_shape(dpcn_conv_net* net, int layer, int* out4);
+/* names: "z" "e" "mu" "preact" "W" "b" "weight.m" "weight.v" "bias.m" "bias.v" */
+DPC_API int64_t dpcn_conv_tensor_size(dpcn_conv_net* net, int layer, const char* name);
+DPC_API int dpcn_conv_get_tensor(dpcn_conv_net* net, int layer, const char* name, float* host_out,
+                                 int64_t count);
+DPC_API int dpcn_conv_set_tensor(dpcn_conv_net* net, int layer, const char* name,
+                                 const float* host_in, int64_t count);
+DPC_API int dpcn_conv_randomize(dpcn_conv_net* net, uint32_t seed);
+/* TrainStep / TrainStepWithProjection; on_device != 0: x and y are device pointers. */
+DPC_API int dpcn_conv_train_step(dpcn_conv_net* net, const float* x, int64_t nx, const float* y,
+                                 int64_t ny, int steps, int with_projection, int on_device,
+                                 float* energy_out);
+/* Predict / PredictWithProjection -> terminal beliefs into host_out. */
+DPC_API int dpcn_conv_predict(dpcn_conv_net* net, const float* x, int64_t nx, int steps,
+                              int with_projection, float* host_out, int64_t nout);
+DPC_API dpc_ctx* dpcn_conv_context(dpcn_conv_net* net);
+DPC_API dpc_conv_plan* dpcn_conv_plan(dpcn_conv_net* net);
+DPC_API int64_t dpcn_conv_launch_count(dpcn_conv_net* net);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,6 +30,8 @@ REF_SOURCES = [
     "src/networks/DirectKPPCNetwork.cpp",
     "src/networks/SimplePCNetwork.cpp",
     "src/networks/FullPCNetwork.cpp",
+    "src/networks/SimpleConvPCNetwork.cpp",
+    "src/layers/SimpleConvPCLayer.cpp",
     "src/layers/DirectKPPCLayer.cpp",
     "src/layers/SimplePCLayer.cpp",
     "src/layers/FullPCLayer.cpp",
@@ -63,7 +65,8 @@ def build(verbose: bool = True) -> str | None:
         raise RuntimeError("scipy's bundled OpenBLAS not found")
     torch_lib = os.path.join(sp, "torch", "lib")
     srcs = [os.path.join(root, s) for s in REF_SOURCES]
-    mine = [os.path.join(HERE, "ref_driver.cpp"), os.path.join(HERE, "shim_kernels.cpp")]
+    mine = [os.path.join(HERE, "ref_driver.cpp"), os.path.join(HERE, "ref_conv_driver.cpp"),
+            os.path.join(HERE, "shim_kernels.cpp")]
     newest = max(os.path.getmtime(p) for p in srcs + mine + [os.path.abspath(__file__)])
     if os.path.exists(OUT) and os.path.getmtime(OUT) >= newest:
         return OUT

@@ -154,3 +154,74 @@ def host_info() -> dict:
     L = lib()
     return {"omp_threads": L.ref_omp_threads(), "nproc": L.ref_num_procs(),
             "blas": L.ref_blas_config().decode()}
+
+
+class RefConvNet:
+    """The reference's CPU SimpleConvPCNetwork (oracle/ref_conv_driver.cpp).
+
+    ``layers``: list of dicts(inC, outC, H, W, kH, kW, sH, sW, pH, pW, act); the last one has
+    outC = 0 (the terminal layer)."""
+
+    def __init__(self, layers, batch, lr, ir, lmbda, optimizer="SGD", center_weights=False):
+        L = lib()
+        f32p = ctypes.POINTER(ctypes.c_float)
+        L.refc_create.restype = ctypes.c_void_p
+        L.refc_create.argtypes = [ctypes.c_int]
+        L.refc_destroy.argtypes = [ctypes.c_void_p]
+        L.refc_add_layer.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 10 + \
+            [ctypes.c_float] * 3 + [ctypes.c_int]
+        L.refc_set_option.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int,
+                                      ctypes.c_float]
+        L.refc_compile.argtypes = [ctypes.c_void_p]
+        L.refc_tensor_size.restype = ctypes.c_int64
+        L.refc_tensor_size.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p]
+        L.refc_get_tensor.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p, f32p,
+                                      ctypes.c_int64]
+        L.refc_set_tensor.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p, f32p,
+                                      ctypes.c_int64]
+        L.refc_train_step.restype = ctypes.c_float
+        L.refc_train_step.argtypes = [ctypes.c_void_p, f32p, ctypes.c_int64, f32p, ctypes.c_int64,
+                                      ctypes.c_int, ctypes.c_int]
+        L.refc_predict.argtypes = [ctypes.c_void_p, f32p, ctypes.c_int64, ctypes.c_int,
+                                   ctypes.c_int, f32p, ctypes.c_int64]
+        self.L, self.batch, self.layers = L, batch, layers
+        self.h = ctypes.c_void_p(L.refc_create(batch))
+        for d in layers:
+            L.refc_add_layer(self.h, d["inC"], d["outC"], d["H"], d["W"], d["kH"], d["kW"],
+                             d["sH"], d["sW"], d["pH"], d["pW"], lr, ir, lmbda, ACT[d["act"]])
+        L.refc_set_option(self.h, b"optimizer", OPT[optimizer], 0.0)
+        L.refc_compile(self.h)
+        L.refc_set_option(self.h, b"center_weights", int(center_weights), 0.0)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.L.refc_destroy(self.h)
+            self.h = None
+
+    def get(self, layer, name):
+        n = self.L.refc_tensor_size(self.h, layer, name.encode())
+        if n < 0:
+            raise KeyError((layer, name))
+        out = np.empty(n, dtype=np.float32)
+        self.L.refc_get_tensor(self.h, layer, name.encode(), _ptr(out), n)
+        return out
+
+    def set(self, layer, name, value):
+        v = np.ascontiguousarray(value, dtype=np.float32).ravel()
+        if self.L.refc_set_tensor(self.h, layer, name.encode(), _ptr(v), v.size) != 0:
+            raise KeyError((layer, name, v.size))
+
+    def train_step(self, x, y, T, with_projection=False):
+        x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+        y = np.ascontiguousarray(y, dtype=np.float32).ravel()
+        return float(self.L.refc_train_step(self.h, _ptr(x), x.size, _ptr(y), y.size, T,
+                                            int(with_projection)))
+
+    def predict(self, x, T, with_projection=False):
+        x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+        last = self.layers[-1]
+        out = np.empty(self.batch * last["inC"] * last["H"] * last["W"], dtype=np.float32)
+        if self.L.refc_predict(self.h, _ptr(x), x.size, T, int(with_projection), _ptr(out),
+                               out.size) != 0:
+            raise RuntimeError("reference Predict() size mismatch")
+        return out

@@ -167,8 +167,9 @@ def run_gpu(case, precision="fp32", use_graph=True, staged_gradients=False):
     return out
 
 
-def compare_outputs(ref, got, tol, what=""):
-    """ref may hold full tensors (t.*) or statistics (stat.*)."""
+def compare_outputs(ref, got, tol, what="", energy_tol=None):
+    """ref may hold full tensors (t.*) or statistics (stat.*).  energy_tol: a separate bound
+    for the energies where the reference's own fp32 accumulation is the limit."""
     worst = 0.0
     bad = []
     for k, r in ref.items():
@@ -183,7 +184,7 @@ def compare_outputs(ref, got, tol, what=""):
         else:
             err = rel_err(r, got[k])
         worst = max(worst, err)
-        if not err <= tol:
+        if not err <= (energy_tol if (k == "energies" and energy_tol) else tol):
             bad.append((k, err))
     assert not bad, f"{what}: beyond tolerance {tol}: {bad[:8]}"
     return worst
