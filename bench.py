@@ -2,7 +2,7 @@
 """Benchmark of the predictive-coding train step (metric: train_step samples/sec).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c3|c2|c1|c4] [--depth D] [--precision fp32|tf32]
+                    [--workload c3|c2|c1|c4|c5] [--depth D] [--precision fp32|tf32]
 
 One "step" is one full ``train_step`` (settle T times, learn, final energy) on one batch of
 synthetic data.  At N=1 the workload is the configuration the headline metric is quoted on:
@@ -54,6 +54,12 @@ WORKLOADS = {
                x="normal", desc="FullPCN 3072-(1024x4)-10 gelu CE Adam B4096 T20"),
 }
 HYPER = dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.0)
+# C5: the reference has no pooling layer, so the 2x2 average pools of the named configuration
+# are folded into stride-2 convolutions (3x3, pad 1); the dense 2048-10 head is a 4x4 convolution.
+C5 = dict(input_shape=(3, 32, 32), batch=128, T=10, act="relu",
+          convs=[(32, 3, 3, 2, 2, 1, 1), (64, 3, 3, 2, 2, 1, 1), (128, 3, 3, 2, 2, 1, 1),
+                 (10, 4, 4, 1, 1, 0, 0)],
+          desc="SimpleConvolutionalPCN 32x32x3 conv3x3/s2 32-64-128 + dense 2048-10 relu B128 T10 SGD")
 
 
 def sizes_of(w, hidden=None):
@@ -192,6 +198,165 @@ def cpu_reference_leg(w, steps, warmup, budget_layers=None):
             "sample": sample, "ms_per_step_sample": dt * 1e3, "last_energy": float(e)}
 
 
+# ------------------------------------------------------------------------------ conv (C5)
+def conv_layers():
+    c, h, w = C5["input_shape"]
+    out = []
+    for i, (o, kh, kw, sh, sw, ph, pw) in enumerate(C5["convs"]):
+        out.append(dict(inC=c, outC=o, H=h, W=w, kH=kh, kW=kw, sH=sh, sW=sw, pH=ph, pW=pw,
+                        act=C5["act"] if i + 1 < len(C5["convs"]) else "linear"))
+        c, h, w = o, (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
+    out.append(dict(inC=c, outC=0, H=h, W=w, kH=1, kW=1, sH=1, sW=1, pH=0, pW=0, act="linear"))
+    return out
+
+
+def conv_synth(layers, B, seed=1234, wseed=99):
+    rng, wr = np.random.default_rng(seed), np.random.default_rng(wseed)
+    f = layers[0]
+    x = rng.normal(size=(B, f["inC"], f["H"], f["W"])).astype(np.float32)
+    y = np.eye(layers[-1]["inC"], dtype=np.float32)[rng.integers(0, layers[-1]["inC"], B)]
+    params = []
+    for d in layers[:-1]:
+        rows = d["inC"] * d["kH"] * d["kW"]
+        params.append(wr.normal(0, np.sqrt(2.0 / rows), (d["outC"], rows)).astype(np.float32))
+    return x, y, params
+
+
+def conv_flops(layers, B, T):
+    """2*B*P*O*(C*kH*kW) per product: T+1 forward (the clamped input layer: 1), T transposed
+    (none for the clamped input layer) and 1 weight-shaped product per weight layer."""
+    total = 0.0
+    for i, d in enumerate(layers[:-1]):
+        oh = (d["H"] + 2 * d["pH"] - d["kH"]) // d["sH"] + 1
+        ow = (d["W"] + 2 * d["pW"] - d["kW"]) // d["sW"] + 1
+        g = 2.0 * B * oh * ow * d["outC"] * d["inC"] * d["kH"] * d["kW"]
+        total += g * ((1 if i == 0 else T + 1) + (0 if i == 0 else T) + 1)
+    return total
+
+
+def conv_cpu_leg(layers, B, T, steps, warmup):
+    from oracle import ref as oref
+    x, y, params = conv_synth(layers, B)
+    if oref.available():
+        kind, cores = "reference", oref.host_info()["omp_threads"]
+        net = oref.RefConvNet(layers, B, HYPER["lr"], HYPER["ir"], HYPER["lmbda"])
+    else:
+        from oracle.conv_oracle import ConvOracle
+        kind, cores = "port", os.cpu_count()
+        net = ConvOracle(layers, B, HYPER["lr"], HYPER["ir"], HYPER["lmbda"])
+    for l, W in enumerate(params):
+        net.set(l, "W", W)
+    for _ in range(warmup):
+        net.train_step(x, y, T)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        e = net.train_step(x, y, T)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return {"value": B / dt, "unit": "samples/s", "cores": int(cores), "kind": kind,
+            "sample": f"{C5['desc']} at full size, {steps} steps of {dt * 1e3:.1f} ms",
+            "last_energy": float(e)}
+
+
+def conv_main(args):
+    """--workload c5: the convolutional network on one GPU (replicas only beyond that)."""
+    layers, B, T = conv_layers(), C5["batch"], C5["T"]
+    config = {"workload": C5["desc"], "global_batch": B, "T": T, "layers": len(layers) - 1,
+              "hyper": {k: HYPER[k] for k in ("lr", "ir", "lmbda")}, "precision": "fp32",
+              "l2": "L2 flushed between timed steps"}
+    if args.impl == "reference":
+        leg = conv_cpu_leg(layers, B, T, max(1, min(args.steps, 3)), min(args.warmup, 1))
+        print(json.dumps({"impl": "reference", "metric": "train_step samples/sec",
+                          "value": leg["value"], "unit": "samples/s", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": B / leg["value"] * 1e3, "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                          "data": "synthetic", "config": config,
+                          "cpu_baseline": {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                          "e2e": {"value": leg["value"], "unit": "samples/s",
+                                  "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    import torch
+    import deepity_b200 as dp
+    from deepity_b200 import _lib
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    arch = []
+    for d in layers:
+        arch.append(dp.Convolution(d["outC"], d["kH"], d["kW"], d["sH"], d["sW"], d["pH"], d["pW"]))
+        if d["act"] != "linear":
+            arch.append(dp.ReLU())
+    net = dp.SimpleConvolutionalPCN(*arch, input_shape=C5["input_shape"], batch_size=B)
+    net.configure(learning_rate=HYPER["lr"], inference_rate=HYPER["ir"], lmbda=HYPER["lmbda"], seed=1)
+    x, y, params = conv_synth(layers, B)
+    for l, W in enumerate(params):
+        net.set_tensor(l, "W", W)
+    xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+    ctx = lib.dpcn_conv_context(net._h)
+    stream = torch.cuda.ExternalStream(lib.dpc_stream(ctx))
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, steps):
+        total = 0.0
+        for _ in range(steps):
+            flush.zero_()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            fn()
+            b.record(stream)
+            b.synchronize()
+            total += a.elapsed_time(b)
+        return total / steps
+
+    for _ in range(args.warmup):
+        energy = net.train_step_device(xd, yd, T)
+    with ClockSampler(0) as clk:
+        n0 = net.launch_count
+        ms = timed(lambda: net.train_step_device(xd, yd, T), args.steps)
+        launches = net.launch_count - n0
+        energy = net.train_step_device(xd, yd, T)
+        e2e_ms = timed(lambda: net.train_step(x, y, T), args.steps)
+        # dominant kernel: the forward implicit GEMM of the widest layer (64 -> 128 channels)
+        plan, big = lib.dpcn_conv_plan(net._h), 2
+        for _ in range(2):
+            lib.dpc_conv_forward(plan, big, 2)
+        k_ms = timed(lambda: lib.dpc_conv_forward(plan, big, 2), max(args.steps, 5))
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    d = layers[big]
+    oh, ow = layers[big + 1]["H"], layers[big + 1]["W"]
+    rows = d["inC"] * d["kH"] * d["kW"]
+    k_flops = 2.0 * B * oh * ow * d["outC"] * rows
+    k_bytes = 4.0 * (B * d["inC"] * d["H"] * d["W"] + d["outC"] * rows + 5 * B * d["outC"] * oh * ow)
+    hbm = peaks.get("hbm_gbs") or 6650.0
+    achieved = k_bytes / (k_ms * 1e-3) / 1e9
+    flops = conv_flops(layers, B, T)
+    line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config, "energy": energy,
+            "algorithmic_flops_per_step": flops, "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
+            "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "conv forward implicit GEMM, 64->128 channels "
+                                                   "(reads z, W, z_up; writes preact, mu, e_up, g)",
+                         "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                         "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback",
+                         "traffic": None, "launch_ms": k_ms, "algorithmic_bytes_per_launch": k_bytes,
+                         "algorithmic_flops_per_launch": k_flops,
+                         "note": "7.6 MB and 0.3 GFLOP per launch on 64 CTAs: latency-bound at this size, "
+                                 "neither roofline binds"},
+            "clocks": clk.summary()}
+    if not args.no_cpu:
+        leg = conv_cpu_leg(layers, B, T, 2, 1)
+        line["cpu_baseline"] = {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line))
+
+
 # ------------------------------------------------------------------------------ GPU leg
 def build_net(w, sizes, precision):
     import deepity_b200 as dp
@@ -218,7 +383,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c5"])
     ap.add_argument("--depth", type=int, default=None, help="override the hidden-layer count")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
@@ -226,6 +391,10 @@ def main():
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.workload == "c5":
+        if rank == 0:
+            conv_main(args)
+        return
     w = dict(WORKLOADS[args.workload])
     if args.depth:
         w["hidden"] = args.depth
