@@ -140,6 +140,89 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
                "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
+// ---- CTA-pair (cta_group::2) helpers: two CTAs of a cluster share one 256-row tile ---------
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank)
+{
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on a barrier given by its shared::cluster address (own CTA or the peer).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr)
+{
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint64_t* bar, uint32_t parity)
+{
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(smem_u32(bar)), "r"(parity)
+               : "memory");
+  return ok;
+}
+// Bounded wait on a barrier that CTAs of the cluster other than this one arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity,
+                                                  volatile int* abort_flag)
+{
+  if (mbar_try_wait_cluster(bar, parity))
+    return true;
+  const long long t0 = clock64();
+  for (;;)
+  {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity))
+        return true;
+    if (*abort_flag)
+      return false;
+    if (clock64() - t0 > kWaitCycles)
+    {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+// TMA load whose completion bytes are counted on a barrier of either CTA of the pair
+// (bar_addr is a shared::cluster address).  No multicast: each CTA fetches its own tiles.
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map,
+                                                 uint32_t bar_addr, int c0, int c1, int c2)
+{
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+               " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_addr)
+{
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before()
 {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -422,13 +505,19 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
 // ------------------------------------------------------------------------------ kernel
 // Warp roles: 0 TMA producer, 1 MMA issuer (+ tensor-memory owner), 2..9 epilogue,
 // 10..13 remainder ("lo") transform (3xTF32 only).
-template <int OP, int BN, bool THREE_X, int BM = 128>
+// PAIR: two CTAs of a cluster (cta_group::2) compute one 256 x BN tile.  Each CTA stages its own
+// 128 rows of A and its own half of B (BN/2 rows) and holds its 128 rows of the accumulator in
+// its own tensor memory, so per output element half as many operand bytes cross L2 -> SM and
+// shared memory as with two independent 128 x BN/2 tiles.
+template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false>
 struct Cfg
 {
   static constexpr bool A_MN = (OP == TC_WG);
   static constexpr bool B_MN = (OP != TC_FWD);
+  static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN; // rows of B this CTA stages
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;   // rows of D per work item
   static constexpr int A_BYTES = BM * TBK * 4;
-  static constexpr int B_BYTES = BN * TBK * 4;
+  static constexpr int B_BYTES = BN_LOCAL * TBK * 4;
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (THREE_X ? 2 : 1);
   // at most 8 stages: the barrier block after the ring is sized for that
   static constexpr int STAGES_RAW = 196608 / STAGE_BYTES;
@@ -442,15 +531,16 @@ struct Cfg
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
                                     ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
-                                    ((uint32_t)(BM >> 4) << 24);
+                                    ((uint32_t)(TILE_M >> 4) << 24);
+  static_assert(!PAIR || (BM == 128 && BN % 64 == 0), "pair tiles are 256 x BN");
 };
 
-template <int OP, int BN, bool THREE_X, int BM = 128>
-__global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
+template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false>
+__global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
     pc_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const TcParams P)
 {
-  using C = Cfg<OP, BN, THREE_X, BM>;
+  using C = Cfg<OP, BN, THREE_X, BM, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -467,9 +557,12 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_per_layer = P.tiles_m * P.tiles_n;
   const int total_tiles = P.count * tiles_per_layer;
-  const int t_begin = P.chain ? 0 : (int)blockIdx.x;
+  // Pair mode: the two CTAs of a cluster walk the same work items; rank 0 issues the MMAs.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0;
+  const bool leader = rank == 0;
+  const int t_begin = P.chain ? 0 : (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x);
   const int t_end = P.chain ? P.count : total_tiles;
-  const int t_step = P.chain ? 1 : (int)gridDim.x;
+  const int t_step = P.chain ? 1 : (PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x);
   const int kblocks = P.K / TBK;
 
   if (threadIdx.x == 0)
@@ -478,12 +571,12 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
     {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&xf[s], 4);
+      mbar_init(&xf[s], PAIR ? 8 : 4); // transform warps of both CTAs arrive on the leader's
     }
     for (int a = 0; a < 2; ++a)
     {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], C::EPI_WARPS);
+      mbar_init(&tempty[a], PAIR ? 2 * C::EPI_WARPS : C::EPI_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -491,16 +584,37 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
   }
   if (warp == 1)
   {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_holder)),
-                 "r"((uint32_t)C::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR)
+    {
+      // one warp of each CTA of the pair takes part in the paired allocation
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(tmem_holder)),
+                   "r"((uint32_t)C::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    else
+    {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(tmem_holder)),
+                   "r"((uint32_t)C::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR)
+    cluster_sync_all(); // the peer's barriers are initialised before anything signals them
+  else
+    __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // Barriers of the leader CTA as seen from either CTA (shared::cluster addresses).
+  const uint32_t lead_full = PAIR ? mapa_u32(smem_u32(full), 0) : 0;
+  const uint32_t lead_xf = PAIR ? mapa_u32(smem_u32(xf), 0) : 0;
+  const uint32_t lead_tempty = PAIR ? mapa_u32(smem_u32(tempty), 0) : 0;
+  const uint32_t peer_empty = PAIR ? mapa_u32(smem_u32(empty), rank ^ 1) : 0;
+  const uint32_t peer_tfull = PAIR ? mapa_u32(smem_u32(tfull), rank ^ 1) : 0;
 
   if (warp == 0)
   {
@@ -514,32 +628,54 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
       {
         const int lrel = P.chain ? t : t / tiles_per_layer;
         const int rem = P.chain ? (int)blockIdx.x : t % tiles_per_layer;
-        const int m0 = (rem / P.tiles_n) * BM, n0 = (rem % P.tiles_n) * BN;
+        // this CTA's rows of A and rows of B (pair mode: its half of each)
+        const int m0 = (rem / P.tiles_n) * C::TILE_M + (int)rank * BM;
+        const int n0 = (rem % P.tiles_n) * BN + (int)rank * C::BN_LOCAL;
         const int lcoord = P.first + lrel - P.run_first;
         for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == C::STAGES ? 0 : s + 1))
         {
           if (s == 0 && !(t == t_begin && kb == 0))
             phase ^= 1;
-          if (!mbar_wait(&empty[s], phase, abort_flag))
+          if (!(PAIR ? mbar_wait_cluster(&empty[s], phase, abort_flag)
+                     : mbar_wait(&empty[s], phase, abort_flag)))
           {
             alive = false;
             break;
           }
           uint8_t* a_dst = stage_base + s * C::STAGE_BYTES;
           uint8_t* b_dst = a_dst + C::A_BYTES;
-          mbar_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
           const int k0 = kb * TBK;
+          if (PAIR && !THREE_X)
+          {
+            // One pass of TF32: the MMA thread of the leader waits on ITS full[s] for the tiles
+            // of both CTAs, so both CTAs' copies count their bytes there.
+            if (leader)
+              mbar_expect_tx(&full[s], 2 * (C::A_BYTES + C::B_BYTES));
+            const uint32_t bar = lead_full + (uint32_t)(s * 8);
+            if (!C::B_MN)
+              tma_load_3d_pair(b_dst, &mapB, bar, k0, n0, lcoord);
+            else
+              for (int i = 0; i < C::BN_LOCAL / 32; ++i)
+                tma_load_3d_pair(b_dst + i * (TBK * 128), &mapB, bar, n0 + 32 * i, k0, lcoord);
+            if (!C::A_MN)
+              tma_load_3d_pair(a_dst, &mapA, bar, k0, m0, lcoord);
+            else
+              for (int i = 0; i < BM / 32; ++i)
+                tma_load_3d_pair(a_dst + i * (TBK * 128), &mapA, bar, m0 + 32 * i, k0, lcoord);
+            continue;
+          }
+          mbar_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
           if (!C::B_MN)
             tma_load_3d(b_dst, &mapB, &full[s], k0, n0, lcoord);
           else
-            for (int i = 0; i < BN / 32; ++i)
+            for (int i = 0; i < C::BN_LOCAL / 32; ++i)
               tma_load_3d(b_dst + i * (TBK * 128), &mapB, &full[s], n0 + 32 * i, k0, lcoord);
           if (P.chain && kb == 0 && t > 0)
           {
             // The rows of this layer's input are the previous layer's output: wait until every
             // tile of that row block has been published (the weights above are already on
             // their way).
-            if (!chain_wait(&P.chain_counters[(t - 1) * P.tiles_m + m0 / BM], P.chain_target,
+            if (!chain_wait(&P.chain_counters[(t - 1) * P.tiles_m + m0 / C::TILE_M], P.chain_target,
                             abort_flag))
               alive = false; // the A copy below still runs so the stage's byte count completes
             trace_stamp(P, t, 0);
@@ -569,7 +705,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
   else if (warp == 1)
   {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0)
+    if (lane == 0 && leader)
     {
       int s = 0, tile_iter = 0;
       uint32_t phase = 0; // parity to wait for on full[s] / xf[s]
@@ -585,14 +721,16 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
       for (int t = t_begin; t < t_end && alive; t += t_step, ++tile_iter)
       {
         const int acc = tile_iter & 1;
-        if (!mbar_wait(&tempty[acc], ((tile_iter >> 1) & 1) ^ 1, abort_flag))
+        if (!(PAIR ? mbar_wait_cluster(&tempty[acc], ((tile_iter >> 1) & 1) ^ 1, abort_flag)
+                   : mbar_wait(&tempty[acc], ((tile_iter >> 1) & 1) ^ 1, abort_flag)))
           break;
         tc_fence_after();
         const uint32_t d_tmem0 = tmem_base + acc * (BN * C::KSPLIT);
         for (int kb = 0; kb < kblocks; ++kb)
         {
           uint64_t* ready = THREE_X ? &xf[s] : &full[s];
-          if (!mbar_wait(ready, phase, abort_flag))
+          if (!(PAIR ? mbar_wait_cluster(ready, phase, abort_flag)
+                     : mbar_wait(ready, phase, abort_flag)))
           {
             alive = false;
             break;
@@ -615,19 +753,45 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
             {
               const uint64_t dal = da + (uint64_t)((C::A_BYTES + C::B_BYTES) >> 4);
               const uint64_t dbl = db + (uint64_t)((C::A_BYTES + C::B_BYTES) >> 4);
-              tc_mma_tf32(d_tmem, da, dbl, C::IDESC, first);
-              tc_mma_tf32(d_tmem, dal, db, C::IDESC, 1);
-              tc_mma_tf32(d_tmem, da, db, C::IDESC, 1);
+              if (PAIR)
+              {
+                tc_mma_tf32_pair(d_tmem, da, dbl, C::IDESC, first);
+                tc_mma_tf32_pair(d_tmem, dal, db, C::IDESC, 1);
+                tc_mma_tf32_pair(d_tmem, da, db, C::IDESC, 1);
+              }
+              else
+              {
+                tc_mma_tf32(d_tmem, da, dbl, C::IDESC, first);
+                tc_mma_tf32(d_tmem, dal, db, C::IDESC, 1);
+                tc_mma_tf32(d_tmem, da, db, C::IDESC, 1);
+              }
             }
+            else if (PAIR)
+              tc_mma_tf32_pair(d_tmem, da, db, C::IDESC, first);
             else
               tc_mma_tf32(d_tmem, da, db, C::IDESC, first);
           }
-          tc_commit(&empty[s]);
+          if (PAIR)
+          {
+            // release the stage in both CTAs (two plain commits, no multicast)
+            tc_commit_pair(smem_u32(&empty[s]));
+            tc_commit_pair(peer_empty + (uint32_t)(s * 8));
+          }
+          else
+            tc_commit(&empty[s]);
           if (++s == C::STAGES)
             s = 0, phase ^= 1;
         }
         if (alive)
-          tc_commit(&tfull[acc]);
+        {
+          if (PAIR)
+          {
+            tc_commit_pair(smem_u32(&tfull[acc]));
+            tc_commit_pair(peer_tfull + (uint32_t)(acc * 8));
+          }
+          else
+            tc_commit(&tfull[acc]);
+        }
       }
     }
   }
@@ -649,7 +813,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
       // M=128: lane i of quarter q holds row 32q+i.  M=64: rows 16q..16q+15 sit in lanes 0..15 of
       // quarter q and the upper 16 lanes hold nothing.
       const bool active = BM == 128 || lane < 16;
-      const int m = (rem / P.tiles_n) * BM + (BM == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15));
+      const int m = (rem / P.tiles_n) * C::TILE_M + (int)rank * BM +
+                    (BM == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15));
       const int n0 = (rem % P.tiles_n) * BN;
       const int li = P.first + lrel;
       const dpc_layer* Lup = (li + 1 < P.n_layers) ? &P.layers[li + 1] : nullptr;
@@ -669,7 +834,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
               ld8(meta.b + n0 + (grp + GROUPS * i) * 16 + k, &bias_pre[i * 16 + k]);
         }
       }
-      if (!mbar_wait(&tfull[acc], (tile_iter >> 1) & 1, abort_flag))
+      if (!(PAIR ? mbar_wait_cluster(&tfull[acc], (tile_iter >> 1) & 1, abort_flag)
+                 : mbar_wait(&tfull[acc], (tile_iter >> 1) & 1, abort_flag)))
         break;
       tc_fence_after();
       if (P.chain && warp == 2 && lane == 0)
@@ -795,7 +961,12 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0)
-        mbar_arrive(&tempty[acc]);
+      {
+        if (PAIR)
+          mbar_arrive_cluster(lead_tempty + (uint32_t)(acc * 8));
+        else
+          mbar_arrive(&tempty[acc]);
+      }
     }
     if (OP == TC_FWD && (P.flags & DPC_FWD_ENERGY))
     {
@@ -843,22 +1014,35 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM>::THREADS, 1)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0)
-          mbar_arrive(&xf[s]);
+        {
+          if (PAIR)
+            mbar_arrive_cluster(lead_xf + (uint32_t)(s * 8));
+          else
+            mbar_arrive(&xf[s]);
+        }
       }
     }
   }
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
-  __syncthreads();
+  if (PAIR)
+    cluster_sync_all(); // neither CTA leaves while the other may still touch its memory
+  else
+    __syncthreads();
   if (threadIdx.x == 0 && *abort_flag)
     atomicExch(P.error_flag, 1);
   if (warp == 1)
   {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"((uint32_t)C::TMEM_COLS)
-                 : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"((uint32_t)C::TMEM_COLS)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"((uint32_t)C::TMEM_COLS)
+                   : "memory");
   }
 }
 
@@ -901,12 +1085,12 @@ bool make_map(CUtensorMap* map, const float* base, int cols, int rows, int layer
   return r == CUDA_SUCCESS;
 }
 
-template <int OP, int BN, bool THREE_X, int BM = 128>
+template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false>
 int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P)
 {
-  using C = Cfg<OP, BN, THREE_X, BM>;
+  using C = Cfg<OP, BN, THREE_X, BM, PAIR>;
   static bool configured = false;
-  auto kern = pc_tc_kernel<OP, BN, THREE_X, BM>;
+  auto kern = pc_tc_kernel<OP, BN, THREE_X, BM, PAIR>;
   if (!configured)
   {
     if (C::SMEM_BYTES > st->max_smem)
@@ -918,6 +1102,28 @@ int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b,
     configured = true;
   }
   const int total = P.count * P.tiles_m * P.tiles_n;
+  if (PAIR)
+  {
+    // one cluster of two CTAs per work item, as many clusters as SM pairs
+    const int pairs = std::min(total, p->ctx->sm_count / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = p->ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, b, P);
+    p->ctx->launches += 1;
+    if (e != cudaSuccess)
+      return cuda_fail(e, "tensor-core pair kernel launch");
+    return DPC_OK;
+  }
   const int grid = P.chain ? P.tiles_m * P.tiles_n : std::min(total, p->ctx->sm_count);
   kern<<<grid, C::THREADS, C::SMEM_BYTES, p->ctx->stream>>>(a, b, P);
   p->ctx->launches += 1;
@@ -1062,6 +1268,14 @@ int tc_check_error(dpc_plan* plan)
   return DPC_OK;
 }
 
+// CTA-pair kernels take 256 x 256 tiles; DPC_DISABLE_CTA_PAIRS keeps the single-CTA kernels
+// (used by the tests that compare the two).
+static bool pair_ok(int rows, int cols)
+{
+  static const bool off = getenv("DPC_DISABLE_CTA_PAIRS") != nullptr;
+  return !off && rows % 256 == 0 && cols % 256 == 0;
+}
+
 static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int M, int N, int K,
                             int BN, int flags, int mode, int BM = TBM)
 {
@@ -1092,7 +1306,14 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
   if (!st || !st->ok || !range_in_run(p, first, count))
     return 1;
   const int H = p->run.width, B = p->batch;
-  if (p->ctx->precision == DPC_PRECISION_TF32)
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  if (pair_ok(B, H))
+  {
+    TcParams P = base_params(p, st, first, count, B, H, H, 256, flags, 0, 256);
+    return tf32 ? launch<TC_FWD, 256, false, 128, true>(p, st, st->z_km, st->w_km128, P)
+                : launch<TC_FWD, 256, true, 128, true>(p, st, st->z_km, st->w_km128, P);
+  }
+  if (tf32)
     return launch<TC_FWD, 256, false>(p, st, st->z_km, st->w_km256,
                                       base_params(p, st, first, count, B, H, H, 256, flags, 0));
   return launch<TC_FWD, 128, true>(p, st, st->z_km, st->w_km128,
@@ -1141,7 +1362,14 @@ int tc_update_state(dpc_plan* p, int first, int count)
   if (!st || !st->ok || !range_in_run(p, first, count))
     return 1;
   const int H = p->run.width, B = p->batch;
-  if (p->ctx->precision == DPC_PRECISION_TF32)
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  if (pair_ok(B, H))
+  {
+    TcParams P = base_params(p, st, first, count, B, H, H, 256, 0, 0, 256);
+    return tf32 ? launch<TC_FB, 256, false, 128, true>(p, st, st->fe_km, st->w_mn, P)
+                : launch<TC_FB, 256, true, 128, true>(p, st, st->fe_km, st->w_mn, P);
+  }
+  if (tf32)
     return launch<TC_FB, 256, false>(p, st, st->fe_km, st->w_mn,
                                      base_params(p, st, first, count, B, H, H, 256, 0, 0));
   return launch<TC_FB, 128, true>(p, st, st->fe_km, st->w_mn,
@@ -1162,7 +1390,14 @@ int tc_weight_gemm(dpc_plan* p, int first, int count, int mode)
       return 1;
   }
   const int H = p->run.width, B = p->batch;
-  if (p->ctx->precision == DPC_PRECISION_TF32)
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  if (pair_ok(H, H))
+  {
+    TcParams P = base_params(p, st, first, count, H, H, B, 256, 0, mode, 256);
+    return tf32 ? launch<TC_WG, 256, false, 128, true>(p, st, st->fe_mn, st->z_mn, P)
+                : launch<TC_WG, 256, true, 128, true>(p, st, st->fe_mn, st->z_mn, P);
+  }
+  if (tf32)
     return launch<TC_WG, 256, false>(p, st, st->fe_mn, st->z_mn,
                                      base_params(p, st, first, count, H, H, B, 256, 0, mode));
   return launch<TC_WG, 128, true>(p, st, st->fe_mn, st->z_mn,

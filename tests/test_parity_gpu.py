@@ -105,6 +105,11 @@ TENSOR = {
     "dkp_tensor_run_mixed": dict(kind="dkp", sizes=[100] + [512] * 4 + [10], batch=256, T=3,
                                  steps=2,
                                  hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="gelu")),
+    # batch and width multiples of 256: the CTA-pair (cta_group::2) kernels
+    "full_pair_tiles_residual_momentum": dict(
+        kind="full", sizes=[64] + [256] * 4 + [10], batch=512, T=3, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="gelu"),
+        options=dict(mupc=1, residual=1, momentum=0.9)),
     "full_tensor_run_residual_momentum": dict(
         kind="full", sizes=[64] + [256] * 4 + [10], batch=128, T=3, steps=2,
         hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="tanh"),
