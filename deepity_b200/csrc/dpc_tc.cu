@@ -52,6 +52,10 @@ struct TcState
 {
   bool ok = false;
   CUtensorMap z_km, z_km64, fe_km, w_km32, w_km64, w_km128, w_km256, z_mn, fe_mn, w_mn;
+  // beliefs / errors of the run's layers AND the layer above its last one (layer coordinate
+  // l+1 = the layer above l): what the forward epilogue reads, staged through shared memory
+  CUtensorMap zup_km, eup_km;
+  bool up_maps = false;
   int* chain_counters = nullptr; // device: [layers of the run][row blocks]
   unsigned long long* trace = nullptr; // optional timing trace buffer of the chain kernel
   int* error_flag = nullptr; // device
@@ -79,6 +83,10 @@ struct TcParams
   // 256 layers, globaltimer stamps of [dependency seen, first operands landed, accumulator
   // complete, epilogue stores issued, published].
   unsigned long long* trace;
+  // Pair-mode forward: 0 = the epilogue reads nothing from the layer above, 1 = its belief
+  // (tensor map mapU covers the z arena), 2 = its stored error (mapU covers the e arena); the
+  // tile is then brought into shared memory by TMA instead of per-lane global loads.
+  int stage_in;
 };
 
 // ------------------------------------------------------------------------------ PTX
@@ -372,11 +380,23 @@ __device__ __forceinline__ void load_fwd_meta(const TcParams& P, int li, FwdMeta
     M.up_z = M.up_e = nullptr, M.up_flags = 0;
 }
 
-template <int ACT, int BN, int GROUPS, bool PREFETCH>
+// Where the staged operand of the layer above sits (pair-mode forward only).
+struct InStage
+{
+  const uint8_t* buf; // IN_BUFS buffers of 128 rows x 128 bytes, 128-byte swizzle
+  uint64_t* full;
+  uint64_t* empty;
+  uint32_t seq;  // sequence number of this tile's first 32-column box
+  int row;       // this lane's row inside the 128-row box
+  int nbufs;     // power of two
+  volatile int* abort_flag;
+};
+
+template <int ACT, int BN, int GROUPS, bool PREFETCH, bool STAGED = false>
 __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMeta& L,
                                                   const float* bias_pre, uint32_t taddr, int m,
                                                   int n0, int grp, float& esum, int tl,
-                                                  bool active)
+                                                  bool active, const InStage* in = nullptr)
 {
   const int act = ACT >= 0 ? ACT : L.act;
   const bool Lup = L.up_z != nullptr;
@@ -399,6 +419,9 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
   float up[CW], upn[CW];
   if (!active)
     up_src = nullptr; // lanes that hold no accumulator row touch no memory
+  const bool staged = STAGED && P.stage_in != 0 && up_src_all != nullptr;
+  if (staged)
+    up_src = nullptr; // the operand comes from shared memory, box by box
   if (up_src)
   {
 #pragma unroll
@@ -410,6 +433,26 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
   {
     const size_t o = row + c * CW;
     float v[CW];
+    if (STAGED && staged)
+    {
+      // 16 columns = one half of a 32-column box; every epilogue warp visits every box once
+      const uint32_t q = in->seq + (uint32_t)(c >> 1);
+      const uint32_t b = q & (uint32_t)(in->nbufs - 1);
+      const uint32_t par = (q / (uint32_t)in->nbufs) & 1u;
+      if (!mbar_wait(&in->full[b], par, in->abort_flag))
+        return;
+      const uint8_t* rowp = in->buf + (size_t)b * (128 * 128) + in->row * 128;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+      {
+        const int ch = (((c & 1) << 2) + i) ^ (in->row & 7);
+        const float4 x = *reinterpret_cast<const float4*>(rowp + ch * 16);
+        up[4 * i] = x.x, up[4 * i + 1] = x.y, up[4 * i + 2] = x.z, up[4 * i + 3] = x.w;
+      }
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0)
+        mbar_arrive(&in->empty[b]);
+    }
     tc_ld16(taddr + c * CW, v);
     if (tl >= 0 && c == grp && threadIdx.x == 64)
       trace_stamp(P, tl, 5);
@@ -520,15 +563,23 @@ struct Cfg
   static constexpr int B_BYTES = BN_LOCAL * TBK * 4;
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (THREE_X ? 2 : 1);
   // at most 8 stages: the barrier block after the ring is sized for that
-  static constexpr int STAGES_RAW = 196608 / STAGE_BYTES;
+  static constexpr int STAGES_RAW =
+      (196608 - ((PAIR && OP == TC_FWD && !THREE_X) ? 4 * BM * 32 * 4 : 0)) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW);
   static constexpr int EPI_WARPS = 8;
-  static constexpr int THREADS = (2 + EPI_WARPS + (THREE_X ? 4 : 0)) * 32;
+  static constexpr int THREADS =
+      (2 + EPI_WARPS + (THREE_X ? 4 : 0) + ((PAIR && OP == TC_FWD) ? 1 : 0)) * 32;
   // (Spreading the k-steps of a narrow tile over several accumulators was measured: it does not
   // shorten the main loop, whose per-k-block cost is the barrier/TMA handshake.)
   static constexpr int KSPLIT = 1;
   static constexpr int TMEM_COLS = 2 * BN * KSPLIT;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  // Pair-mode forward: the operand of the layer above (128 rows x 32 columns per box, 16 KB)
+  // arrives through IN_BUFS shared-memory buffers filled by a dedicated TMA warp.
+  static constexpr bool STAGE_IN = PAIR && OP == TC_FWD;
+  static constexpr int IN_BYTES = BM * 32 * 4;
+  static constexpr int IN_BUFS = STAGE_IN ? (THREE_X ? 2 : 4) : 0;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + IN_BUFS * IN_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
                                     ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TILE_M >> 4) << 24);
@@ -538,20 +589,23 @@ struct Cfg
 template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false>
 __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
     pc_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 const TcParams P)
+                 const __grid_constant__ CUtensorMap mapU, const TcParams P)
 {
   using C = Cfg<OP, BN, THREE_X, BM, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* in_base = smem + C::STAGES * C::STAGE_BYTES; // staged operand of the layer above
+  uint64_t* bars = reinterpret_cast<uint64_t*>(in_base + C::IN_BUFS * C::IN_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + C::STAGES;
   uint64_t* xf = bars + 2 * C::STAGES;
   uint64_t* tfull = bars + 3 * C::STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* in_full = tempty + 2;
+  uint64_t* in_empty = in_full + 4;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(in_empty + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -577,6 +631,11 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
     {
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], PAIR ? 2 * C::EPI_WARPS : C::EPI_WARPS);
+    }
+    for (int b = 0; b < C::IN_BUFS; ++b)
+    {
+      mbar_init(&in_full[b], 1);
+      mbar_init(&in_empty[b], C::EPI_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -845,16 +904,22 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
       if (OP == TC_FWD)
       {
         constexpr bool PF = !THREE_X;
+        constexpr bool SI = C::STAGE_IN;
+        InStage in;
+        in.buf = in_base, in.full = in_full, in.empty = in_empty;
+        in.seq = (uint32_t)tile_iter * (uint32_t)(BN / 32);
+        in.row = quarter * 32 + lane, in.nbufs = C::IN_BUFS > 0 ? C::IN_BUFS : 1;
+        in.abort_flag = abort_flag;
         switch (meta.act)
         {
         case DPC_ACT_TANH:
-          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active);
+          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF, SI>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
           break;
         case DPC_ACT_GELU:
-          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active);
+          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF, SI>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
           break;
         default:
-          fwd_epilogue_tile<-1, BN, GROUPS, false>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active);
+          fwd_epilogue_tile<-1, BN, GROUPS, false, SI>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
         }
       }
       else if (OP == TC_FB)
@@ -977,6 +1042,36 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
         atomicAdd(P.energy, (double)(0.5f * esum));
     }
   }
+  else if (C::STAGE_IN && warp == 2 + C::EPI_WARPS + (THREE_X ? 4 : 0))
+  {
+    // ---------------------------------------------------------------- staged-operand loader
+    // Brings this CTA's 128 rows of the layer above (belief or error) into shared memory, one
+    // 32-column box at a time, in the order the epilogue warps consume them.
+    if (lane == 0 && P.stage_in)
+    {
+      constexpr uint32_t NBUF = C::IN_BUFS > 0 ? C::IN_BUFS : 1;
+      uint32_t q = 0;
+      bool alive = true;
+      for (int t = t_begin; t < t_end && alive; t += t_step)
+      {
+        const int lrel = t / tiles_per_layer, rem = t % tiles_per_layer;
+        const int m0 = (rem / P.tiles_n) * C::TILE_M + (int)rank * BM;
+        const int n0 = (rem % P.tiles_n) * BN;
+        const int lcoord = P.first + lrel - P.run_first + 1;
+        for (int j = 0; j < BN / 32; ++j, ++q)
+        {
+          const uint32_t b = q & (NBUF - 1);
+          if (!mbar_wait(&in_empty[b], ((q / NBUF) & 1u) ^ 1u, abort_flag))
+          {
+            alive = false;
+            break;
+          }
+          mbar_expect_tx(&in_full[b], C::IN_BYTES);
+          tma_load_3d(in_base + b * C::IN_BYTES, &mapU, &in_full[b], n0 + 32 * j, m0, lcoord);
+        }
+      }
+    }
+  }
   else if (THREE_X)
   {
     // ---------------------------------------------------------------- remainder transform
@@ -1086,8 +1181,10 @@ bool make_map(CUtensorMap* map, const float* base, int cols, int rows, int layer
 }
 
 template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false>
-int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P)
+int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P,
+           const CUtensorMap* up = nullptr)
 {
+  const CUtensorMap& u = up ? *up : a; // unused unless P.stage_in
   using C = Cfg<OP, BN, THREE_X, BM, PAIR>;
   static bool configured = false;
   auto kern = pc_tc_kernel<OP, BN, THREE_X, BM, PAIR>;
@@ -1118,14 +1215,14 @@ int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b,
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, b, P);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, b, u, P);
     p->ctx->launches += 1;
     if (e != cudaSuccess)
       return cuda_fail(e, "tensor-core pair kernel launch");
     return DPC_OK;
   }
   const int grid = P.chain ? P.tiles_m * P.tiles_n : std::min(total, p->ctx->sm_count);
-  kern<<<grid, C::THREADS, C::SMEM_BYTES, p->ctx->stream>>>(a, b, P);
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, p->ctx->stream>>>(a, b, u, P);
   p->ctx->launches += 1;
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess)
@@ -1215,6 +1312,26 @@ int tc_plan_init(dpc_plan* plan)
   ok &= make_map(&st->w_mn, L0.W, H, H, best_count, plan->run.w_stride, 32, true);
   if (!ok)
     return DPC_OK; // the driver refused a tensor map: stay on the CUDA-core path
+  {
+    // Maps over beliefs and errors that also cover the layer above the run's last layer (it
+    // has the run's width, and sits one stride further when the arenas are contiguous).
+    const int top = best_first + best_count;
+    bool fits = top < n && best_count >= 1 && plan->h[top].size == H && plan->h[top].e &&
+                ((uintptr_t)L0.e % 128 == 0);
+    if (fits && best_count >= 2)
+    {
+      const int64_t es = plan->h[best_first + 1].e - L0.e;
+      fits = es == plan->run.z_stride;
+      for (int j = best_first + 1; fits && j <= top; ++j)
+        fits = plan->h[j].z - plan->h[j - 1].z == plan->run.z_stride &&
+               plan->h[j].e - plan->h[j - 1].e == es;
+    }
+    else if (fits)
+      fits = plan->h[top].z - L0.z == plan->run.z_stride && plan->h[top].e - L0.e == plan->run.z_stride;
+    if (fits)
+      st->up_maps = make_map(&st->zup_km, L0.z, H, B, best_count + 1, plan->run.z_stride, TBM, false) &&
+                    make_map(&st->eup_km, L0.e, H, B, best_count + 1, plan->run.z_stride, TBM, false);
+  }
   if (cudaMalloc(&st->chain_counters, sizeof(int) * (size_t)best_count * (B / 64)) != cudaSuccess ||
       cudaMalloc(&st->error_flag, sizeof(int)) != cudaSuccess ||
       cudaMemset(st->error_flag, 0, sizeof(int)) != cudaSuccess ||
@@ -1297,6 +1414,7 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
   P.chain_counters = nullptr;
   P.chain_target = 0;
   P.trace = nullptr;
+  P.stage_in = 0;
   return P;
 }
 
@@ -1310,8 +1428,21 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
   if (pair_ok(B, H))
   {
     TcParams P = base_params(p, st, first, count, B, H, H, 256, flags, 0, 256);
-    return tf32 ? launch<TC_FWD, 256, false, 128, true>(p, st, st->z_km, st->w_km128, P)
-                : launch<TC_FWD, 256, true, 128, true>(p, st, st->z_km, st->w_km128, P);
+    // What the epilogue reads from the layer above is the same for every layer of the launch
+    // unless a softmax head sits right above the range: stage it through shared memory.
+    const CUtensorMap* up = nullptr;
+    bool ce = false;
+    for (int i = first; i <= first + count && i < p->n; ++i)
+      ce |= (p->h[i].flags & DPC_LAYER_SOFTMAX_CE) != 0;
+    if (st->up_maps && !ce && !getenv("DPC_DISABLE_STAGED_INPUT"))
+    {
+      if ((flags & DPC_FWD_ERR_NEXT) && !(flags & DPC_FWD_COPY_NEXT))
+        P.stage_in = 1, up = &st->zup_km;
+      else if ((flags & DPC_FWD_FE) && !(flags & DPC_FWD_ERR_NEXT))
+        P.stage_in = 2, up = &st->eup_km;
+    }
+    return tf32 ? launch<TC_FWD, 256, false, 128, true>(p, st, st->z_km, st->w_km128, P, up)
+                : launch<TC_FWD, 256, true, 128, true>(p, st, st->z_km, st->w_km128, P, up);
   }
   if (tf32)
     return launch<TC_FWD, 256, false>(p, st, st->z_km, st->w_km256,
