@@ -522,7 +522,7 @@ int dpc_project_forward(dpc_plan* p, int first, int count, int skip_last_copy)
 
 int dpc_project_forward_ex(dpc_plan* p, int first, int count, int skip_last_copy, int extra)
 {
-  extra &= DPC_FWD_NO_MU;
+  extra &= DPC_FWD_NO_MU | DPC_FWD_NO_PREACT;
   int rc = check_range(p, first, count);
   if (rc != DPC_OK)
     return rc;
@@ -720,6 +720,56 @@ static int weight_gemm_simt(dpc_plan* p, int first, int count, int mode, int fla
   return DPC_OK;
 }
 
+// The DFA projection over layers [first, first+count): four-units-per-thread kernel where the
+// shapes allow it, the general kernel elsewhere.
+static int launch_dfa_proj(dpc_plan* p, int first, int count, int from_output)
+{
+  cudaStream_t st = p->ctx->stream;
+  auto vec_ok = [&](int i)
+  {
+    const dpc_layer& L = p->h[i];
+    return L.next_size > 0 && L.next_size % 4 == 0 && L.terminal_size <= 16 &&
+           ((uintptr_t)L.fe % 16 == 0) && ((uintptr_t)L.preact % 16 == 0) &&
+           (i + 1 >= p->n || (uintptr_t)p->h[i + 1].z % 16 == 0);
+  };
+  int i = first;
+  while (i < first + count)
+  {
+    const bool v = vec_ok(i);
+    int j = i + 1;
+    while (j < first + count && j - i < kMaxZ && vec_ok(j) == v &&
+           (!v || p->h[j].terminal_size == p->h[i].terminal_size))
+      ++j;
+    const int c = j - i;
+    int mxn = 1;
+    for (int k = i; k < j; ++k)
+      mxn = std::max(mxn, p->h[k].next_size);
+    if (v)
+    {
+      dim3 grid(cdiv(mxn, 256), cdiv(p->batch, DFA_ROWS), c);
+      const int ts4 = cdiv(std::max(p->h[i].terminal_size, 1), 4);
+      if (ts4 <= 1)
+        dfa_proj4_kernel<1><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+      else if (ts4 == 2)
+        dfa_proj4_kernel<2><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+      else if (ts4 == 3)
+        dfa_proj4_kernel<3><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+      else
+        dfa_proj4_kernel<4><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+    }
+    else
+    {
+      dim3 grid(cdiv(mxn, 128), cdiv(p->batch, DFA_ROWS), c);
+      dfa_proj_kernel<<<grid, 128, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+    }
+    int rc = check_launch(p->ctx, "dfa_proj kernel");
+    if (rc != DPC_OK)
+      return rc;
+    i = j;
+  }
+  return DPC_OK;
+}
+
 int dpc_direct_feedback(dpc_plan* p, int first, int count, int decay_w)
 {
   int rc = check_range(p, first, count);
@@ -730,18 +780,9 @@ int dpc_direct_feedback(dpc_plan* p, int first, int count, int decay_w)
     count -= 1;
   if (count <= 0)
     return DPC_OK;
-  cudaStream_t st = p->ctx->stream;
-  for (int f = first; f < first + count; f += kMaxZ)
-  {
-    const int c = std::min(kMaxZ, first + count - f);
-    int mxn = 1;
-    for (int i = f; i < f + c; ++i)
-      mxn = std::max(mxn, p->h[i].next_size);
-    dim3 grid(cdiv(mxn, 128), cdiv(p->batch, DFA_ROWS), c);
-    dfa_proj_kernel<<<grid, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal);
-    if ((rc = check_launch(p->ctx, "dfa_proj kernel")) != DPC_OK)
-      return rc;
-  }
+  if ((rc = launch_dfa_proj(p, first, count, (decay_w & DPC_DFA_FROM_OUTPUT) ? 1 : 0)) != DPC_OK)
+    return rc;
+  decay_w &= DPC_DFA_DECAY_W;
   const int flags = decay_w ? 1 : 0;
   if (!decay_w)
   {
@@ -844,17 +885,8 @@ int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
   cudaStream_t st = p->ctx->stream;
   if (which == 1)
   {
-    for (int f = first; f < first + count; f += kMaxZ)
-    {
-      const int c = std::min(kMaxZ, first + count - f);
-      int mxn = 1;
-      for (int i = f; i < f + c; ++i)
-        mxn = std::max(mxn, p->h[i].next_size);
-      dim3 grid(cdiv(mxn, 128), cdiv(p->batch, DFA_ROWS), c);
-      dfa_proj_kernel<<<grid, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal);
-      if ((rc = check_launch(p->ctx, "dfa_proj kernel")) != DPC_OK)
-        return rc;
-    }
+    if ((rc = launch_dfa_proj(p, first, count, 0)) != DPC_OK)
+      return rc;
     return weight_gemm_simt(p, first, count, WG_DFA | WG_GRAD_ONLY, 0);
   }
   if ((rc = weight_gemm_simt(p, first, count, WG_LEARN | WG_GRAD_ONLY, 0)) != DPC_OK)

@@ -91,6 +91,30 @@ __device__ __forceinline__ float act_deriv(int act, float z)
   }
 }
 
+// f'(preact) recovered from the activation value f(preact) itself, bit-identical to
+// act_deriv(act, preact) for the activations where that is possible (see act_has_output_deriv).
+__device__ __host__ __forceinline__ bool act_has_output_deriv(int act)
+{
+  return act == DPC_ACT_TANH || act == DPC_ACT_SIGMOID || act == DPC_ACT_RELU ||
+         act == DPC_ACT_LINEAR || act == DPC_ACT_HARD_TANH;
+}
+__device__ __forceinline__ float act_deriv_from_output(int act, float f)
+{
+  switch (act)
+  {
+  case DPC_ACT_TANH:
+    return 1.0f - f * f;
+  case DPC_ACT_SIGMOID:
+    return f * (1.0f - f);
+  case DPC_ACT_RELU:
+    return f > 0.0f ? 1.0f : 0.0f;
+  case DPC_ACT_HARD_TANH:
+    return (f > -1.0f && f < 1.0f) ? 1.0f : 0.0f;
+  default:
+    return 1.0f;
+  }
+}
+
 // Activation and derivative together (one transcendental for tanh / sigmoid / gelu).
 __device__ __forceinline__ void act_both(int act, float z, float& f, float& d)
 {

@@ -295,9 +295,10 @@ __global__ void __launch_bounds__(NTHREADS)
         }
         if (!(flags & DPC_FWD_TRANSIENT))
         {
-          if (L.preact)
+          const bool no_mu = do_copy && (flags & DPC_FWD_NO_MU);
+          if (L.preact && !(no_mu && (flags & DPC_FWD_NO_PREACT)))
             L.preact[o] = pre;
-          if (!(do_copy && (flags & DPC_FWD_NO_MU)))
+          if (!no_mu)
             L.mu[o] = mu;
         }
         if (do_copy)
@@ -606,7 +607,7 @@ __global__ void relax_kernel(const dpc_layer* __restrict__ layers, int first, in
 // rows whose terminal errors sit in shared memory, so preact/fe stream through coalesced.
 constexpr int DFA_ROWS = 32;
 __global__ void dfa_proj_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
-                                int batch, const float* __restrict__ eT)
+                                int batch, const float* __restrict__ eT, int from_output)
 {
   const int li = first + blockIdx.z;
   if (li + 1 >= n_layers)
@@ -658,10 +659,77 @@ __global__ void dfa_proj_kernel(const dpc_layer* __restrict__ layers, int first,
         if (kc > 0)
           acc += L.fe[o];
         if (last)
-          acc *= act_deriv(L.act, L.preact[o]);
+          acc *= (from_output && act_has_output_deriv(L.act))
+                     ? act_deriv_from_output(L.act, Lup.z[o])
+                     : act_deriv(L.act, L.preact[o]);
         L.fe[o] = acc;
       }
     }
+  }
+}
+
+// The same projection, four output units per thread with 128-bit accesses, for the common
+// aligned case: next_size a multiple of 4, terminal_size <= 4*TS4, 16-byte aligned rows.
+template <int TS4>
+__global__ void __launch_bounds__(64)
+    dfa_proj4_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
+                     const float* __restrict__ eT, int from_output)
+{
+  const int li = first + blockIdx.z;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  const dpc_layer Lup = layers[li + 1];
+  if (L.next_size <= 0 || Lup.Psi == nullptr)
+    return;
+  const int TS = L.terminal_size, n = L.next_size;
+  const int b0 = blockIdx.y * DFA_ROWS;
+  const int j = (blockIdx.x * 64 + threadIdx.x) * 4;
+  if (b0 >= batch || (int)(blockIdx.x * 256) >= n)
+    return;
+  __shared__ __align__(16) float es[DFA_ROWS][TS4 * 4];
+  for (int idx = threadIdx.x; idx < DFA_ROWS * TS4 * 4; idx += 64)
+  {
+    const int r = idx / (TS4 * 4), k = idx - r * (TS4 * 4);
+    es[r][k] = (b0 + r < batch && k < TS) ? eT[(size_t)(b0 + r) * TS + k] : 0.0f;
+  }
+  __syncthreads();
+  if (j >= n)
+    return;
+  float psi[4][TS4 * 4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int k = 0; k < TS4 * 4; ++k)
+      psi[c][k] = k < TS ? Lup.Psi[(size_t)(j + c) * Lup.psi_stride + k] : 0.0f;
+  const bool out_d = from_output && act_has_output_deriv(L.act);
+  const float* src = out_d ? Lup.z : L.preact;
+  const int rows = min(DFA_ROWS, batch - b0);
+#pragma unroll 4
+  for (int r = 0; r < rows; ++r)
+  {
+    const size_t o = (size_t)(b0 + r) * n + j;
+    const float4 s4 = *reinterpret_cast<const float4*>(src + o);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int k4 = 0; k4 < TS4; ++k4)
+    {
+      const float4 e4 = *reinterpret_cast<const float4*>(&es[r][k4 * 4]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+      {
+        acc[c] = fmaf(e4.x, psi[c][k4 * 4], acc[c]);
+        acc[c] = fmaf(e4.y, psi[c][k4 * 4 + 1], acc[c]);
+        acc[c] = fmaf(e4.z, psi[c][k4 * 4 + 2], acc[c]);
+        acc[c] = fmaf(e4.w, psi[c][k4 * 4 + 3], acc[c]);
+      }
+    }
+    const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+    float out[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      out[c] = acc[c] * (out_d ? act_deriv_from_output(L.act, sv[c]) : act_deriv(L.act, sv[c]));
+    *reinterpret_cast<float4*>(L.fe + o) = make_float4(out[0], out[1], out[2], out[3]);
   }
 }
 

@@ -493,7 +493,8 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
       }
       if (store && active)
       {
-        st8(L.preact + o + k, pre);
+        if (!(no_mu && (P.flags & DPC_FWD_NO_PREACT)))
+          st8(L.preact + o + k, pre);
         if (!no_mu)
           st8(L.mu + o + k, mu);
       }

@@ -554,8 +554,10 @@ void PCNetwork::ProjectForward()
   {
     // Inside a whole train step only the clamped input layer's mu is read again before it is
     // recomputed (its cached prediction); the others skip the store.
-    Check(dpc_project_forward_ex(plan, 0, n - 1, layers.back()->clamped ? 1 : 0,
-                                 transientFlag ? DPC_FWD_NO_MU : 0));
+    int extra = transientFlag ? DPC_FWD_NO_MU : 0;
+    if (extra && sweepFeedsDfa)
+      extra |= DPC_FWD_NO_PREACT; // the direct-feedback update takes f' from the copied outputs
+    Check(dpc_project_forward_ex(plan, 0, n - 1, layers.back()->clamped ? 1 : 0, extra));
     for (int i = 0; i < n - 1; ++i)
       if (layers[i]->clamped)
         layers[i]->cacheValid = true;
@@ -583,12 +585,13 @@ void PCNetwork::DirectFeedbackUpdate()
     // Refresh preact against the settled z first (src/networks/FullPCNetwork.cpp:72-82).
     ForwardRange(0, n - 1, 0);
   }
-  const int decayW = kind == NetworkKind::FULL ? 1 : 0;
+  const int decayW = (kind == NetworkKind::FULL ? DPC_DFA_DECAY_W : 0) |
+                     (sweepFeedsDfa && !gradSync ? DPC_DFA_FROM_OUTPUT : 0);
   if (gradSync)
   {
     Check(dpc_weight_gradients(plan, 0, n - 1, 1));
     SyncGradients(gradWCount);
-    Check(dpc_apply_gradients(plan, 0, n - 1, 1, globalBatch, decayW));
+    Check(dpc_apply_gradients(plan, 0, n - 1, 1, globalBatch, decayW & DPC_DFA_DECAY_W));
   }
   else
     Check(dpc_direct_feedback(plan, 0, n - 1, decayW));
@@ -611,8 +614,9 @@ float PCNetwork::CalculateState(bool needEnergy)
   RequireCompiled();
   const int n = (int)layers.size();
   Check(dpc_zero(ctx, layers[0]->d.e, (size_t)batchSize * layers[0]->d.size * sizeof(float)));
-  int flags = StateFlags(kind, needEnergy) | (needEnergy ? 0 : transientFlag);
-  // The energy pass that closes a train step is followed by no state update: nobody reads fe.
+  int flags = StateFlags(kind, needEnergy) | transientFlag;
+  // The energy pass that closes a train step is followed by no state update: nobody reads fe,
+  // and its predictions are written only if somebody asks for them (RefreshPredictions).
   if (needEnergy && transientFlag)
     flags &= ~DPC_FWD_FE;
   ForwardRange(0, n - 1, flags);
@@ -723,6 +727,18 @@ struct TransientScope
   ~TransientScope() { flag = 0; }
 };
 
+// The last pass of a train step computes every layer's prediction for the energy but does not
+// store it; whoever wants to look at mu / preact afterwards gets them recomputed here from the
+// same beliefs and weights (a clamped layer keeps its cached prediction, as in the reference).
+void PCNetwork::RefreshPredictions()
+{
+  if (!predictionsStale || !plan)
+    return;
+  predictionsStale = false;
+  ForwardRange(0, (int)layers.size() - 1, 0);
+  Check(dpc_sync(ctx));
+}
+
 void PCNetwork::RunTrainPhases(int mode, int steps)
 {
   const int n = (int)layers.size();
@@ -735,9 +751,23 @@ void PCNetwork::RunTrainPhases(int mode, int steps)
   };
   if (kind == NetworkKind::DIRECT_KP)
   {
+    // The direct-feedback update follows the sweep at once: z[l+1] still equals f(preact[l]),
+    // so it can take f' from z[l+1] and the sweep need not store preact -- when every
+    // activation's derivative is a function of its output and no gradient staging is on.
+    bool fromOutput = !gradSync && !ghostTop;
+    for (int i = 0; i + 1 < n && fromOutput; ++i)
+    {
+      const int a = layers[i]->d.act;
+      fromOutput = a == DPC_ACT_TANH || a == DPC_ACT_SIGMOID || a == DPC_ACT_RELU ||
+                   a == DPC_ACT_LINEAR || a == DPC_ACT_HARD_TANH;
+      for (int k = 1; k + 1 < n; ++k)
+        fromOutput = fromOutput && !layers[k]->clamped;
+    }
+    sweepFeedsDfa = fromOutput;
     ProjectForward();
     CalculateTerminalError();
     DirectFeedbackUpdate();
+    sweepFeedsDfa = false;
     for (int t = 0; t < steps; ++t)
       settle(false);
     UpdateWeights();
@@ -804,6 +834,7 @@ float PCNetwork::TrainStepRaw(int mode, const float* x, size_t nx, const float* 
     mode = 0;
   SyncPlan();
   const int n = (int)layers.size();
+  predictionsStale = false; // everything is recomputed from here on
   ResetState();
   if (onDevice)
   {
@@ -847,6 +878,9 @@ float PCNetwork::TrainStepRaw(int mode, const float* x, size_t nx, const float* 
   }
   else
     RunTrainPhases(mode, steps);
+  // (same condition as the TransientScope of RunTrainPhases; a graph replay runs no host code)
+  predictionsStale =
+      kind != NetworkKind::SIMPLE && !(layers.back()->d.flags & DPC_LAYER_SOFTMAX_CE);
 
   double energy = 0.0;
   if (readEnergy)
@@ -897,6 +931,7 @@ void PCNetwork::PredictRaw(const float* x, size_t nx, int steps, bool withProjec
     throw std::invalid_argument("deepity_b200: Predict() output buffer has the wrong size");
   if (kind != NetworkKind::SIMPLE)
     withProjection = true;
+  predictionsStale = false;
   ResetState();
   ClampHost(0, x, nx);
   for (int i = 1; i < n; ++i)
@@ -1123,6 +1158,8 @@ bool PCNetwork::FindTensor(int layer, const std::string& name, float** ptr, size
     p = ghostET, r = B, c = ts;
   else if (n > 0)
   {
+    if (name == "mu" || name == "preact")
+      RefreshPredictions();
     if (name == "mu")
       p = d.mu, r = B, c = n;
     else if (name == "preact")

@@ -168,8 +168,13 @@ public:
   dpc_ctx* Context() noexcept { return ctx; }
   dpc_plan* Plan() noexcept { return plan; }
   bool IsCompiled() const noexcept { return plan != nullptr; }
-  // Re-uploads the layer table if a setter changed it since the last step.
-  void FlushSettings() { SyncPlan(); }
+  // Re-uploads the layer table if a setter changed it since the last step and brings lazily
+  // skipped predictions up to date.
+  void FlushSettings()
+  {
+    SyncPlan();
+    RefreshPredictions(); // whoever drives single phases next expects mu / preact in memory
+  }
   int64_t LaunchCount() const;
   double TrainStepFlops(int steps) const;
 
@@ -184,6 +189,7 @@ private:
   void SyncPlan();
   void EnsureOptimizerState();
   void EnsureGradientStaging();
+  void RefreshPredictions();
   void SyncGradients(size_t count);
   void ForwardRange(int first, int count, int flags);
   void RunTrainPhases(int mode, int steps);
@@ -211,6 +217,8 @@ private:
   int globalBatch = 0;
   float* gradBuffer = nullptr; // [g_W of every layer | g_b | g_Psi], each padded to 64 floats
   size_t gradCount = 0, gradWCount = 0;
+  bool predictionsStale = false; // mu / preact in memory are older than the last energy pass
+  bool sweepFeedsDfa = false; // inside a DirectKP train step, between sweep and direct feedback
   int transientFlag = 0; // DPC_FWD_TRANSIENT while a whole train step is being issued
   // key of the graph captured in slot s: mode*1e6+steps (train) or steps (predict); -1 none
   long graphKey[4] = {-1, -1, -1, -1};

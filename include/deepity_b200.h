@@ -196,6 +196,9 @@ enum
                                  cached prediction, DirectKPPCLayer.cpp:275-280)          */
   DPC_FWD_NO_MU = 1 << 9,     /* with COPY_NEXT: mu[l] itself is not written (z[l+1] holds the
                                  same values and mu is recomputed before anyone reads it)  */
+  DPC_FWD_NO_PREACT = 1 << 11, /* with COPY_NEXT and NO_MU: preact[l] is not written either (the
+                                 next reader, dpc_direct_feedback with DPC_DFA_FROM_OUTPUT,
+                                 takes f'(preact[l]) from z[l+1] = f(preact[l]))           */
   DPC_FWD_TRANSIENT = 1 << 8  /* preact/mu of this pass are consumed only through the fused
                                  e/fe outputs and recomputed before anyone reads them: do
                                  not write them to memory                                  */
@@ -239,8 +242,16 @@ DPC_API int dpc_epc_adjoint(dpc_plan* plan, int layer, int from_terminal, float 
 DPC_API int dpc_relax(dpc_plan* plan, int layer);
 /* DirectFeedbackUpdate for every layer of the range whose upper neighbour has Psi:
  * proj = (e_T·Psi[l+1]ᵀ) * f'(preact[l]);  W[l] += (fl*a/B) projᵀ·z[l]
- * (DirectKPPCLayer.cpp:503-549, FullPCLayer.cpp:514-572; decay_w applies the FullPC
- * (1-lmbda) pre-scale). */
+ * (DirectKPPCLayer.cpp:503-549, FullPCLayer.cpp:514-572).  decay_w is a bit set: bit 0
+ * applies the FullPC (1-lmbda) pre-scale; bit 1 (DPC_DFA_FROM_OUTPUT) tells that z[l+1]
+ * still equals f(preact[l]) for the layers of the range (the call follows the forward sweep
+ * directly), so f' is taken from z[l+1] where the activation allows it -- same values, one
+ * transcendental less per element, and preact need not have been stored. */
+enum
+{
+  DPC_DFA_DECAY_W = 1,
+  DPC_DFA_FROM_OUTPUT = 2
+};
 DPC_API int dpc_direct_feedback(dpc_plan* plan, int first, int count, int decay_w);
 /* UpdateWeights for every layer of the range from fe[l] (DirectKP/Full) or e[l+1]
  * (Simple): W, b and Psi with SGD / Adam / AdamW, optional row centring
