@@ -1067,6 +1067,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
             alive = false;
             break;
           }
+          // order the epilogue warps' (generic-proxy) reads of this buffer before the copy
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           mbar_expect_tx(&in_full[b], C::IN_BYTES);
           tma_load_3d(in_base + b * C::IN_BYTES, &mapU, &in_full[b], n0 + 32 * j, m0, lcoord);
         }

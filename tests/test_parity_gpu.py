@@ -143,6 +143,17 @@ def test_tensor_core_path_tf32_bound(name, built_library):
     compare_outputs(run_oracle(case), run_gpu(case, precision="tf32"), TF32_TOL, name)
 
 
+def test_deep_stack_at_benchmark_layer_shape(built_library):
+    """48 layers of the deep-stack benchmark's shape (batch 1024, width 512): many tiles per
+    CTA through the persistent pair kernels, the staged epilogue operands and the sequential
+    sweep -- the place where a pipeline race would show."""
+    case = dict(kind="dkp", sizes=[512] + [512] * 48 + [10], batch=1024, T=2, steps=2, seed=3,
+                hyper=dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.0, act="tanh"))
+    ref = run_oracle(case)
+    compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "deep stack fp32")
+    compare_outputs(ref, run_gpu(case, precision="tf32"), TF32_TOL, "deep stack tf32")
+
+
 def test_training_continues_to_track_the_oracle(built_library):
     """Ten consecutive steps: errors must not accumulate beyond the bound."""
     case = dict(kind="dkp", sizes=[32, 64, 64, 64, 10], batch=32, T=2, steps=10,
