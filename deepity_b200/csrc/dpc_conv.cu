@@ -52,7 +52,8 @@ __device__ __forceinline__ void block_energy(float local, double* energy)
 template <int OP>
 __global__ void __launch_bounds__(THREADS)
     conv_gemm_kernel(const dpc_conv_layer L, float* __restrict__ z_up, float* __restrict__ e_up,
-                     int batch, int flags, double* energy, int k_chunk)
+                     int batch, int flags, double* energy, int k_chunk,
+                     float* __restrict__ split_out = nullptr)
 {
   const int C = L.in_c, O = L.out_c, H = L.in_h, Wd = L.in_w, kH = L.k_h, kW = L.k_w;
   const int oH = L.out_h, oW = L.out_w, P = oH * oW, HW = H * Wd, KK = kH * kW;
@@ -65,8 +66,11 @@ __global__ void __launch_bounds__(THREADS)
   else
     M = O, N = rows, K = batch * P;
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  // k_chunk > 0: the reduction is split over blockIdx.z and the partial sums are added
+  // atomically into a zeroed buffer (g_W for the weight gradient, preact for the forward
+  // product, `split_out` for the state update); a second kernel applies the epilogue.
   int k_begin = 0, k_end = K;
-  if (OP == C_WG)
+  if (k_chunk > 0)
   {
     k_begin = blockIdx.z * k_chunk;
     k_end = min(K, k_begin + k_chunk);
@@ -241,6 +245,28 @@ __global__ void __launch_bounds__(THREADS)
   }
 
   // ------------------------------------------------------------------ epilogues
+  if (OP != C_WG && k_chunk > 0)
+  {
+    float* dst = OP == C_FWD ? L.preact : split_out;
+    const int PP = OP == C_FWD ? P : HW; // pixels per (image, channel) plane of the output
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+      const int m = m0 + ty * 4 + i;
+      if (m >= M)
+        continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+      {
+        const int n = n0 + tx * 4 + j;
+        if (n >= N)
+          continue;
+        const int b = n / PP, q = n - b * PP;
+        atomicAdd(&dst[((size_t)b * M + m) * PP + q], acc[i][j]);
+      }
+    }
+    return;
+  }
   if (OP == C_FWD)
   {
     float esum = 0.0f;
@@ -315,6 +341,48 @@ __global__ void __launch_bounds__(THREADS)
       }
     }
   }
+}
+
+// Second half of a split forward product: preact holds the raw sums; bias, activation, the
+// error of the layer above, the gated error and the energy as in the fused epilogue.
+__global__ void conv_forward_finish_kernel(const dpc_conv_layer L, float* __restrict__ z_up,
+                                           float* __restrict__ e_up, int batch, int flags,
+                                           double* energy)
+{
+  const int P = L.out_h * L.out_w;
+  const size_t total = (size_t)batch * L.out_c * P;
+  float esum = 0.0f;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+       o += (size_t)gridDim.x * blockDim.x)
+  {
+    const int oc = (int)((o / P) % L.out_c);
+    const float pre = L.preact[o] + L.b[oc];
+    float mu, d;
+    act_both(L.act, pre, mu, d);
+    L.preact[o] = pre;
+    L.mu[o] = mu;
+    if (flags & DPC_CONV_COPY_NEXT)
+      z_up[o] = mu;
+    if (flags & DPC_CONV_ERR_NEXT)
+    {
+      const float e = ((flags & DPC_CONV_COPY_NEXT) ? mu : z_up[o]) - mu;
+      e_up[o] = e;
+      esum += e * e;
+      L.g[o] = e * d;
+    }
+  }
+  if (flags & DPC_CONV_ENERGY)
+    block_energy(esum, energy);
+}
+
+// Second half of a split state update: z += ir*(dz - e) with dz = the summed partials.
+__global__ void conv_state_finish_kernel(const dpc_conv_layer L, const float* __restrict__ dz,
+                                         int batch)
+{
+  const size_t total = (size_t)batch * L.in_c * L.in_h * L.in_w;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+       o += (size_t)gridDim.x * blockDim.x)
+    L.z[o] += L.ir * (dz[o] - L.e[o]);
 }
 
 // A clamped layer whose prediction is cached: no convolution, preact/mu are read back.
@@ -477,10 +545,30 @@ struct dpc_conv_plan
   std::vector<dpc_conv_layer> h;
   double* energy = nullptr;
   double* energy_host = nullptr;
+  float* scratch = nullptr; // one state-sized buffer for split state updates (largest layer)
+  size_t scratch_floats = 0;
 };
 
 namespace
 {
+// How many ways to split a reduction of length K over CTAs when the tile grid alone does not
+// fill the GPU (returns 1 for "do not split"); k_chunk comes back as a multiple of TK.
+int choose_split(int tiles, long long K, int sm_count, int* k_chunk)
+{
+  int splits = 1;
+  if (tiles < sm_count && K >= 8 * TK)
+    splits = (int)std::min<long long>((2LL * sm_count + tiles - 1) / tiles, K / (2 * TK));
+  if (splits <= 1)
+  {
+    *k_chunk = 0;
+    return 1;
+  }
+  long long chunk = (K + splits - 1) / splits;
+  chunk = (chunk + TK - 1) / TK * TK;
+  *k_chunk = (int)chunk;
+  return (int)((K + chunk - 1) / chunk);
+}
+
 int conv_check_launch(dpc_ctx* ctx, const char* what)
 {
   ctx->launches += 1;
@@ -565,6 +653,16 @@ int dpc_conv_plan_create(dpc_ctx* ctx, const dpc_conv_layer* layers, int n_layer
     return cuda_fail(cudaGetLastError(), "conv plan allocation");
   }
   cudaMemset(p->energy, 0, sizeof(double));
+  for (int i = 0; i < n_layers; ++i)
+    p->scratch_floats = std::max(p->scratch_floats, (size_t)batch * layers[i].in_c *
+                                                        layers[i].in_h * layers[i].in_w);
+  if (cudaMalloc(&p->scratch, p->scratch_floats * sizeof(float)) != cudaSuccess)
+  {
+    cudaFree(p->energy);
+    cudaFreeHost(p->energy_host);
+    delete p;
+    return cuda_fail(cudaGetLastError(), "conv plan scratch allocation");
+  }
   *out = p;
   return DPC_OK;
 }
@@ -590,6 +688,8 @@ int dpc_conv_plan_destroy(dpc_conv_plan* p)
     cudaFree(p->energy);
   if (p->energy_host)
     cudaFreeHost(p->energy_host);
+  if (p->scratch)
+    cudaFree(p->scratch);
   delete p;
   return DPC_OK;
 }
@@ -615,6 +715,21 @@ int dpc_conv_forward(dpc_conv_plan* p, int layer, int flags)
   }
   const long long N = (long long)p->batch * L.out_h * L.out_w;
   dim3 grid(cdiv_i(N, TN), cdiv_i(L.out_c, TM), 1);
+  int k_chunk = 0;
+  const int splits = choose_split((int)(grid.x * grid.y), (long long)L.in_c * L.k_h * L.k_w,
+                                  p->ctx->sm_count, &k_chunk);
+  if (splits > 1)
+  {
+    grid.z = splits;
+    DPC_CUDA(cudaMemsetAsync(L.preact, 0, outs * sizeof(float), st));
+    conv_gemm_kernel<C_FWD><<<grid, THREADS, 0, st>>>(L, U.z, U.e, p->batch, flags, p->energy,
+                                                     k_chunk);
+    if ((rc = conv_check_launch(p->ctx, "conv forward kernel (split)")) != DPC_OK)
+      return rc;
+    conv_forward_finish_kernel<<<elem_grid(p, outs), THREADS, 0, st>>>(L, U.z, U.e, p->batch, flags,
+                                                                      p->energy);
+    return conv_check_launch(p->ctx, "conv forward finish kernel");
+  }
   conv_gemm_kernel<C_FWD><<<grid, THREADS, 0, st>>>(L, U.z, U.e, p->batch, flags, p->energy, 0);
   return conv_check_launch(p->ctx, "conv forward kernel");
 }
@@ -634,6 +749,20 @@ int dpc_conv_update_state(dpc_conv_plan* p, int layer)
   }
   const long long N = (long long)p->batch * L.in_h * L.in_w;
   dim3 grid(cdiv_i(N, TN), cdiv_i(L.in_c, TM), 1);
+  int k_chunk = 0;
+  const int splits = choose_split((int)(grid.x * grid.y), (long long)L.out_c * L.k_h * L.k_w,
+                                  p->ctx->sm_count, &k_chunk);
+  if (splits > 1)
+  {
+    grid.z = splits;
+    DPC_CUDA(cudaMemsetAsync(p->scratch, 0, ins * sizeof(float), st));
+    conv_gemm_kernel<C_BWD><<<grid, THREADS, 0, st>>>(L, nullptr, nullptr, p->batch, 0, p->energy,
+                                                     k_chunk, p->scratch);
+    if ((rc = conv_check_launch(p->ctx, "conv state update kernel (split)")) != DPC_OK)
+      return rc;
+    conv_state_finish_kernel<<<elem_grid(p, ins), THREADS, 0, st>>>(L, p->scratch, p->batch);
+    return conv_check_launch(p->ctx, "conv state finish kernel");
+  }
   conv_gemm_kernel<C_BWD><<<grid, THREADS, 0, st>>>(L, nullptr, nullptr, p->batch, 0, p->energy, 0);
   return conv_check_launch(p->ctx, "conv state update kernel");
 }

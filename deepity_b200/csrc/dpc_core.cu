@@ -784,13 +784,9 @@ int dpc_direct_feedback(dpc_plan* p, int first, int count, int decay_w)
     return rc;
   decay_w &= DPC_DFA_DECAY_W;
   const int flags = decay_w ? 1 : 0;
-  if (!decay_w)
-  {
-    return dispatch_range(
-        p, first, count, [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_DFA); },
-        [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA, flags); });
-  }
-  return weight_gemm_simt(p, first, count, WG_DFA, flags);
+  return dispatch_range(
+      p, first, count, [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_DFA, decay_w); },
+      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA, flags); });
 }
 
 int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
@@ -821,12 +817,35 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
   }
   rc = dispatch_range(
       p, first, count,
-      [&](int f, int c)
+      [&](int f, int c) -> int
       {
+        bool all_sgd = true, all_staged = true;
         for (int i = f; i < f + c; ++i)
-          if (p->h[i].opt != DPC_OPT_SGD)
-            return 1;
-        return tc_weight_gemm(p, f, c, WG_LEARN);
+        {
+          all_sgd &= p->h[i].opt == DPC_OPT_SGD;
+          all_staged &= p->h[i].g_W != nullptr;
+        }
+        if (all_sgd)
+          return tc_weight_gemm(p, f, c, WG_LEARN);
+        if (!all_staged)
+          return 1;
+        // Adam-type optimizers: tensor-core product into the staging buffer, then the
+        // optimizer as an elementwise kernel over W (b and Psi follow below as usual).
+        int r = tc_weight_gemm(p, f, c, WG_LEARN | WG_GRAD_ONLY);
+        if (r != DPC_OK)
+          return r;
+        size_t max_w = 1;
+        for (int i = f; i < f + c; ++i)
+          max_w = std::max(max_w, (size_t)p->h[i].next_size * p->h[i].size);
+        for (int g = f; g < f + c; g += kMaxZ)
+        {
+          const int cc = std::min(kMaxZ, f + c - g);
+          dim3 grid(elem_blocks(p, max_w), cc);
+          apply_gradients_kernel<<<grid, NTHREADS, 0, p->ctx->stream>>>(p->d, g, p->n, p->batch, 2, 0);
+          if ((r = check_launch(p->ctx, "apply_gradients kernel")) != DPC_OK)
+            return r;
+        }
+        return DPC_OK;
       },
       [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_LEARN, 0); });
   if (rc != DPC_OK)
@@ -887,9 +906,16 @@ int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
   {
     if ((rc = launch_dfa_proj(p, first, count, 0)) != DPC_OK)
       return rc;
-    return weight_gemm_simt(p, first, count, WG_DFA | WG_GRAD_ONLY, 0);
+    return dispatch_range(
+        p, first, count,
+        [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_DFA | WG_GRAD_ONLY); },
+        [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA | WG_GRAD_ONLY, 0); });
   }
-  if ((rc = weight_gemm_simt(p, first, count, WG_LEARN | WG_GRAD_ONLY, 0)) != DPC_OK)
+  rc = dispatch_range(
+      p, first, count,
+      [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_LEARN | WG_GRAD_ONLY); },
+      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_LEARN | WG_GRAD_ONLY, 0); });
+  if (rc != DPC_OK)
     return rc;
   bool any_psi = false;
   int max_next = 0, max_size = 0;

@@ -71,7 +71,8 @@ void tc_plan_free(dpc_plan* plan);
 int tc_forward(dpc_plan* plan, int first, int count, int flags);
 int tc_update_state(dpc_plan* plan, int first, int count);
 int tc_project_forward(dpc_plan* plan, int first, int count, int flags);
-int tc_weight_gemm(dpc_plan* plan, int first, int count, int mode);
+// mode: 0 learn, 1 direct feedback, +2: only store the raw sums in the layers' g_W.
+int tc_weight_gemm(dpc_plan* plan, int first, int count, int mode, int decay_w = 0);
 // Synchronous: reads the device-side status flag the kernels raise when a bounded wait runs
 // out; DPC_ERR_TIMEOUT if it was raised.
 int tc_check_error(dpc_plan* plan);

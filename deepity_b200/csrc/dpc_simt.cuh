@@ -889,7 +889,8 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
 // Applies staged gradients (the raw sums that the WG_GRAD_ONLY weight kernel and the grad_only
 // bias / Psi kernels left in g_W, g_b, g_Psi, possibly summed over batch shards since) with
 // exactly the formulas of the fused updates above; `batch` is the batch the sums cover (the
-// global one).  which = WG_LEARN: W, b and Psi; WG_DFA: W only (DirectFeedbackUpdate).
+// global one).  which = WG_LEARN: W, b and Psi; WG_DFA: W only (DirectFeedbackUpdate);
+// 2: W only with the learn-step formulas (b and Psi are updated by their own fused kernels).
 __global__ void apply_gradients_kernel(const dpc_layer* __restrict__ layers, int first,
                                        int n_layers, int batch, int which, int flags)
 {
@@ -930,8 +931,9 @@ __global__ void apply_gradients_kernel(const dpc_layer* __restrict__ layers, int
         w *= decay;
       L.W[o] = fmaf(alpha, L.g_W[o], w);
     }
-    for (size_t j = tid; j < (size_t)L.next_size; j += nthr)
-      L.b[j] += (L.lr / Bf) * L.g_b[j];
+    if (which != 2)
+      for (size_t j = tid; j < (size_t)L.next_size; j += nthr)
+        L.b[j] += (L.lr / Bf) * L.g_b[j];
   }
   else
   {
@@ -945,15 +947,16 @@ __global__ void apply_gradients_kernel(const dpc_layer* __restrict__ layers, int
       L.m_W[o] = mm;
       L.v_W[o] = vv;
     }
-    for (size_t j = tid; j < (size_t)L.next_size; j += nthr)
-    {
-      float m = L.m_b[j], v = L.v_b[j];
-      L.b[j] = adam_update(L.b[j], -L.g_b[j], m, v, step, -1.0f);
-      L.m_b[j] = m;
-      L.v_b[j] = v;
-    }
+    if (which != 2)
+      for (size_t j = tid; j < (size_t)L.next_size; j += nthr)
+      {
+        float m = L.m_b[j], v = L.v_b[j];
+        L.b[j] = adam_update(L.b[j], -L.g_b[j], m, v, step, -1.0f);
+        L.m_b[j] = m;
+        L.v_b[j] = v;
+      }
   }
-  if (L.Psi == nullptr || simple)
+  if (L.Psi == nullptr || simple || which == 2)
     return;
   const bool full_kind = (L.flags & DPC_LAYER_FULLPC_PSI) != 0;
   const float rate = full_kind ? L.fl * L.a : L.fl;

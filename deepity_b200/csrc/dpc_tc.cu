@@ -46,7 +46,7 @@ enum
   TC_FB = 1,
   TC_WG = 2
 };
-constexpr int WG_LEARN_MODE = 0, WG_DFA_MODE = 1;
+constexpr int WG_LEARN_MODE = 0, WG_DFA_MODE = 1, WG_GRAD_MODE = 2; // GRAD is or-ed in
 
 struct TcState
 {
@@ -980,14 +980,34 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
         const dpc_layer L = P.layers[li];
         const float Bf = (float)P.batch;
         float alpha, decay = 1.0f;
-        if (P.mode == WG_DFA_MODE)
+        if ((P.mode & 1) == WG_DFA_MODE)
+        {
           alpha = L.fl * L.a / Bf;
+          // the FullPC pre-scale of the direct-feedback update (FullPCLayer.cpp:514-572)
+          if ((P.flags & 1) && L.lmbda > 0.0f && L.fl != 0.0f)
+            decay = 1.0f - L.lmbda;
+        }
         else
         {
           alpha = L.a * L.lr / Bf;
           if (L.lmbda > 0.0f)
             decay = 1.0f - L.lmbda;
         }
+        if (P.mode & WG_GRAD_MODE)
+        {
+          // raw sums into the gradient staging buffer: an optimizer kernel (Adam-type updates,
+          // or a sum over batch shards first) applies them
+          for (int c = grp; c < BN / 32; c += GROUPS)
+          {
+            const size_t o = (size_t)m * P.N + n0 + c * 32;
+            float v[32];
+            tc_ld32(taddr + c * 32, v);
+#pragma unroll
+            for (int k = 0; k < 32; k += 8)
+              st8(L.g_W + o + k, &v[k]);
+          }
+        }
+        else
         for (int c = grp; c < BN / 32; c += GROUPS)
         {
           const size_t o = (size_t)m * P.N + n0 + c * 32;
@@ -1510,7 +1530,7 @@ int tc_update_state(dpc_plan* p, int first, int count)
                                   base_params(p, st, first, count, B, H, H, 128, 0, 0));
 }
 
-int tc_weight_gemm(dpc_plan* p, int first, int count, int mode)
+int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
 {
   auto* st = static_cast<TcState*>(p->tc);
   if (!st || !st->ok || !range_in_run(p, first, count))
@@ -1519,22 +1539,26 @@ int tc_weight_gemm(dpc_plan* p, int first, int count, int mode)
   {
     const dpc_layer& L = p->h[i];
     if (mode == WG_LEARN_MODE && L.opt != DPC_OPT_SGD)
+      return 1; // Adam-type updates go through the staging buffer (mode | WG_GRAD_MODE)
+    if ((mode & WG_GRAD_MODE) && (!L.g_W || ((uintptr_t)L.g_W % 32) != 0))
       return 1;
-    if (mode == WG_DFA_MODE && (i + 1 >= p->n || !p->h[i + 1].Psi))
+    if ((mode & 1) == WG_DFA_MODE && (i + 1 >= p->n || !p->h[i + 1].Psi))
       return 1;
   }
   const int H = p->run.width, B = p->batch;
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
   if (pair_ok(H, H))
   {
-    TcParams P = base_params(p, st, first, count, H, H, B, 256, 0, mode, 256);
+    TcParams P = base_params(p, st, first, count, H, H, B, 256, decay_w ? 1 : 0, mode, 256);
     return tf32 ? launch<TC_WG, 256, false, 128, true>(p, st, st->fe_mn, st->z_mn, P)
                 : launch<TC_WG, 256, true, 128, true>(p, st, st->fe_mn, st->z_mn, P);
   }
   if (tf32)
-    return launch<TC_WG, 256, false>(p, st, st->fe_mn, st->z_mn,
-                                     base_params(p, st, first, count, H, H, B, 256, 0, mode));
-  return launch<TC_WG, 128, true>(p, st, st->fe_mn, st->z_mn,
-                                  base_params(p, st, first, count, H, H, B, 128, 0, mode));
+    return launch<TC_WG, 256, false>(
+        p, st, st->fe_mn, st->z_mn,
+        base_params(p, st, first, count, H, H, B, 256, decay_w ? 1 : 0, mode));
+  return launch<TC_WG, 128, true>(
+      p, st, st->fe_mn, st->z_mn,
+      base_params(p, st, first, count, H, H, B, 128, decay_w ? 1 : 0, mode));
 }
 } // namespace dpc

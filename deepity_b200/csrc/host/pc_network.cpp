@@ -311,7 +311,9 @@ void PCNetwork::EnsureOptimizerState()
 
 void PCNetwork::EnsureGradientStaging()
 {
-  if (!gradSync || gradBuffer)
+  // Staging is needed for batch sharding, and lets Adam-type weight updates of the tensor-core
+  // layers run as "product into the staging buffer + elementwise optimizer".
+  if (!(gradSync || opt != OptimizerType::SGD) || gradBuffer)
     return;
   size_t tw = 0, tb = 0, tp = 0;
   for (auto& l : layers)

@@ -143,6 +143,17 @@ def test_tensor_core_path_tf32_bound(name, built_library):
     compare_outputs(run_oracle(case), run_gpu(case, precision="tf32"), TF32_TOL, name)
 
 
+def test_adam_on_tensor_core_layers(built_library):
+    """Adam / AdamW weight updates of the tensor-core layers: product into the staging buffer,
+    optimizer as an elementwise kernel; FullPC's decayed direct-feedback update on tensor cores."""
+    case = dict(kind="full", sizes=[64] + [256] * 4 + [10], batch=256, T=3, steps=3,
+                hyper=dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.01, act="gelu"),
+                options=dict(optimizer="ADAMW", psi_optimizer="ADAM", cross_entropy=1))
+    assert _tensor_run_of(case, "fp32")[1] >= 3
+    ref = run_oracle(case)
+    compare_outputs(ref, run_gpu(case, precision="fp32"), ADAM_TOL, "adam on tensor cores")
+
+
 def test_deep_stack_at_benchmark_layer_shape(built_library):
     """48 layers of the deep-stack benchmark's shape (batch 1024, width 512): many tiles per
     CTA through the persistent pair kernels, the staged epilogue operands and the sequential
