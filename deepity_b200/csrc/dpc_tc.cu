@@ -420,8 +420,6 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
   if (!active)
     up_src = nullptr; // lanes that hold no accumulator row touch no memory
   const bool staged = STAGED && P.stage_in != 0 && up_src_all != nullptr;
-  const bool dbg_nostore = (P.flags & (1 << 13)) != 0;
-  const bool dbg_nomath = (P.flags & (1 << 14)) != 0;
   if (staged)
     up_src = nullptr; // the operand comes from shared memory, box by box
   if (up_src)
@@ -480,9 +478,7 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
       for (int q = 0; q < 8; ++q)
       {
         pre[q] = L.a * v[k + q] + bb[q];
-        if (dbg_nomath)
-          mu[q] = pre[q], d[q] = 1.0f - pre[q];
-        else if (do_fe)
+        if (do_fe)
           act_both(act, pre[q], mu[q], d[q]);
         else
           mu[q] = act_fwd(act, pre[q]), d[q] = 1.0f;
@@ -512,7 +508,7 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
           e[q] = (do_copy || !active) ? 0.0f : up[k + q] - mu[q];
           esum += e[q] * e[q];
         }
-        if (active && !dbg_nostore)
+        if (active)
           st8(up_e + o + k, e);
       }
       else if (do_fe)
@@ -526,7 +522,7 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
 #pragma unroll
         for (int q = 0; q < 8; ++q)
           e[q] *= d[q];
-        if (active && (!dbg_nostore || e[0] == 123.456f))
+        if (active)
           st8(L.fe + o + k, e);
       }
       if (tl >= 0 && c == grp && k == 0 && threadIdx.x == 64)
@@ -1434,8 +1430,6 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
   P.tiles_m = M / BM;
   P.tiles_n = N / BN;
   P.flags = flags;
-  if (const char* d = getenv("DPC_TC_DEBUG"))
-    P.flags |= atoi(d) << 13;
   P.mode = mode;
   P.energy = p->energy;
   P.error_flag = st->error_flag;
