@@ -1,9 +1,10 @@
 """Build the oracle: the reference's own CPU train-step path, compiled where it lies.
 
 Test infrastructure only.  Compiles the reference sources for the Simple /
-DirectKP / Full predictive-coding networks and the CPU backend straight from the
-reference checkout (``DEEPITY_REFERENCE`` or ``/root/reference``), together with
-``ref_driver.cpp`` (a flat C interface) and ``shim_kernels.cpp`` (scalar
+DirectKP / Full / SimpleConv predictive-coding networks and the CPU backend straight
+from the reference checkout (environment variable ``DEEPITY_REFERENCE``, else the
+default of ``reference_root()``), together with ``ref_driver.cpp`` and
+``ref_conv_driver.cpp`` (flat C interfaces) and ``shim_kernels.cpp`` (scalar
 restatements of the few Highway / scalar-SLEEF symbols this image lacks), into
 ``oracle/_ref/libdeepity_ref.so``.  The reference's own CMake build cannot run
 offline (it fetches SLEEF, Highway, oneDNN, CUTLASS and nanobind), so the handful
