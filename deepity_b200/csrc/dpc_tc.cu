@@ -390,9 +390,10 @@ struct InStage
   int row;       // this lane's row inside the 128-row box
   int nbufs;     // power of two
   volatile int* abort_flag;
+  const uint8_t* rx; // K-split sweep: the peer's partial sums for this CTA's 32 columns
 };
 
-template <int ACT, int BN, int GROUPS, bool PREFETCH, bool STAGED = false>
+template <int ACT, int BN, int GROUPS, bool PREFETCH, bool STAGED = false, bool KSUM = false>
 __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMeta& L,
                                                   const float* bias_pre, uint32_t taddr, int m,
                                                   int n0, int grp, float& esum, int tl,
@@ -454,6 +455,17 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
         mbar_arrive(&in->empty[b]);
     }
     tc_ld16(taddr + c * CW, v);
+    if (KSUM)
+    {
+      // add the other CTA's half of the K sum (rows of 128 bytes, 16-byte chunks swizzled by row)
+      const uint8_t* rowp = in->rx + in->row * 128;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+      {
+        const float4 x = *reinterpret_cast<const float4*>(rowp + (((c * 4 + i) ^ (in->row & 7)) << 4));
+        v[4 * i] += x.x, v[4 * i + 1] += x.y, v[4 * i + 2] += x.z, v[4 * i + 3] += x.w;
+      }
+    }
     if (tl >= 0 && c == grp && threadIdx.x == 64)
       trace_stamp(P, tl, 5);
     if (PREFETCH && up_src && c + GROUPS < BN / CW)
@@ -553,9 +565,13 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
 // 128 rows of A and its own half of B (BN/2 rows) and holds its 128 rows of the accumulator in
 // its own tensor memory, so per output element half as many operand bytes cross L2 -> SM and
 // shared memory as with two independent 128 x BN/2 tiles.
-template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false>
+// KS = 2 (sequential sweep only): two CTAs of a cluster share one 128 x BN tile, each running
+// the main loop over half of K; they exchange the half of the partial tile the other one
+// finishes through distributed shared memory.  Halves every CTA's operand traffic per layer.
+template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
 struct Cfg
 {
+  static constexpr int RX_BYTES = KS == 2 ? 128 * 32 * 4 : 0; // partial tile from the peer
   static constexpr bool A_MN = (OP == TC_WG);
   static constexpr bool B_MN = (OP != TC_FWD);
   static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN; // rows of B this CTA stages
@@ -565,7 +581,7 @@ struct Cfg
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (THREE_X ? 2 : 1);
   // at most 8 stages: the barrier block after the ring is sized for that
   static constexpr int STAGES_RAW =
-      (196608 - ((PAIR && OP == TC_FWD && !THREE_X) ? 4 * BM * 32 * 4 : 0)) / STAGE_BYTES;
+      (196608 - ((PAIR && OP == TC_FWD && !THREE_X) ? 4 * BM * 32 * 4 : 0) - RX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW);
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS =
@@ -580,25 +596,28 @@ struct Cfg
   static constexpr int IN_BYTES = BM * 32 * 4;
   static constexpr int IN_BUFS = STAGE_IN ? (THREE_X ? 2 : 4) : 0;
   static constexpr int SMEM_BYTES =
-      STAGES * STAGE_BYTES + IN_BUFS * IN_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+      STAGES * STAGE_BYTES + IN_BUFS * IN_BYTES + RX_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
                                     ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TILE_M >> 4) << 24);
   static_assert(!PAIR || (BM == 128 && BN % 64 == 0), "pair tiles are 256 x BN");
+  static_assert(KS == 1 || (KS == 2 && !PAIR && OP == TC_FWD && BM == 128 && BN == 64),
+                "the K-split sweep uses 128 x 64 tiles");
 };
 
-template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false>
-__global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
+template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
+__global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1)
     pc_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const __grid_constant__ CUtensorMap mapU, const TcParams P)
 {
-  using C = Cfg<OP, BN, THREE_X, BM, PAIR>;
+  using C = Cfg<OP, BN, THREE_X, BM, PAIR, KS>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
   uint8_t* in_base = smem + C::STAGES * C::STAGE_BYTES; // staged operand of the layer above
-  uint64_t* bars = reinterpret_cast<uint64_t*>(in_base + C::IN_BUFS * C::IN_BYTES);
+  uint8_t* rx_base = in_base + C::IN_BUFS * C::IN_BYTES; // K-split sweep: peer's partial tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rx_base + C::RX_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + C::STAGES;
   uint64_t* xf = bars + 2 * C::STAGES;
@@ -606,7 +625,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
   uint64_t* tempty = tfull + 2;
   uint64_t* in_full = tempty + 2;
   uint64_t* in_empty = in_full + 4;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(in_empty + 4);
+  uint64_t* rx_full = in_empty + 4;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(rx_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -615,10 +635,12 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
   // Pair mode: the two CTAs of a cluster walk the same work items; rank 0 issues the MMAs.
   const uint32_t rank = PAIR ? cluster_ctarank() : 0;
   const bool leader = rank == 0;
+  // K-split sweep: which half of K this CTA multiplies and which 32 columns it finishes.
+  const uint32_t krank = KS > 1 ? cluster_ctarank() : 0;
   const int t_begin = P.chain ? 0 : (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x);
   const int t_end = P.chain ? P.count : total_tiles;
   const int t_step = P.chain ? 1 : (PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x);
-  const int kblocks = P.K / TBK;
+  const int kblocks = P.K / TBK / KS;
 
   if (threadIdx.x == 0)
   {
@@ -638,6 +660,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
       mbar_init(&in_full[b], 1);
       mbar_init(&in_empty[b], C::EPI_WARPS);
     }
+    mbar_init(rx_full, C::EPI_WARPS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -663,12 +686,14 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
     }
   }
   tc_fence_before();
-  if (PAIR)
+  if (PAIR || KS > 1)
     cluster_sync_all(); // the peer's barriers are initialised before anything signals them
   else
     __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  const uint32_t peer_rx = KS > 1 ? mapa_u32(smem_u32(rx_base), krank ^ 1) : 0;
+  const uint32_t peer_rx_full = KS > 1 ? mapa_u32(smem_u32(rx_full), krank ^ 1) : 0;
   // Barriers of the leader CTA as seen from either CTA (shared::cluster addresses).
   const uint32_t lead_full = PAIR ? mapa_u32(smem_u32(full), 0) : 0;
   const uint32_t lead_xf = PAIR ? mapa_u32(smem_u32(xf), 0) : 0;
@@ -687,7 +712,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
       for (int t = t_begin; t < t_end && alive; t += t_step)
       {
         const int lrel = P.chain ? t : t / tiles_per_layer;
-        const int rem = P.chain ? (int)blockIdx.x : t % tiles_per_layer;
+        const int rem = P.chain ? (int)blockIdx.x / KS : t % tiles_per_layer;
         // this CTA's rows of A and rows of B (pair mode: its half of each)
         const int m0 = (rem / P.tiles_n) * C::TILE_M + (int)rank * BM;
         const int n0 = (rem % P.tiles_n) * BN + (int)rank * C::BN_LOCAL;
@@ -704,7 +729,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
           }
           uint8_t* a_dst = stage_base + s * C::STAGE_BYTES;
           uint8_t* b_dst = a_dst + C::A_BYTES;
-          const int k0 = kb * TBK;
+          const int k0 = ((int)krank * kblocks + kb) * TBK;
           if (PAIR && !THREE_X)
           {
             // One pass of TF32: the MMA thread of the leader waits on ITS full[s] for the tiles
@@ -869,13 +894,15 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
     for (int t = t_begin; t < t_end; t += t_step, ++tile_iter)
     {
       const int lrel = P.chain ? t : t / tiles_per_layer;
-        const int rem = P.chain ? (int)blockIdx.x : t % tiles_per_layer;
+      const int rem = P.chain ? (int)blockIdx.x / KS : t % tiles_per_layer;
       // M=128: lane i of quarter q holds row 32q+i.  M=64: rows 16q..16q+15 sit in lanes 0..15 of
       // quarter q and the upper 16 lanes hold nothing.
       const bool active = BM == 128 || lane < 16;
       const int m = (rem / P.tiles_n) * C::TILE_M + (int)rank * BM +
                     (BM == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15));
-      const int n0 = (rem % P.tiles_n) * BN;
+      // K-split sweep: this CTA finishes columns [32*krank, 32*krank+32) of the 64-wide tile
+      constexpr int BNE = KS == 2 ? 32 : BN;
+      const int n0 = (rem % P.tiles_n) * BN + (KS == 2 ? 32 * (int)krank : 0);
       const int li = P.first + lrel;
       const dpc_layer* Lup = (li + 1 < P.n_layers) ? &P.layers[li + 1] : nullptr;
       const int acc = tile_iter & 1;
@@ -884,11 +911,11 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
       if (OP == TC_FWD)
       {
         load_fwd_meta(P, li, meta);
-        if (BN / GROUPS <= 32)
+        if (BNE / GROUPS <= 32)
         {
           // Narrow tiles (the sequential sweep): this warp's bias values are fetched now too.
 #pragma unroll
-          for (int i = 0; i < (BN / GROUPS) / 16; ++i)
+          for (int i = 0; i < (BNE / GROUPS) / 16; ++i)
 #pragma unroll
             for (int k = 0; k < 16; k += 8)
               ld8(meta.b + n0 + (grp + GROUPS * i) * 16 + k, &bias_pre[i * 16 + k]);
@@ -900,27 +927,53 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
       tc_fence_after();
       if (P.chain && warp == 2 && lane == 0)
         trace_stamp(P, t, 2);
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (BN * C::KSPLIT);
+      uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (BN * C::KSPLIT);
 
       if (OP == TC_FWD)
       {
         constexpr bool PF = !THREE_X;
         constexpr bool SI = C::STAGE_IN;
+        constexpr bool KSUM = KS == 2;
         InStage in;
         in.buf = in_base, in.full = in_full, in.empty = in_empty;
         in.seq = (uint32_t)tile_iter * (uint32_t)(BN / 32);
         in.row = quarter * 32 + lane, in.nbufs = C::IN_BUFS > 0 ? C::IN_BUFS : 1;
         in.abort_flag = abort_flag;
+        in.rx = rx_base;
+        if (KS == 2)
+        {
+          // Hand the peer this CTA's partial sums of the 32 columns the peer finishes (16 per
+          // warp), then wait for the peer's partial sums of this CTA's own 32 columns.
+          const uint32_t peer = krank ^ 1u;
+          float pv[16];
+          tc_ld16(taddr + 32 * peer + 16 * grp, pv);
+          const int row = quarter * 32 + lane;
+          const uint32_t dst = peer_rx + (uint32_t)row * 128u;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+          {
+            const uint32_t a = dst + (uint32_t)((((grp << 2) + i) ^ (row & 7)) << 4);
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                         "f"(pv[4 * i]), "f"(pv[4 * i + 1]), "f"(pv[4 * i + 2]), "f"(pv[4 * i + 3])
+                         : "memory");
+          }
+          __syncwarp();
+          if (lane == 0)
+            mbar_arrive_cluster(peer_rx_full);
+          if (!mbar_wait_cluster(rx_full, (uint32_t)(tile_iter & 1), abort_flag))
+            break;
+          taddr += 32 * krank; // this CTA's own columns of the accumulator
+        }
         switch (meta.act)
         {
         case DPC_ACT_TANH:
-          fwd_epilogue_tile<DPC_ACT_TANH, BN, GROUPS, PF, SI>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
+          fwd_epilogue_tile<DPC_ACT_TANH, BNE, GROUPS, PF, SI, KSUM>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
           break;
         case DPC_ACT_GELU:
-          fwd_epilogue_tile<DPC_ACT_GELU, BN, GROUPS, PF, SI>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
+          fwd_epilogue_tile<DPC_ACT_GELU, BNE, GROUPS, PF, SI, KSUM>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
           break;
         default:
-          fwd_epilogue_tile<-1, BN, GROUPS, false, SI>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
+          fwd_epilogue_tile<-1, BNE, GROUPS, false, SI, KSUM>(P, meta, bias_pre, taddr, m, n0, grp, esum, P.chain ? t : -1, active, &in);
         }
       }
       else if (OP == TC_FB)
@@ -1144,7 +1197,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR>::THREADS, 1)
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
-  if (PAIR)
+  if (PAIR || KS > 1)
     cluster_sync_all(); // neither CTA leaves while the other may still touch its memory
   else
     __syncthreads();
@@ -1203,14 +1256,14 @@ bool make_map(CUtensorMap* map, const float* base, int cols, int rows, int layer
   return r == CUDA_SUCCESS;
 }
 
-template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false>
+template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
 int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P,
            const CUtensorMap* up = nullptr)
 {
   const CUtensorMap& u = up ? *up : a; // unused unless P.stage_in
-  using C = Cfg<OP, BN, THREE_X, BM, PAIR>;
+  using C = Cfg<OP, BN, THREE_X, BM, PAIR, KS>;
   static bool configured = false;
-  auto kern = pc_tc_kernel<OP, BN, THREE_X, BM, PAIR>;
+  auto kern = pc_tc_kernel<OP, BN, THREE_X, BM, PAIR, KS>;
   if (!configured)
   {
     if (C::SMEM_BYTES > st->max_smem)
@@ -1222,10 +1275,11 @@ int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b,
     configured = true;
   }
   const int total = P.count * P.tiles_m * P.tiles_n;
-  if (PAIR)
+  if (PAIR || KS > 1)
   {
-    // one cluster of two CTAs per work item, as many clusters as SM pairs
-    const int pairs = std::min(total, p->ctx->sm_count / 2);
+    // one cluster of two CTAs per work item, as many clusters as SM pairs (the sweep: one
+    // cluster per tile, all of them resident at once)
+    const int pairs = P.chain ? P.tiles_m * P.tiles_n : std::min(total, p->ctx->sm_count / 2);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(C::THREADS);
@@ -1503,6 +1557,24 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   if (e != cudaSuccess)
     return cuda_fail(e, "cudaMemsetAsync(chain counters)");
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  // K-split variant: 128 x 64 tiles, two CTAs (one cluster) per tile with half of K each.
+  // Summing K in two halves rounds differently from the settling passes' single accumulation,
+  // so right after the sweep e = z - mu is ~1e-7 where it is exactly 0 with matching orders
+  // (as in the reference, which uses one GEMM routine for both).  Harmless for SGD; Adam-type
+  // updates normalise such noise up to a full step, so they keep the single-accumulation sweep.
+  bool sgd_only = true;
+  for (int i = 0; i < p->n; ++i)
+    sgd_only &= p->h[i].next_size <= 0 || p->h[i].opt == DPC_OPT_SGD;
+  const int ks_tiles = (B / TBM) * (H / 64);
+  if (sgd_only && 2 * ks_tiles <= p->ctx->sm_count && (H / TBK) % 2 == 0 &&
+      !getenv("DPC_DISABLE_KSPLIT"))
+  {
+    TcParams Q = base_params(p, st, first, count, B, H, H, 64, flags, 0);
+    Q.chain = 1, Q.chain_counters = st->chain_counters, Q.trace = st->trace;
+    Q.chain_target = (H / 64) * 2 * 8; // column tiles x CTAs per tile x epilogue warps
+    return tf32 ? launch<TC_FWD, 64, false, 128, false, 2>(p, st, st->z_km, st->w_km64, Q)
+                : launch<TC_FWD, 64, true, 128, false, 2>(p, st, st->z_km, st->w_km64, Q);
+  }
   if (BNC == 32)
     return tf32 ? launch<TC_FWD, 32, false>(p, st, st->z_km, st->w_km32, P)
                 : launch<TC_FWD, 32, true>(p, st, st->z_km, st->w_km32, P);
