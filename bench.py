@@ -526,181 +526,6 @@ def main():
                      "hbm_gbs_at_algorithmic_bytes": gbs, "hbm_peak_gbs": hbm_peak})
     line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": config, "energy": energy,
-            "algorithmic_flops_per_step": flops, "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
-            "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8},
-            "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "conv forward implicit GEMM, 64->128 channels "
-                                                   "(reads z, W, z_up; writes preact, mu, e_up, g)",
-                         "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback",
-                         "traffic": None, "launch_ms": k_ms, "algorithmic_bytes_per_launch": k_bytes,
-                         "algorithmic_flops_per_launch": k_flops,
-                         "note": "7.6 MB and 0.3 GFLOP per launch on 64 CTAs: latency-bound at this size, "
-                                 "neither roofline binds"},
-            "clocks": clk.summary()}
-    if not args.no_cpu:
-        leg = conv_cpu_leg(layers, B, T, 2, 1)
-        line["cpu_baseline"] = {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    print(json.dumps(line))
-
-
-# ------------------------------------------------------------------------------ GPU leg
-def build_net(w, sizes, precision):
-    import deepity_b200 as dp
-    acts = {"tanh": dp.TanH, "sigmoid": dp.Sigmoid, "gelu": dp.GeLU, "relu": dp.ReLU}
-    arch = []
-    for l in range(len(sizes) - 1):
-        arch.append(dp.Linear(sizes[l], sizes[l + 1]))
-        arch.append(acts[w["act"]]())
-    cls = {"dkp": dp.DKPPCN, "simple": dp.SimplePCN, "full": dp.FullPCN}[w["kind"]]
-    net = cls(*arch, batch_size=w["batch"], device=f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}")
-    kw = dict(learning_rate=HYPER["lr"], inference_rate=HYPER["ir"], lmbda=HYPER["lmbda"], seed=1,
-              precision=precision)
-    if w["kind"] != "simple":
-        kw.update(feedback_rate=HYPER["fl"])
-    if w["kind"] == "full":
-        kw.update(use_cross_entropy=True, optimizer="ADAM", psi_optimizer="ADAM")
-    net.configure(**kw)
-    return net
-
-
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c5"])
-    ap.add_argument("--depth", type=int, default=None, help="override the hidden-layer count")
-    ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32"])
-    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    args = ap.parse_args()
-
-    rank = int(os.environ.get("RANK", 0))
-    world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.workload == "c5":
-        if rank == 0:
-            conv_main(args)
-        return
-    w = dict(WORKLOADS[args.workload])
-    if args.depth:
-        w["hidden"] = args.depth
-        w["desc"] += f" (depth overridden to {args.depth})"
-    sizes = sizes_of(w)
-    B, T = w["batch"], w["T"]
-    config = {"workload": w["desc"], "global_batch": B, "T": T, "layers": len(sizes) - 1,
-              "hyper": HYPER, "precision": args.precision,
-              "l2": "working set (z,e,preact,mu,fe,W of every layer) is far larger than the 126 MB L2"
-              if args.workload in ("c3", "c4") else "L2 flushed between timed steps"}
-
-    if args.impl == "reference":
-        if rank != 0:
-            return
-        leg = cpu_reference_leg(w, max(1, min(args.steps, 3)), min(args.warmup, 1))
-        line = {"impl": "reference", "metric": "train_step samples/sec", "value": leg["value"],
-                "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": B / leg["value"] * 1e3,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": config,
-                "cpu_baseline": {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample")},
-                "e2e": {"value": leg["value"], "unit": "samples/s", "h2d_bytes_per_step": 0,
-                        "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
-        return
-
-    import torch
-    import torch.distributed as dist
-    from deepity_b200 import _lib
-
-    if world > 1:
-        from deepity_b200 import sharded
-        # deep stacks shard by layers; wide, shallow networks by batch rows
-        if w["kind"] == "dkp" and len(sizes) - 1 >= world:
-            sharded.bench_main(args, w, sizes, config)
-        else:
-            sharded.batch_bench_main(args, w, sizes, config)
-        return
-
-    torch.cuda.set_device(0)
-    lib = _lib.load()
-    net = build_net(w, sizes, args.precision)
-    x, y, params = synth(w, sizes)
-    for l, p in enumerate(params):
-        for nm, v in p.items():
-            net.set_tensor(l, nm, v)
-    xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
-    xh, yh = x.ravel().copy(), y.ravel().copy()
-    torch.cuda.synchronize()
-    stream = torch.cuda.ExternalStream(lib.dpc_stream(lib.dpcn_context(net._h)))
-    flush = None
-    if args.workload in ("c1", "c2"):
-        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-
-    def timed(fn, steps):
-        """Mean ms per step over `steps` calls, CUDA events on the library's stream."""
-        total = 0.0
-        for _ in range(steps):
-            if flush is not None:
-                flush.zero_()
-                torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            fn()
-            b.record(stream)
-            b.synchronize()
-            total += a.elapsed_time(b)
-        return total / steps
-
-    flops = net.train_step_flops(T)
-    for _ in range(args.warmup):
-        energy = net.train_step_device(xd, yd, T)
-    lib.dpc_sync(lib.dpcn_context(net._h))
-    with ClockSampler(0) as clk:
-        n0 = net.launch_count
-        ms = timed(lambda: net.train_step_device(xd, yd, T, read_energy=False), args.steps)
-        launches = net.launch_count - n0
-        energy = net.train_step_device(xd, yd, T)
-        # end to end: host buffers in, energy out
-        for _ in range(2):
-            net.train_step(xh, yh, T)
-        t0 = time.perf_counter()
-        e2e_ms_ev = timed(lambda: net.train_step(xh, yh, T), args.steps)
-        e2e_wall = (time.perf_counter() - t0) / args.steps * 1e3
-        e2e_ms = max(e2e_ms_ev, e2e_wall) if flush is None else e2e_ms_ev
-        # dominant kernel: the grouped forward GEMM with fused error + feedback error
-        plan = lib.dpcn_plan(net._h)
-        n = len(sizes)
-        fwd_flags = 2 | 8  # DPC_FWD_ERR_NEXT | DPC_FWD_FE
-        for _ in range(2):
-            lib.dpc_forward(plan, 1, n - 2, fwd_flags)
-        k_ms = timed(lambda: lib.dpc_forward(plan, 1, n - 2, fwd_flags), max(args.steps, 5))
-    clocks = clk.summary()
-
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
-    peak_tf = peaks.get("bf16_tflops_sustained") or 1590.0
-    peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback 1.59 PF"
-    k_flops = sum(2.0 * B * sizes[i] * sizes[i + 1] for i in range(1, n - 1))
-    k_bytes = sum(4.0 * (B * sizes[i] + sizes[i] * sizes[i + 1] + 3 * B * sizes[i + 1])
-                  for i in range(1, n - 1))
-    achieved = k_flops / (k_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": "grouped forward GEMM + error + feedback-error epilogue",
-                "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                "peak_source": peak_src, "traffic": None, "launch_ms": k_ms,
-                "algorithmic_flops_per_launch": k_flops,
-                "algorithmic_bytes_per_launch": k_bytes,
-                "hbm_gbs_at_algorithmic_bytes": k_bytes / (k_ms * 1e-3) / 1e9,
-                "hbm_peak_gbs": peaks.get("hbm_gbs"),
-                "note": "fp32-accurate arithmetic cannot exceed 1/2 (TF32) or 1/6 (3xTF32) of the "
-                        "bf16 peak used as denominator"}
-    line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
-            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
             "config": config, "energy": energy,
