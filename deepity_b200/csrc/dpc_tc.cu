@@ -206,7 +206,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   }
 }
 // TMA load whose completion bytes are counted on a barrier of either CTA of the pair
-// (bar_addr is a shared::cluster address).  No multicast: each CTA fetches its own tiles.
+// (bar_addr is a shared::cluster address).  Each CTA fetches its own tiles.
 __device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map,
                                                  uint32_t bar_addr, int c0, int c1, int c2)
 {
@@ -858,7 +858,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           }
           if (PAIR)
           {
-            // release the stage in both CTAs (two plain commits, no multicast)
+            // release the stage in both CTAs (two plain commits, one per CTA)
             tc_commit_pair(smem_u32(&empty[s]));
             tc_commit_pair(peer_empty + (uint32_t)(s * 8));
           }
