@@ -81,6 +81,8 @@ class GpuEngine:
                                                 device=torch.device("cuda", device))
         self.ghost_top = ghost_top
         self._views = {}
+        # activations whose derivative is a function of their output (see dpc_direct_feedback)
+        self.output_deriv = act in ("tanh", "sigmoid", "relu", "linear", "hard_tanh")
 
     # -- tensors as torch views over the library's device memory (zero copy) ---------------
     def tensor(self, layer: int, name: str):
@@ -116,13 +118,20 @@ class GpuEngine:
         self.check(self.lib.dpcn_reset_state(self.h))
 
     def project_forward(self, skip_last_copy: bool):
-        self.check(self.lib.dpc_project_forward(self.plan, 0, self.n - 1, int(skip_last_copy)))
+        # Inside a train step nothing reads mu / preact of the swept layers before they are
+        # recomputed (the direct-feedback update takes f' from the copied outputs), so the sweep
+        # only writes the beliefs of the layers above.
+        extra = (512 | 2048) if self.output_deriv else 0  # DPC_FWD_NO_MU | DPC_FWD_NO_PREACT
+        self.check(self.lib.dpc_project_forward_ex(self.plan, 0, self.n - 1, int(skip_last_copy),
+                                                   extra))
 
     def terminal_error(self):
         self.check(self.lib.dpc_error(self.plan, self.n - 1, 0))
 
     def dfa(self):
-        self.check(self.lib.dpc_direct_feedback(self.plan, 0, self.n - 1, 0))
+        # 2 = DPC_DFA_FROM_OUTPUT: z[l+1] still equals f(preact[l]) right after the sweep
+        self.check(self.lib.dpc_direct_feedback(self.plan, 0, self.n - 1,
+                                                2 if self.output_deriv else 0))
 
     def forward_state(self, first_cached: bool, flags: int):
         """ComputeMuOnly + error of the layer above for every local weight layer."""
@@ -258,7 +267,8 @@ class ShardedDKPPCN:
         eng.forward_state(self.is_first, FWD_FE | FWD_TRANSIENT)
         eng.update_weights()
         eng.energy_reset()
-        eng.forward_state(self.is_first, FWD_ERR | FWD_ENERGY | FWD_FE)
+        # last pass: errors and energy only (nobody reads fe or the predictions afterwards)
+        eng.forward_state(self.is_first, FWD_ERR | FWD_ENERGY | FWD_TRANSIENT)
         if self.world > 1:
             # leave the boundary error where a reader of the rank above expects it
             self._exchange(send=None if self.is_last else (eng.tensor(n - 1, "e"), up),
