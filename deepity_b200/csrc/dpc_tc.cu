@@ -660,7 +660,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
       mbar_init(&in_full[b], 1);
       mbar_init(&in_empty[b], C::EPI_WARPS);
     }
-    mbar_init(rx_full, C::EPI_WARPS);
+    mbar_init(rx_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -949,17 +949,21 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           tc_ld16(taddr + 32 * peer + 16 * grp, pv);
           const int row = quarter * 32 + lane;
           const uint32_t dst = peer_rx + (uint32_t)row * 128u;
+          // asynchronous remote stores that count their bytes on the peer's barrier: no separate
+          // release + arrive round trip
 #pragma unroll
           for (int i = 0; i < 4; ++i)
           {
             const uint32_t a = dst + (uint32_t)((((grp << 2) + i) ^ (row & 7)) << 4);
-            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a),
-                         "f"(pv[4 * i]), "f"(pv[4 * i + 1]), "f"(pv[4 * i + 2]), "f"(pv[4 * i + 3])
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 "
+                         "[%0], {%1, %2, %3, %4}, [%5];" ::"r"(a),
+                         "f"(pv[4 * i]), "f"(pv[4 * i + 1]), "f"(pv[4 * i + 2]), "f"(pv[4 * i + 3]),
+                         "r"(peer_rx_full)
                          : "memory");
           }
-          __syncwarp();
-          if (lane == 0)
-            mbar_arrive_cluster(peer_rx_full);
+          // this CTA expects the peer's 128 rows x 128 bytes once per layer
+          if (warp == 2 && lane == 0)
+            mbar_expect_tx(rx_full, 128 * 128);
           if (!mbar_wait_cluster(rx_full, (uint32_t)(tile_iter & 1), abort_flag))
             break;
           taddr += 32 * krank; // this CTA's own columns of the accumulator
