@@ -2,7 +2,7 @@
 """Benchmark of the predictive-coding train step (metric: train_step samples/sec).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c3|c2|c1|c4|c5] [--depth D] [--precision fp32|tf32]
+                    [--workload c3|c2|c1|c4|c5] [--depth D] [--precision fp32|tf32|mixed]
 
 One "step" is one full ``train_step`` (settle T times, learn, final energy) on one batch of
 synthetic data.  At N=1 the workload is the configuration the headline metric is quoted on:
@@ -385,7 +385,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c5"])
     ap.add_argument("--depth", type=int, default=None, help="override the hidden-layer count")
-    ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32"])
+    ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "mixed"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     args = ap.parse_args()
 
@@ -527,7 +527,8 @@ def main():
     line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
+            "dtype": {"fp32": "f32", "tf32": "tf32", "mixed": "f32 state path, tf32 gradient path"}[
+                args.precision], "data": "synthetic",
             "config": config, "energy": energy,
             "algorithmic_flops_per_step": flops, "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
             "frac_of_gemm_peak_step": flops / (ms * 1e-3) / 1e12 / peak_tf,

@@ -143,7 +143,8 @@ int dpc_destroy(dpc_ctx* ctx)
 
 int dpc_set_precision(dpc_ctx* ctx, int precision)
 {
-  if (!ctx || (precision != DPC_PRECISION_FP32 && precision != DPC_PRECISION_TF32))
+  if (!ctx || (precision != DPC_PRECISION_FP32 && precision != DPC_PRECISION_TF32 &&
+               precision != DPC_PRECISION_MIXED))
     return fail(DPC_ERR_INVALID, "dpc_set_precision: bad argument");
   ctx->precision = precision;
   return DPC_OK;

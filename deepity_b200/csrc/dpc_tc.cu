@@ -1474,6 +1474,18 @@ static bool pair_ok(int rows, int cols)
   return !off && rows % 256 == 0 && cols % 256 == 0;
 }
 
+// DPC_PRECISION_MIXED: gradient-path products in one TF32 pass when every weight optimizer is
+// SGD (an Adam-type update would turn the TF32 rounding of a near-zero gradient into a full step).
+static bool fast_grad(const dpc_plan* p)
+{
+  if (p->ctx->precision != DPC_PRECISION_MIXED)
+    return false;
+  for (int i = 0; i < p->n; ++i)
+    if (p->h[i].next_size > 0 && p->h[i].opt != DPC_OPT_SGD)
+      return false;
+  return true;
+}
+
 static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int M, int N, int K,
                             int BN, int flags, int mode, int BM = TBM)
 {
@@ -1505,7 +1517,10 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
   if (!st || !st->ok || !range_in_run(p, first, count))
     return 1;
   const int H = p->run.width, B = p->batch;
-  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  // the pass after the last settling step: it only refreshes the errors the learning phase reads
+  const bool refresh =
+      (flags & DPC_FWD_FE) && !(flags & DPC_FWD_ERR_NEXT) && (flags & DPC_FWD_TRANSIENT);
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || (refresh && fast_grad(p));
   if (pair_ok(B, H))
   {
     TcParams P = base_params(p, st, first, count, B, H, H, 256, flags, 0, 256);
@@ -1622,7 +1637,7 @@ int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
       return 1;
   }
   const int H = p->run.width, B = p->batch;
-  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || fast_grad(p);
   if (pair_ok(H, H))
   {
     TcParams P = base_params(p, st, first, count, H, H, B, 256, decay_w ? 1 : 0, mode, 256);

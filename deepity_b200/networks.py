@@ -199,7 +199,7 @@ class _Network:
 
     def set_precision(self, precision: str) -> None:
         """'fp32' (parity with the CPU reference at 1e-4) or 'tf32' (one tensor-core pass)."""
-        self._option("precision", {"fp32": 0, "tf32": 1}[precision])
+        self._option("precision", {"fp32": 0, "tf32": 1, "mixed": 2}[precision])
 
     def set_use_graph(self, enabled: bool) -> None:
         self._option("use_graph", int(bool(enabled)))

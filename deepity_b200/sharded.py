@@ -72,7 +72,7 @@ class GpuEngine:
                                            hyper["ir"], hyper["fl"], hyper["lmbda"],
                                            ACT_IDS["linear"]))
         self.check(self.lib.dpcn_set_option(self.h, b"ghost_top", int(ghost_top), 0.0))
-        self.check(self.lib.dpcn_set_option(self.h, b"precision", {"fp32": 0, "tf32": 1}[precision],
+        self.check(self.lib.dpcn_set_option(self.h, b"precision", {"fp32": 0, "tf32": 1, "mixed": 2}[precision],
                                             0.0))
         self.check(self.lib.dpcn_compile(self.h))
         self.ctx = self.lib.dpcn_context(self.h)
@@ -421,7 +421,7 @@ def bench_main(args, w, sizes, config):
         line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
+                "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
                 "config": config, "energy": energy, "algorithmic_flops_per_step": flops,
                 "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
                 "frac_of_gemm_peak_step": flops / (ms * 1e-3) / 1e12 / peak,
@@ -496,7 +496,7 @@ def batch_bench_main(args, w, sizes, config):
         line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
+                "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
                 "config": config, "energy": energy, "algorithmic_flops_per_step": flops,
                 "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
                 "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,

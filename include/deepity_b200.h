@@ -70,11 +70,17 @@ typedef enum dpc_opt
  * the tensor cores where the shape allows) — the mode judged at 1e-4 against the CPU
  * reference.  TF32: one tensor-core pass with fp32 accumulation, the analogue of the
  * reference's default cuBLAS TF32 math mode (src/backend/cuda/CUDABackendCore.cu:54-67,
- * IComputeBackend::SetAllowTF32); judged at the reference's own 1e-2 CPU-vs-GPU bound. */
+ * IComputeBackend::SetAllowTF32); judged at the reference's own 1e-2 CPU-vs-GPU bound.
+ * MIXED (not the default, no counterpart in the reference): the state path -- forward sweep,
+ * settling passes, energy -- as in FP32; the gradient path of the tensor-core layers -- the
+ * prediction refresh before learning and the two weight-shaped products -- as in TF32, when
+ * every weight optimizer is SGD.  The TF32 rounding (5e-4 relative) then lands on the UPDATE
+ * of W, not on W; judged at 1e-3. */
 typedef enum dpc_precision
 {
   DPC_PRECISION_FP32 = 0,
-  DPC_PRECISION_TF32 = 1
+  DPC_PRECISION_TF32 = 1,
+  DPC_PRECISION_MIXED = 2
 } dpc_precision;
 
 typedef struct dpc_ctx dpc_ctx;

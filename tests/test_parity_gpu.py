@@ -154,6 +154,17 @@ def test_adam_on_tensor_core_layers(built_library):
     compare_outputs(ref, run_gpu(case, precision="fp32"), ADAM_TOL, "adam on tensor cores")
 
 
+def test_mixed_precision_mode_bound(built_library):
+    """precision="mixed": state path in 3xTF32, gradient path of the tensor-core layers in one
+    TF32 pass (SGD only): held to 1e-3, and tighter than the all-TF32 mode."""
+    case = dict(kind="dkp", sizes=[512] + [512] * 24 + [10], batch=1024, T=2, steps=3, seed=3,
+                hyper=dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.0, act="tanh"))
+    ref = run_oracle(case)
+    mixed = compare_outputs(ref, run_gpu(case, precision="mixed"), 1e-3, "mixed")
+    tf32 = compare_outputs(ref, run_gpu(case, precision="tf32"), TF32_TOL, "tf32")
+    assert mixed < tf32
+
+
 def test_deep_stack_at_benchmark_layer_shape(built_library):
     """48 layers of the deep-stack benchmark's shape (batch 1024, width 512): many tiles per
     CTA through the persistent pair kernels, the staged epilogue operands and the sequential
