@@ -198,7 +198,8 @@ class _Network:
         self._inference_rate = inference_rate
 
     def set_precision(self, precision: str) -> None:
-        """'fp32' (parity with the CPU reference at 1e-4) or 'tf32' (one tensor-core pass)."""
+        """'fp32' (parity with the CPU reference at 1e-4), 'tf32' (one tensor-core pass, 1e-2) or
+        'mixed' (fp32 state path, tf32 gradient products when all weight optimizers are SGD, 1e-3)."""
         self._option("precision", {"fp32": 0, "tf32": 1, "mixed": 2}[precision])
 
     def set_use_graph(self, enabled: bool) -> None:
