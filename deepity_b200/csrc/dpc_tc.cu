@@ -6,9 +6,14 @@
 //   * tcgen05.mma (kind::tf32, M=128, N=128|256, K=8) issued by one thread, fp32 accumulators
 //     in tensor memory, double-buffered so the epilogue of tile i overlaps the main loop of
 //     tile i+1;
-//   * fp32 mode = 3xTF32: the raw fp32 tile feeds the tensor core as the "high" part (the
-//     hardware reads the top 19 bits), four extra warps compute the exact remainders into a
+//   * fp32 mode, scheme 1 = 3xTF32: the raw fp32 tile feeds the tensor core as the "high" part
+//     (the hardware reads the top 19 bits), four extra warps compute the exact remainders into a
 //     second pair of tiles, and each k-step issues A*B_lo + A_lo*B + A*B;
+//   * fp32 mode, scheme 2 = 3xBF16 (kind::f16): the four extra warps split the raw tile into
+//     bf16(x) and bf16(x - bf16(x)) tiles in a second ring of slots, rewritten into the bf16
+//     operand layouts (K-major 64-byte swizzle, MN-major 128-byte swizzle), and each k-step
+//     issues hi*mid + mid*hi + hi*hi: half the tensor-pipe time and power of scheme 1 at a
+//     per-product error of 2^-16, used when every weight optimizer is SGD;
 //   * the predictive-coding elementwise work runs in the epilogue straight out of tensor
 //     memory: bias + activation + error + energy + feedback error (forward), the state
 //     update (feedback), the SGD weight update (weight-shaped product).
@@ -27,6 +32,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+
+#include <cuda_bf16.h>
 
 #include "dpc_internal.h"
 #include "dpc_math.cuh"
@@ -254,6 +261,24 @@ __device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, ui
                "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
                : "memory");
 }
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
 {
   uint32_t r[32];
@@ -357,6 +382,93 @@ __device__ __forceinline__ void st8(float* p, const float* r)
 // layer.  The operand read from the layer above is fetched one chunk ahead when PREFETCH.
 // The fields of the layer table the forward epilogue needs, fetched BEFORE the warp waits for
 // the accumulator so their latency overlaps the main loop (registers are scarce: only these).
+// ---- BF16 split of a raw fp32 tile (THREE_X == 2): hi = bf16(x), mid = bf16(x - hi); the three
+// products hi*mid, mid*hi, hi*hi drop terms of relative size 2^-16 only.
+__device__ __forceinline__ void split8(const float4& a, const float4& b, uint4& hi, uint4& mid)
+{
+  auto two = [](float x0, float x1, uint32_t& h, uint32_t& m) {
+    const __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
+    const __nv_bfloat162 mm = __floats2bfloat162_rn(x0 - __low2float(hh), x1 - __high2float(hh));
+    h = *reinterpret_cast<const uint32_t*>(&hh);
+    m = *reinterpret_cast<const uint32_t*>(&mm);
+  };
+  two(a.x, a.y, hi.x, mid.x);
+  two(a.z, a.w, hi.y, mid.y);
+  two(b.x, b.y, hi.z, mid.z);
+  two(b.z, b.w, hi.w, mid.w);
+}
+// K-major.  Raw: ROWS rows of 32 floats, 128 bytes per row, 16-byte chunks xor-ed with (row & 7)
+// (what TMA's 128-byte swizzle wrote).  Out: ROWS rows of 32 bf16, 64 bytes per row, atoms of 8
+// rows, 16-byte chunks xor-ed with ((row >> 1) & 3): the K-major 64-byte-swizzle operand layout.
+// Eight neighbouring lanes take the eight rows of an atom: loads and stores are conflict-free.
+template <int ROWS>
+__device__ __forceinline__ void split_kmajor(const uint8_t* raw, uint8_t* hi, uint8_t* mid, int tid)
+{
+  // work item idx = tid + 128 j covers row r0 + 32 j, k-chunk kc: the swizzle terms depend on
+  // (r & 7) only, so they are per-thread constants.  All loads are issued before any store (the
+  // compiler cannot prove that the output tiles do not alias the raw one).
+  constexpr int NIT = ROWS * 4 / 128;
+  const int r0 = ((tid >> 5) << 3) | (tid & 7), kc = (tid >> 3) & 3;
+  if (ROWS * 4 < 128 && tid >= ROWS * 4)
+    return;
+  const uint8_t* src0 = raw + r0 * 128 + (((2 * kc) ^ (r0 & 7)) << 4);
+  const uint8_t* src1 = raw + r0 * 128 + (((2 * kc + 1) ^ (r0 & 7)) << 4);
+  const int off = (r0 >> 3) * 512 + (r0 & 7) * 64 + ((kc ^ ((r0 >> 1) & 3)) << 4);
+  constexpr int N = NIT > 0 ? NIT : 1;
+  float4 a[N], b[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j)
+  {
+    a[j] = *reinterpret_cast<const float4*>(src0 + j * 4096);
+    b[j] = *reinterpret_cast<const float4*>(src1 + j * 4096);
+  }
+#pragma unroll
+  for (int j = 0; j < N; ++j)
+  {
+    uint4 h, m;
+    split8(a[j], b[j], h, m);
+    *reinterpret_cast<uint4*>(hi + off + j * 2048) = h;
+    *reinterpret_cast<uint4*>(mid + off + j * 2048) = m;
+  }
+}
+// MN-major.  Raw: slabs of 32 columns, each 32 k-rows of 128 bytes, 32-byte units xor-ed with
+// (k & 3).  Out: blocks of 64 columns, each 32 k-rows of 128 bytes (64 bf16), 16-byte chunks
+// xor-ed with (k & 7): the MN-major 128-byte-swizzle operand layout.  Neighbouring lanes pair rows
+// k and k+4 and read their halves in opposite order, which keeps loads and stores conflict-free.
+template <int E>
+__device__ __forceinline__ void split_mnmajor(const uint8_t* raw, uint8_t* hi, uint8_t* mid, int tid)
+{
+  // work item idx = tid + 128 j covers slab j, k-row k, 32-byte unit u: per-thread constants
+  constexpr int N = E / 32;
+  const int l = tid & 31, p = l & 1, u = (l >> 1) & 3;
+  const int k = ((tid >> 5) << 3) + (l >> 3) + (p << 2);
+  const uint8_t* unit = raw + k * 128 + ((u ^ (k & 3)) << 5);
+  float4 first[N], second[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j)
+  {
+    first[j] = *reinterpret_cast<const float4*>(unit + j * 4096 + (p << 4));
+    second[j] = *reinterpret_cast<const float4*>(unit + j * 4096 + ((p ^ 1) << 4));
+  }
+#pragma unroll
+  for (int j = 0; j < N; ++j)
+  {
+    // (first, second) is (upper, lower) half on odd lanes: convert in load order, then put the
+    // packed words in column order with selects instead of a divergent branch
+    uint4 h, m;
+    split8(first[j], second[j], h, m);
+    if (p)
+    {
+      h = make_uint4(h.z, h.w, h.x, h.y);
+      m = make_uint4(m.z, m.w, m.x, m.y);
+    }
+    const int c = ((j & 1) << 2) | u;
+    const int off = (j >> 1) * 4096 + k * 128 + ((c ^ (k & 7)) << 4);
+    *reinterpret_cast<uint4*>(hi + off) = h;
+    *reinterpret_cast<uint4*>(mid + off) = m;
+  }
+}
+
 struct FwdMeta
 {
   float a;
@@ -560,7 +672,8 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
 
 // ------------------------------------------------------------------------------ kernel
 // Warp roles: 0 TMA producer, 1 MMA issuer (+ tensor-memory owner), 2..9 epilogue,
-// 10..13 remainder ("lo") transform (3xTF32 only).
+// 10..13 operand split (fp32 modes only): THREE_X == 1 writes the TF32 remainder tile beside the
+// raw one; THREE_X == 2 reads the raw tile and writes bf16 "hi" and "mid" tiles into a second ring.
 // PAIR: two CTAs of a cluster (cta_group::2) compute one 256 x BN tile.  Each CTA stages its own
 // 128 rows of A and its own half of B (BN/2 rows) and holds its 128 rows of the accumulator in
 // its own tensor memory, so per output element half as many operand bytes cross L2 -> SM and
@@ -568,7 +681,7 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
 // KS = 2 (sequential sweep only): two CTAs of a cluster share one 128 x BN tile, each running
 // the main loop over half of K; they exchange the half of the partial tile the other one
 // finishes through distributed shared memory.  Halves every CTA's operand traffic per layer.
-template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
+template <int OP, int BN, int THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
 struct Cfg
 {
   static constexpr int RX_BYTES = KS == 2 ? 128 * 32 * 4 : 0; // partial tile from the peer
@@ -578,11 +691,22 @@ struct Cfg
   static constexpr int TILE_M = PAIR ? 2 * BM : BM;   // rows of D per work item
   static constexpr int A_BYTES = BM * TBK * 4;
   static constexpr int B_BYTES = BN_LOCAL * TBK * 4;
-  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (THREE_X ? 2 : 1);
+  // THREE_X: 0 one TF32 pass; 1 three TF32 passes over (x, x - tf32(x)); 2 three BF16 passes over
+  // (bf16(x), bf16(x - bf16(x))) at twice the tensor rate.
+  static constexpr bool B16 = THREE_X == 2;
+  static constexpr int RAWB = A_BYTES + B_BYTES;
+  // B16: two rings of RAWB-byte slots.  NR raw slots (TMA -> split warps) are held only while a
+  // load is in flight and being split; NB slots of [A hi][A mid][B hi][B mid] (split warps ->
+  // tensor core) only while the MMAs read them.  Otherwise one ring of STAGES stages.
+  static constexpr int SLOTS_RAW = (196608 - RX_BYTES) / RAWB;
+  static constexpr int NB = 2; // (3 + 3 slots measured the same as 4 + 2)
+  static constexpr int NR = SLOTS_RAW - NB > 6 ? 6 : (SLOTS_RAW - NB < 2 ? 2 : SLOTS_RAW - NB);
+  static constexpr int STAGE_BYTES = B16 ? RAWB : RAWB * (THREE_X ? 2 : 1);
   // at most 8 stages: the barrier block after the ring is sized for that
   static constexpr int STAGES_RAW =
       (196608 - ((PAIR && OP == TC_FWD && !THREE_X) ? 4 * BM * 32 * 4 : 0) - RX_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW);
+  static constexpr int STAGES = B16 ? NR : (STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW));
+  static constexpr int RING_BYTES = B16 ? (NR + NB) * RAWB : STAGES * STAGE_BYTES;
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS =
       (2 + EPI_WARPS + (THREE_X ? 4 : 0) + ((PAIR && OP == TC_FWD) ? 1 : 0)) * 32;
@@ -596,8 +720,9 @@ struct Cfg
   static constexpr int IN_BYTES = BM * 32 * 4;
   static constexpr int IN_BUFS = STAGE_IN ? (THREE_X ? 2 : 4) : 0;
   static constexpr int SMEM_BYTES =
-      STAGES * STAGE_BYTES + IN_BUFS * IN_BYTES + RX_BYTES + 1024 /*align*/ + 512 /*barriers*/;
-  static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
+      RING_BYTES + IN_BUFS * IN_BYTES + RX_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr uint32_t FMT = B16 ? 1u : 2u; // operand format: 1 = BF16, 2 = TF32
+  static constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1u : 0u) << 15) |
                                     ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TILE_M >> 4) << 24);
   static_assert(!PAIR || (BM == 128 && BN % 64 == 0), "pair tiles are 256 x BN");
@@ -605,7 +730,7 @@ struct Cfg
                 "the K-split sweep uses 128 x 64 tiles");
 };
 
-template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
+template <int OP, int BN, int THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
 __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1)
     pc_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const __grid_constant__ CUtensorMap mapU, const TcParams P)
@@ -615,13 +740,14 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
-  uint8_t* in_base = smem + C::STAGES * C::STAGE_BYTES; // staged operand of the layer above
+  uint8_t* in_base = smem + C::RING_BYTES; // staged operand of the layer above
   uint8_t* rx_base = in_base + C::IN_BUFS * C::IN_BYTES; // K-split sweep: peer's partial tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(rx_base + C::RX_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + C::STAGES;
   uint64_t* xf = bars + 2 * C::STAGES;
-  uint64_t* tfull = bars + 3 * C::STAGES;
+  uint64_t* rempty = bars + 3 * C::STAGES; // B16: raw slot read by the split warps
+  uint64_t* tfull = bars + 4 * C::STAGES;
   uint64_t* tempty = tfull + 2;
   uint64_t* in_full = tempty + 2;
   uint64_t* in_empty = in_full + 4;
@@ -649,6 +775,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
       mbar_init(&xf[s], PAIR ? 8 : 4); // transform warps of both CTAs arrive on the leader's
+      mbar_init(&rempty[s], 4);
     }
     for (int a = 0; a < 2; ++a)
     {
@@ -721,12 +848,15 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         {
           if (s == 0 && !(t == t_begin && kb == 0))
             phase ^= 1;
-          if (!(PAIR ? mbar_wait_cluster(&empty[s], phase, abort_flag)
-                     : mbar_wait(&empty[s], phase, abort_flag)))
+          if (!(C::B16 ? mbar_wait(&rempty[s], phase, abort_flag)
+                       : (PAIR ? mbar_wait_cluster(&empty[s], phase, abort_flag)
+                               : mbar_wait(&empty[s], phase, abort_flag))))
           {
             alive = false;
             break;
           }
+          if (C::B16) // the split warps' reads of the slot come before the copy that refills it
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           uint8_t* a_dst = stage_base + s * C::STAGE_BYTES;
           uint8_t* b_dst = a_dst + C::A_BYTES;
           const int k0 = ((int)krank * kblocks + kb) * TBK;
@@ -796,13 +926,22 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
       uint32_t phase = 0; // parity to wait for on full[s] / xf[s]
       bool alive = true;
       const uint32_t a_lbo = C::A_MN ? TBK * 128 : 16, b_lbo = C::B_MN ? TBK * 128 : 16;
-      const uint32_t a_adv = C::A_MN ? 1024 : UMMA_K * 4, b_adv = C::B_MN ? 1024 : UMMA_K * 4;
-      // MN-major tiles: 4 k-rows of 128 bytes per swizzle atom (512 B between k-groups), slabs of
-      // 32 columns TBK*128 bytes apart.  K-major tiles: 8 rows per atom (1024 B between groups).
-      const uint32_t a_sbo = C::A_MN ? 512 : 1024, b_sbo = C::B_MN ? 512 : 1024;
-      const uint32_t a_lay = C::A_MN ? 1 : 2, b_lay = C::B_MN ? 1 : 2;
-      const uint64_t da0 = make_desc(smem_u32(stage_base), a_lbo, a_sbo, a_lay);
-      const uint64_t db0 = make_desc(smem_u32(stage_base) + C::A_BYTES, b_lbo, b_sbo, b_lay);
+      // 32-bit tiles, MN-major: 4 k-rows of 128 bytes per swizzle atom (512 B between k-groups),
+      // slabs of 32 columns TBK*128 bytes apart; K-major: 8 rows per atom (1024 B between groups).
+      // BF16 tiles, MN-major: blocks of 64 columns TBK*128 bytes apart, 8 k-rows of 128 bytes per
+      // atom, 16 k-rows per instruction; K-major: 64-byte rows, 8 per atom (512 B between groups).
+      const uint32_t a_adv = C::B16 ? (C::A_MN ? 2048 : 32) : (C::A_MN ? 1024 : UMMA_K * 4);
+      const uint32_t b_adv = C::B16 ? (C::B_MN ? 2048 : 32) : (C::B_MN ? 1024 : UMMA_K * 4);
+      const uint32_t a_sbo = C::B16 ? (C::A_MN ? 1024 : 512) : (C::A_MN ? 512 : 1024);
+      const uint32_t b_sbo = C::B16 ? (C::B_MN ? 1024 : 512) : (C::B_MN ? 512 : 1024);
+      const uint32_t a_lay = C::B16 ? (C::A_MN ? 2 : 4) : (C::A_MN ? 1 : 2);
+      const uint32_t b_lay = C::B16 ? (C::B_MN ? 2 : 4) : (C::B_MN ? 1 : 2);
+      // BF16 split: the slots of [A hi][A mid][B hi][B mid] follow the NR raw slots
+      constexpr uint32_t OPB = C::B16 ? C::NR * C::RAWB : 0;
+      constexpr int MS = C::B16 ? C::NB : C::STAGES; // slots the tensor core cycles through
+      const uint64_t da0 = make_desc(smem_u32(stage_base) + OPB, a_lbo, a_sbo, a_lay);
+      const uint64_t db0 = make_desc(smem_u32(stage_base) + OPB + C::A_BYTES, b_lbo, b_sbo, b_lay);
+      constexpr int KSTEPS = C::B16 ? TBK / 16 : TBK / UMMA_K;
       for (int t = t_begin; t < t_end && alive; t += t_step, ++tile_iter)
       {
         const int acc = tile_iter & 1;
@@ -828,13 +967,30 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           const uint64_t sa = da0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
           const uint64_t sb = db0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
 #pragma unroll
-          for (int ks = 0; ks < TBK / UMMA_K; ++ks)
+          for (int ks = 0; ks < KSTEPS; ++ks)
           {
             const uint64_t da = sa + (uint64_t)(ks * (a_adv >> 4));
             const uint64_t db = sb + (uint64_t)(ks * (b_adv >> 4));
             const uint32_t d_tmem = d_tmem0 + (ks % C::KSPLIT) * BN;
             const uint32_t first = C::KSPLIT > 1 ? (kb != 0) : ((kb | ks) != 0);
-            if (THREE_X)
+            if (C::B16)
+            {
+              const uint64_t dam = da + (uint64_t)((C::A_BYTES / 2) >> 4);
+              const uint64_t dbm = db + (uint64_t)((C::B_BYTES / 2) >> 4);
+              if (PAIR)
+              {
+                tc_mma_bf16_pair(d_tmem, da, dbm, C::IDESC, first);
+                tc_mma_bf16_pair(d_tmem, dam, db, C::IDESC, 1);
+                tc_mma_bf16_pair(d_tmem, da, db, C::IDESC, 1);
+              }
+              else
+              {
+                tc_mma_bf16(d_tmem, da, dbm, C::IDESC, first);
+                tc_mma_bf16(d_tmem, dam, db, C::IDESC, 1);
+                tc_mma_bf16(d_tmem, da, db, C::IDESC, 1);
+              }
+            }
+            else if (THREE_X)
             {
               const uint64_t dal = da + (uint64_t)((C::A_BYTES + C::B_BYTES) >> 4);
               const uint64_t dbl = db + (uint64_t)((C::A_BYTES + C::B_BYTES) >> 4);
@@ -864,7 +1020,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           }
           else
             tc_commit(&empty[s]);
-          if (++s == C::STAGES)
+          if (++s == MS)
             s = 0, phase ^= 1;
         }
         if (alive)
@@ -1159,8 +1315,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
     // when it reads the raw tile as TF32.  Elementwise on identical offsets, so the swizzled
     // layout of the tile carries over unchanged.
     const int tid = threadIdx.x - (2 + C::EPI_WARPS) * 32;
-    int s = 0;
-    uint32_t phase = 0;
+    int s = 0, sb = 0;
+    uint32_t phase = 0, phase_b = 1; // phase_b: parity to wait for on empty[sb] (B16)
     bool alive = true;
     for (int t = t_begin; t < t_end && alive; t += t_step)
     {
@@ -1170,6 +1326,41 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         {
           alive = false;
           break;
+        }
+        if (C::B16)
+        {
+          // the slot the tensor core reads must have been released by its last MMAs
+          if (!(PAIR ? mbar_wait_cluster(&empty[sb], phase_b, abort_flag)
+                     : mbar_wait(&empty[sb], phase_b, abort_flag)))
+          {
+            alive = false;
+            break;
+          }
+          uint8_t* raw = stage_base + s * C::RAWB;
+          uint8_t* out = stage_base + (C::NR + sb) * C::RAWB;
+          if (C::A_MN)
+            split_mnmajor<BM>(raw, out, out + C::A_BYTES / 2, tid);
+          else
+            split_kmajor<BM>(raw, out, out + C::A_BYTES / 2, tid);
+          if (C::B_MN)
+            split_mnmajor<C::BN_LOCAL>(raw + C::A_BYTES, out + C::A_BYTES,
+                                       out + C::A_BYTES + C::B_BYTES / 2, tid);
+          else
+            split_kmajor<C::BN_LOCAL>(raw + C::A_BYTES, out + C::A_BYTES,
+                                      out + C::A_BYTES + C::B_BYTES / 2, tid);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0)
+          {
+            mbar_arrive(&rempty[s]); // the raw slot may be refilled
+            if (PAIR)
+              mbar_arrive_cluster(lead_xf + (uint32_t)(sb * 8));
+            else
+              mbar_arrive(&xf[sb]);
+          }
+          if (++sb == C::NB)
+            sb = 0, phase_b ^= 1;
+          continue;
         }
         const float4* src = reinterpret_cast<const float4*>(stage_base + s * C::STAGE_BYTES);
         float4* dst = reinterpret_cast<float4*>(stage_base + s * C::STAGE_BYTES + C::A_BYTES +
@@ -1260,7 +1451,7 @@ bool make_map(CUtensorMap* map, const float* base, int cols, int rows, int layer
   return r == CUDA_SUCCESS;
 }
 
-template <int OP, int BN, bool THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
+template <int OP, int BN, int THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
 int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P,
            const CUtensorMap* up = nullptr)
 {
@@ -1474,16 +1665,33 @@ static bool pair_ok(int rows, int cols)
   return !off && rows % 256 == 0 && cols % 256 == 0;
 }
 
-// DPC_PRECISION_MIXED: gradient-path products in one TF32 pass when every weight optimizer is
-// SGD (an Adam-type update would turn the TF32 rounding of a near-zero gradient into a full step).
-static bool fast_grad(const dpc_plan* p)
+static bool all_sgd(const dpc_plan* p)
 {
-  if (p->ctx->precision != DPC_PRECISION_MIXED)
-    return false;
   for (int i = 0; i < p->n; ++i)
     if (p->h[i].next_size > 0 && p->h[i].opt != DPC_OPT_SGD)
       return false;
   return true;
+}
+
+// DPC_PRECISION_MIXED: gradient-path products in one TF32 pass when every weight optimizer is
+// SGD (an Adam-type update would turn the TF32 rounding of a near-zero gradient into a full step).
+static bool fast_grad(const dpc_plan* p)
+{
+  return p->ctx->precision == DPC_PRECISION_MIXED && all_sgd(p);
+}
+
+// fp32 mode: how the operands are split for the tensor cores.  2 = three BF16 passes over
+// (bf16(x), bf16(x - bf16(x))): per-product error 2^-16, measured 2e-5 on whole train steps against
+// the 1e-4 bound, at twice the tensor rate of 1 = three TF32 passes (error 2^-21).  Adam-type
+// updates amplify rounding noise up to a full step per element, so networks that use them keep
+// scheme 1; so does anything run with DPC_FP32_SCHEME=tf32x3.  One scheme per plan: the sweep and
+// the settling passes must round alike for the errors right after the sweep to vanish.
+static int split_scheme(const dpc_plan* p)
+{
+  const char* env = getenv("DPC_FP32_SCHEME");
+  if (env && !strcmp(env, "tf32x3"))
+    return 1;
+  return all_sgd(p) ? 2 : 1;
 }
 
 static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int M, int N, int K,
@@ -1521,6 +1729,7 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
   const bool refresh =
       (flags & DPC_FWD_FE) && !(flags & DPC_FWD_ERR_NEXT) && (flags & DPC_FWD_TRANSIENT);
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || (refresh && fast_grad(p));
+  const int scheme = split_scheme(p);
   if (pair_ok(B, H))
   {
     TcParams P = base_params(p, st, first, count, B, H, H, 256, flags, 0, 256);
@@ -1537,14 +1746,16 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
       else if ((flags & DPC_FWD_FE) && !(flags & DPC_FWD_ERR_NEXT))
         P.stage_in = 2, up = &st->eup_km;
     }
-    return tf32 ? launch<TC_FWD, 256, false, 128, true>(p, st, st->z_km, st->w_km128, P, up)
-                : launch<TC_FWD, 256, true, 128, true>(p, st, st->z_km, st->w_km128, P, up);
+    return tf32 ? launch<TC_FWD, 256, 0, 128, true>(p, st, st->z_km, st->w_km128, P, up)
+         : scheme == 2 ? launch<TC_FWD, 256, 2, 128, true>(p, st, st->z_km, st->w_km128, P, up)
+                       : launch<TC_FWD, 256, 1, 128, true>(p, st, st->z_km, st->w_km128, P, up);
   }
   if (tf32)
-    return launch<TC_FWD, 256, false>(p, st, st->z_km, st->w_km256,
+    return launch<TC_FWD, 256, 0>(p, st, st->z_km, st->w_km256,
                                       base_params(p, st, first, count, B, H, H, 256, flags, 0));
-  return launch<TC_FWD, 128, true>(p, st, st->z_km, st->w_km128,
-                                   base_params(p, st, first, count, B, H, H, 128, flags, 0));
+  TcParams P = base_params(p, st, first, count, B, H, H, 128, flags, 0);
+  return scheme == 2 ? launch<TC_FWD, 128, 2>(p, st, st->z_km, st->w_km128, P)
+                     : launch<TC_FWD, 128, 1>(p, st, st->z_km, st->w_km128, P);
 }
 
 // The sequential forward sweep over layers [first, first+count) of the run as ONE persistent
@@ -1576,6 +1787,7 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   if (e != cudaSuccess)
     return cuda_fail(e, "cudaMemsetAsync(chain counters)");
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  const int scheme = split_scheme(p);
   // K-split variant: 128 x 64 tiles, two CTAs (one cluster) per tile with half of K each.
   // Summing K in two halves rounds differently from the settling passes' single accumulation,
   // so right after the sweep e = z - mu is ~1e-7 where it is exactly 0 with matching orders
@@ -1591,14 +1803,17 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
     TcParams Q = base_params(p, st, first, count, B, H, H, 64, flags, 0);
     Q.chain = 1, Q.chain_counters = st->chain_counters, Q.trace = st->trace;
     Q.chain_target = (H / 64) * 2 * 8; // column tiles x CTAs per tile x epilogue warps
-    return tf32 ? launch<TC_FWD, 64, false, 128, false, 2>(p, st, st->z_km, st->w_km64, Q)
-                : launch<TC_FWD, 64, true, 128, false, 2>(p, st, st->z_km, st->w_km64, Q);
+    return tf32 ? launch<TC_FWD, 64, 0, 128, false, 2>(p, st, st->z_km, st->w_km64, Q)
+         : scheme == 2 ? launch<TC_FWD, 64, 2, 128, false, 2>(p, st, st->z_km, st->w_km64, Q)
+                       : launch<TC_FWD, 64, 1, 128, false, 2>(p, st, st->z_km, st->w_km64, Q);
   }
   if (BNC == 32)
-    return tf32 ? launch<TC_FWD, 32, false>(p, st, st->z_km, st->w_km32, P)
-                : launch<TC_FWD, 32, true>(p, st, st->z_km, st->w_km32, P);
-  return tf32 ? launch<TC_FWD, 64, false>(p, st, st->z_km, st->w_km64, P)
-              : launch<TC_FWD, 64, true>(p, st, st->z_km, st->w_km64, P);
+    return tf32 ? launch<TC_FWD, 32, 0>(p, st, st->z_km, st->w_km32, P)
+         : scheme == 2 ? launch<TC_FWD, 32, 2>(p, st, st->z_km, st->w_km32, P)
+                       : launch<TC_FWD, 32, 1>(p, st, st->z_km, st->w_km32, P);
+  return tf32 ? launch<TC_FWD, 64, 0>(p, st, st->z_km, st->w_km64, P)
+         : scheme == 2 ? launch<TC_FWD, 64, 2>(p, st, st->z_km, st->w_km64, P)
+                       : launch<TC_FWD, 64, 1>(p, st, st->z_km, st->w_km64, P);
 }
 
 int tc_update_state(dpc_plan* p, int first, int count)
@@ -1608,17 +1823,20 @@ int tc_update_state(dpc_plan* p, int first, int count)
     return 1;
   const int H = p->run.width, B = p->batch;
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  const int scheme = split_scheme(p);
   if (pair_ok(B, H))
   {
     TcParams P = base_params(p, st, first, count, B, H, H, 256, 0, 0, 256);
-    return tf32 ? launch<TC_FB, 256, false, 128, true>(p, st, st->fe_km, st->w_mn, P)
-                : launch<TC_FB, 256, true, 128, true>(p, st, st->fe_km, st->w_mn, P);
+    return tf32 ? launch<TC_FB, 256, 0, 128, true>(p, st, st->fe_km, st->w_mn, P)
+         : scheme == 2 ? launch<TC_FB, 256, 2, 128, true>(p, st, st->fe_km, st->w_mn, P)
+                       : launch<TC_FB, 256, 1, 128, true>(p, st, st->fe_km, st->w_mn, P);
   }
   if (tf32)
-    return launch<TC_FB, 256, false>(p, st, st->fe_km, st->w_mn,
+    return launch<TC_FB, 256, 0>(p, st, st->fe_km, st->w_mn,
                                      base_params(p, st, first, count, B, H, H, 256, 0, 0));
-  return launch<TC_FB, 128, true>(p, st, st->fe_km, st->w_mn,
-                                  base_params(p, st, first, count, B, H, H, 128, 0, 0));
+  TcParams P = base_params(p, st, first, count, B, H, H, 128, 0, 0);
+  return scheme == 2 ? launch<TC_FB, 128, 2>(p, st, st->fe_km, st->w_mn, P)
+                     : launch<TC_FB, 128, 1>(p, st, st->fe_km, st->w_mn, P);
 }
 
 int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
@@ -1638,18 +1856,20 @@ int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
   }
   const int H = p->run.width, B = p->batch;
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || fast_grad(p);
+  const int scheme = split_scheme(p);
   if (pair_ok(H, H))
   {
     TcParams P = base_params(p, st, first, count, H, H, B, 256, decay_w ? 1 : 0, mode, 256);
-    return tf32 ? launch<TC_WG, 256, false, 128, true>(p, st, st->fe_mn, st->z_mn, P)
-                : launch<TC_WG, 256, true, 128, true>(p, st, st->fe_mn, st->z_mn, P);
+    return tf32 ? launch<TC_WG, 256, 0, 128, true>(p, st, st->fe_mn, st->z_mn, P)
+         : scheme == 2 ? launch<TC_WG, 256, 2, 128, true>(p, st, st->fe_mn, st->z_mn, P)
+                       : launch<TC_WG, 256, 1, 128, true>(p, st, st->fe_mn, st->z_mn, P);
   }
   if (tf32)
-    return launch<TC_WG, 256, false>(
+    return launch<TC_WG, 256, 0>(
         p, st, st->fe_mn, st->z_mn,
         base_params(p, st, first, count, H, H, B, 256, decay_w ? 1 : 0, mode));
-  return launch<TC_WG, 128, true>(
-      p, st, st->fe_mn, st->z_mn,
-      base_params(p, st, first, count, H, H, B, 128, decay_w ? 1 : 0, mode));
+  TcParams P = base_params(p, st, first, count, H, H, B, 128, decay_w ? 1 : 0, mode);
+  return scheme == 2 ? launch<TC_WG, 128, 2>(p, st, st->fe_mn, st->z_mn, P)
+                     : launch<TC_WG, 128, 1>(p, st, st->fe_mn, st->z_mn, P);
 }
 } // namespace dpc
