@@ -165,6 +165,20 @@ def test_mixed_precision_mode_bound(built_library):
     assert mixed < tf32
 
 
+def test_both_fp32_operand_splits(built_library, monkeypatch):
+    """fp32 mode has two operand splits on the tensor cores: three BF16 passes (the default when
+    every weight optimizer is SGD) and three TF32 passes (Adam-type networks, or on request).
+    Both are held to the fp32 bound on the same SGD network; the TF32 split is the tighter one."""
+    case = dict(kind="dkp", sizes=[512] + [512] * 12 + [10], batch=1024, T=2, steps=3, seed=5,
+                hyper=dict(lr=1e-2, ir=0.1, fl=1e-3, lmbda=0.0, act="tanh"))
+    ref = run_oracle(case)
+    bf16 = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "3xBF16 split")
+    monkeypatch.setenv("DPC_FP32_SCHEME", "tf32x3")
+    tf32 = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "3xTF32 split")
+    print(f"worst relative error: 3xBF16 {bf16:.2e}, 3xTF32 {tf32:.2e}")
+    assert tf32 <= bf16
+
+
 def test_deep_stack_at_benchmark_layer_shape(built_library):
     """48 layers of the deep-stack benchmark's shape (batch 1024, width 512): many tiles per
     CTA through the persistent pair kernels, the staged epilogue operands and the sequential
