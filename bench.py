@@ -513,8 +513,9 @@ def main():
                     "frac": gbs / hbm_peak,
                     "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback"}
     else:
-        # 3xTF32: three tensor passes per product -> tensor-bound; the denominator is the measured
-        # bf16 peak, of which fp32-accurate arithmetic can reach at most 1/6
+        # fp32 mode: three tensor passes per product (3xBF16 on SGD networks, else 3xTF32) ->
+        # tensor-bound; the denominator is the measured bf16 peak, of which fp32-accurate
+        # arithmetic can reach at most 1/3 (3xBF16) or 1/6 (3xTF32)
         roofline = {"bound": "tensor", "achieved": tflops, "peak": peak_tf, "unit": "TFLOP/s",
                     "frac": tflops / peak_tf, "peak_source": peak_src}
     roofline.update({"kernel": "grouped forward GEMM of a settling pass + error + feedback-error "
