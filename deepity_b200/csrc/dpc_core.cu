@@ -747,16 +747,18 @@ static int launch_dfa_proj(dpc_plan* p, int first, int count, int from_output)
       mxn = std::max(mxn, p->h[k].next_size);
     if (v)
     {
-      dim3 grid(cdiv(mxn, 256), cdiv(p->batch, DFA_ROWS), c);
+      const int rpb =
+          cdiv(mxn, 256) * cdiv(p->batch, DFA4_ROWS) * c >= 4 * p->ctx->sm_count ? DFA4_ROWS : 32;
+      dim3 grid(cdiv(mxn, 256), cdiv(p->batch, rpb), c);
       const int ts4 = cdiv(std::max(p->h[i].terminal_size, 1), 4);
       if (ts4 <= 1)
-        dfa_proj4_kernel<1><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+        dfa_proj4_kernel<1><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb);
       else if (ts4 == 2)
-        dfa_proj4_kernel<2><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+        dfa_proj4_kernel<2><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb);
       else if (ts4 == 3)
-        dfa_proj4_kernel<3><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+        dfa_proj4_kernel<3><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb);
       else
-        dfa_proj4_kernel<4><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output);
+        dfa_proj4_kernel<4><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb);
     }
     else
     {

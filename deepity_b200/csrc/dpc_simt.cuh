@@ -669,11 +669,15 @@ __global__ void dfa_proj_kernel(const dpc_layer* __restrict__ layers, int first,
 }
 
 // The same projection, four output units per thread with 128-bit accesses, for the common
+// Rows per block of the aligned kernel: its per-thread rows of Psi are strided 4-byte loads that
+// cost as much L2 traffic as 32 rows of useful data, so a block amortises them over up to 128 rows
+// (the host picks fewer when that would leave SMs without a block).
+constexpr int DFA4_ROWS = 128;
 // aligned case: next_size a multiple of 4, terminal_size <= 4*TS4, 16-byte aligned rows.
 template <int TS4>
 __global__ void __launch_bounds__(64)
     dfa_proj4_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
-                     const float* __restrict__ eT, int from_output)
+                     const float* __restrict__ eT, int from_output, int rows_per_block)
 {
   const int li = first + blockIdx.z;
   if (li + 1 >= n_layers)
@@ -683,12 +687,12 @@ __global__ void __launch_bounds__(64)
   if (L.next_size <= 0 || Lup.Psi == nullptr)
     return;
   const int TS = L.terminal_size, n = L.next_size;
-  const int b0 = blockIdx.y * DFA_ROWS;
+  const int b0 = blockIdx.y * rows_per_block; // rows_per_block <= DFA4_ROWS
   const int j = (blockIdx.x * 64 + threadIdx.x) * 4;
   if (b0 >= batch || (int)(blockIdx.x * 256) >= n)
     return;
-  __shared__ __align__(16) float es[DFA_ROWS][TS4 * 4];
-  for (int idx = threadIdx.x; idx < DFA_ROWS * TS4 * 4; idx += 64)
+  __shared__ __align__(16) float es[DFA4_ROWS][TS4 * 4];
+  for (int idx = threadIdx.x; idx < rows_per_block * TS4 * 4; idx += 64)
   {
     const int r = idx / (TS4 * 4), k = idx - r * (TS4 * 4);
     es[r][k] = (b0 + r < batch && k < TS) ? eT[(size_t)(b0 + r) * TS + k] : 0.0f;
@@ -704,8 +708,8 @@ __global__ void __launch_bounds__(64)
       psi[c][k] = k < TS ? Lup.Psi[(size_t)(j + c) * Lup.psi_stride + k] : 0.0f;
   const bool out_d = from_output && act_has_output_deriv(L.act);
   const float* src = out_d ? Lup.z : L.preact;
-  const int rows = min(DFA_ROWS, batch - b0);
-#pragma unroll 4
+  const int rows = min(rows_per_block, batch - b0);
+#pragma unroll 8
   for (int r = 0; r < rows; ++r)
   {
     const size_t o = (size_t)(b0 + r) * n + j;
