@@ -721,6 +721,7 @@ struct Cfg
   static constexpr int IN_BUFS = STAGE_IN ? (THREE_X ? 2 : 4) : 0;
   static constexpr int SMEM_BYTES =
       RING_BYTES + IN_BUFS * IN_BYTES + RX_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static_assert(SMEM_BYTES <= 232448, "more than the 227 KB of shared memory a CTA can have");
   static constexpr uint32_t FMT = B16 ? 1u : 2u; // operand format: 1 = BF16, 2 = TF32
   static constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1u : 0u) << 15) |
                                     ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
