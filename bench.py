@@ -22,14 +22,27 @@ JSON line with
                 layers, scaled to the full depth by the layer ratio;
 * clocks sampled with nvidia-smi during the timed region.
 
-``--impl reference`` times only the CPU leg, with the threads the reference's own policy
-picks, and prints the same line shape with ``"impl": "reference"``.
+``--impl reference`` times only the CPU leg and prints the same line shape with
+``"impl": "reference"``: every one of its K steps is one train step of a BOUNDED SAMPLE of the
+workload (the same network cut to fewer hidden layers, chosen so that the K+W steps end within
+a couple of minutes); ``ms_per_step`` is the measured time of such a sample step and ``value``
+is scaled to the full depth by the ratio of algorithmic FLOPs (``"extrapolated": true`` and
+the sample depth are stated at the top level of the line).
+
+Multi-GPU (launched by torchrun, one rank per GPU): the deep stack is layer-sharded, strong
+scaling; the line then also carries ``batch_sharded_c4``, the wide FullPCN workload
+batch-sharded over the same ranks.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+
+# The compiled reference runs OpenMP regions AND OpenBLAS's own thread pool; with OpenMP's
+# default active spinning the two pools fight for the cores of a small host (measured: 6x
+# slower at 8 threads on 8 hardware threads).  Must be set before libgomp is loaded.
+os.environ.setdefault("OMP_WAIT_POLICY", "PASSIVE")
 import statistics
 import subprocess
 import sys
@@ -86,26 +99,7 @@ def synth(w, sizes, seed=1234, wseed=99):
     return x, y, params
 
 
-def algorithmic_flops(kind, sizes, B, T):
-    """GEMM FLOPs one train step needs under the reference's CPU semantics (2*M*N*K each):
-    per weight layer T+3 (DirectKP), T+4 (Full) or T+1 (Simple) forward products, T feedback
-    products and the weight-shaped products (learn, plus the direct-feedback update when the
-    layer above owns feedback weights), plus the skinny Psi / projection products; the clamped
-    input layer evaluates its prediction once and is never updated."""
-    n = len(sizes)
-    total = 0.0
-    for i in range(n - 1):
-        s, nx, ts = sizes[i], sizes[i + 1], sizes[-1]
-        g = 2.0 * B * s * nx
-        if kind == "simple":
-            fwd, fb, wg = T + 1, T, 1
-        else:
-            fwd, fb, wg = (T + 3 if kind == "dkp" else T + 4), T, (2 if i + 2 < n else 1)
-            total += 2.0 * B * s * ts + (2.0 * B * nx * ts if i + 2 < n else 0.0)
-        if i == 0:
-            fwd, fb = 1, 0
-        total += g * (fwd + fb + wg)
-    return total
+from deepity_b200.flops import algorithmic_flops  # noqa: E402
 
 
 # ------------------------------------------------------------------------------ clocks
@@ -151,13 +145,23 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------ CPU leg
-def cpu_reference_leg(w, steps, warmup, budget_layers=None):
-    """The reference's CPU train step on a depth-reduced copy of the workload.
+def host_cpu_info():
+    """What bounds the CPU arm on this host: the affinity mask and the cgroup CPU quota."""
+    info = {"affinity_cpus": len(os.sched_getaffinity(0)), "os_cpu_count": os.cpu_count(),
+            "cgroup_cpu_quota": None, "omp_wait_policy": os.environ.get("OMP_WAIT_POLICY")}
+    try:
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()[:2]
+        if quota != "max":
+            info["cgroup_cpu_quota"] = float(quota) / float(period)
+    except Exception:
+        pass
+    return info
 
-    Returns dict(value=samples/s scaled to the full depth, cores, kind, sample)."""
+
+def _cpu_net(w, hidden):
+    """The reference network (or its numpy restatement) cut to `hidden` hidden layers, with
+    the benchmark's seeded parameters; returns (run one step, kind, x, y)."""
     from oracle import ref as oref
-    full_hidden = w["hidden"]
-    hidden = min(full_hidden, budget_layers or (64 if w["width"] >= 512 else full_hidden))
     sizes = sizes_of(w, hidden)
     x, y, params = synth(w, sizes)
     opts = {}
@@ -166,8 +170,6 @@ def cpu_reference_leg(w, steps, warmup, budget_layers=None):
     if oref.available():
         kind = "reference"
         net = oref.RefNet(w["kind"], sizes, w["batch"], act=w["act"], options=opts, **HYPER)
-        info = oref.host_info()
-        cores = info["omp_threads"]
     else:
         from oracle.pc_oracle import PCOracle
         kind = "port"
@@ -175,27 +177,94 @@ def cpu_reference_leg(w, steps, warmup, budget_layers=None):
         if w["kind"] == "full":
             kw.update(cross_entropy=True, optimizer="ADAM", psi_optimizer="ADAM")
         net = PCOracle(w["kind"], sizes, w["batch"], act=w["act"], **kw)
-        cores = os.cpu_count()
     for l, p in enumerate(params):
         for nm, v in p.items():
             net.set(l, nm, v)
     run = (lambda: net.train_step_python(x, y, w["T"])) if (kind == "port" and w["kind"] == "simple") \
         else (lambda: net.train_step(x, y, w["T"]))
+    return run, kind, sizes
+
+
+def cpu_reference_leg(w, steps, warmup, budget_s=25.0, sample_hidden=None):
+    """The reference's CPU train step on a depth-reduced copy of the workload.
+
+    The sample depth is picked from a calibration step on a 16-layer cut so that
+    warmup + steps sample steps take about `budget_s` seconds (capped at 256 layers), unless
+    `sample_hidden` fixes it.  Threads: the reference's own DynamicThread policy first
+    (include/deepity/utils/Optimize.h:108-131); if half the affinity mask is faster on this
+    host (OpenMP plus OpenBLAS pools oversubscribing it), that count is used instead and both
+    timings are reported.  Returns samples/s scaled to the full depth by the FLOP ratio."""
+    from oracle import ref as oref
+    host = host_cpu_info()
+    full_hidden = w["hidden"]
+    threads_policy = threads_used = None
+    calib = {}
+    deep = w["width"] >= 512 and full_hidden > 32
+    if deep and oref.available():
+        run16, _, sizes16 = _cpu_net(w, 16)
+        run16()
+        threads_policy = oref.host_info()["omp_threads"]
+        t0 = time.perf_counter()
+        run16()
+        t_policy = time.perf_counter() - t0
+        half = max(1, min(threads_policy, host["affinity_cpus"] // 2))
+        oref.set_threads(half)
+        run16()
+        t0 = time.perf_counter()
+        run16()
+        t_half = time.perf_counter() - t0
+        threads_used = half if t_half < t_policy else threads_policy
+        oref.set_threads(threads_used)
+        per_layer = min(t_half, t_policy) / 17.0
+        calib = {"calibration_layers": 16, "ms_per_step_policy_threads": t_policy * 1e3,
+                 "ms_per_step_half_affinity_threads": t_half * 1e3,
+                 "ms_per_layer_at_16": per_layer * 1e3}
+        if sample_hidden is None:
+            want = budget_s / ((steps + warmup) * per_layer)
+            sample_hidden = 256 if want >= 256 else 128 if want >= 128 else 64 if want >= 64 else 32
+    hidden = min(full_hidden, sample_hidden or (64 if deep else full_hidden))
+    run, kind, sizes = _cpu_net(w, hidden)
     for _ in range(warmup):
         run()
-    t0 = time.perf_counter()
+    if kind == "reference":
+        info = oref.host_info()
+        if threads_used is None:
+            threads_policy = threads_used = info["omp_threads"]
+        cores, blas = int(threads_used), info["blas"]
+    else:
+        cores, blas = os.cpu_count(), "numpy"
+    times = []
     for _ in range(steps):
+        t0 = time.perf_counter()
         e = run()
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    # Scale the sample's time to the full depth by the ratio of algorithmic FLOPs.
-    scale = (algorithmic_flops(w["kind"], sizes_of(w), w["batch"], w["T"]) /
-             algorithmic_flops(w["kind"], sizes, w["batch"], w["T"]))
-    sps = w["batch"] / (dt * scale)
-    sample = (f"{w['desc']} cut to {hidden} hidden layers ({steps} steps of {dt * 1e3:.1f} ms); "
-              f"scaled x{scale:.2f} to {full_hidden} layers" if hidden != full_hidden
-              else f"{w['desc']} at full size, {steps} steps of {dt * 1e3:.1f} ms")
-    return {"value": sps, "unit": "samples/s", "cores": int(cores), "kind": kind,
-            "sample": sample, "ms_per_step_sample": dt * 1e3, "last_energy": float(e)}
+        times.append(time.perf_counter() - t0)
+    dt_mean, dt_min, dt_med = sum(times) / len(times), min(times), statistics.median(times)
+    sample_flops = algorithmic_flops(w["kind"], sizes, w["batch"], w["T"])
+    scale = algorithmic_flops(w["kind"], sizes_of(w), w["batch"], w["T"]) / sample_flops
+    sps = w["batch"] / (dt_mean * scale)
+    sample = (f"{w['desc']} cut to {hidden} hidden layers ({steps} steps, mean {dt_mean * 1e3:.1f} "
+              f"min {dt_min * 1e3:.1f} median {dt_med * 1e3:.1f} ms); scaled x{scale:.2f} to "
+              f"{full_hidden} layers by algorithmic FLOPs" if hidden != full_hidden
+              else f"{w['desc']} at full size, {steps} steps, mean {dt_mean * 1e3:.1f} ms")
+    return {"value": sps, "unit": "samples/s", "cores": cores, "kind": kind, "sample": sample,
+            "extrapolated": hidden != full_hidden, "sample_hidden_layers": hidden,
+            "scale_to_full_depth": scale, "steps_run": steps, "warmup_run": warmup,
+            "ms_per_step_sample": dt_mean * 1e3, "ms_per_step_sample_min": dt_min * 1e3,
+            "ms_per_step_sample_median": dt_med * 1e3,
+            "ms_per_layer_sample": dt_mean * 1e3 / (hidden + 1),
+            "cpu_gflops": sample_flops / dt_mean / 1e9, "threads_reference_policy": threads_policy,
+            "threads_used": cores, "blas": blas, "host": host, "last_energy": float(e), **calib}
+
+
+CPU_KEYS = ("value", "unit", "cores", "kind", "sample", "extrapolated", "sample_hidden_layers",
+            "scale_to_full_depth", "steps_run", "ms_per_step_sample", "ms_per_step_sample_min",
+            "ms_per_step_sample_median", "ms_per_layer_sample", "ms_per_layer_at_16", "cpu_gflops",
+            "threads_reference_policy", "threads_used", "blas", "host",
+            "ms_per_step_policy_threads", "ms_per_step_half_affinity_threads")
+
+
+def cpu_keys(leg):
+    return {k: leg[k] for k in CPU_KEYS if k in leg}
 
 
 # ------------------------------------------------------------------------------ conv (C5)
@@ -264,7 +333,7 @@ def conv_main(args):
               "hyper": {k: HYPER[k] for k in ("lr", "ir", "lmbda")}, "precision": "fp32",
               "l2": "L2 flushed between timed steps"}
     if args.impl == "reference":
-        leg = conv_cpu_leg(layers, B, T, max(1, min(args.steps, 3)), min(args.warmup, 1))
+        leg = conv_cpu_leg(layers, B, T, max(1, args.steps), max(1, args.warmup))
         print(json.dumps({"impl": "reference", "metric": "train_step samples/sec",
                           "value": leg["value"], "unit": "samples/s", "n_gpus": args.gpus,
                           "steps": args.steps, "warmup": args.warmup,
@@ -377,6 +446,227 @@ def build_net(w, sizes, precision):
     return net
 
 
+def load_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+# DRAM bytes per 1024x512x512 layer of one launch of the dominant kernel, measured with ncu
+# (dram__bytes_read.sum + dram__bytes_write.sum) as the difference between a 127-layer and a
+# 63-layer capture divided by 64, so that the dirty lines a launch leaves in L2 cancel.
+# None until such a pair of captures exists for the current kernel.
+NCU_DRAM_BYTES_PER_LAYER = None
+
+
+def forward_roofline(B, sizes, k_ms, precision, passes, peaks):
+    """Roofline object of the grouped forward GEMM of a settling pass (layers 1..n-2).
+
+    Both floors are stated: tensor time = passes x algorithmic FLOPs / measured dense bf16
+    burst peak (a TF32 pass counts twice: half the bf16 rate), HBM time = algorithmic bytes /
+    measured copy bandwidth.  `bound` is the larger floor; achieved/peak/frac follow it."""
+    n = len(sizes)
+    k_flops = sum(2.0 * B * sizes[i] * sizes[i + 1] for i in range(1, n - 1))
+    # per layer: read z and W (operands), z of the layer above; write e of the layer above, fe
+    k_bytes = sum(4.0 * (B * sizes[i] + sizes[i] * sizes[i + 1] + 3 * B * sizes[i + 1])
+                  for i in range(1, n - 1))
+    peak_tf = peaks.get("bf16_tflops") or 1590.0
+    hbm = peaks.get("hbm_gbs") or 6650.0
+    src = "measured (MEASURED_PEAKS.json)" if peaks else "fallback (6.65 TB/s, 1.59 PFLOP/s)"
+    t = k_ms * 1e-3
+    tflops, gbs = k_flops / t / 1e12, k_bytes / t / 1e9
+    tensor_floor_ms = passes * k_flops / (peak_tf * 1e12) * 1e3
+    hbm_floor_ms = k_bytes / (hbm * 1e9) * 1e3
+    bound = "hbm" if hbm_floor_ms >= tensor_floor_ms else "tensor"
+    r = {"bound": bound,
+         "achieved": gbs if bound == "hbm" else tflops,
+         "peak": hbm if bound == "hbm" else peak_tf,
+         "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
+         "frac": gbs / hbm if bound == "hbm" else tflops / peak_tf,
+         "peak_source": src + (": hbm_gbs" if bound == "hbm" else ": bf16_tflops (burst; kernel timed alone)"),
+         "traffic": (NCU_DRAM_BYTES_PER_LAYER * (n - 2)
+                     if NCU_DRAM_BYTES_PER_LAYER and (B, sizes[1]) == (1024, 512) else None),
+         "kernel": "grouped forward GEMM of a settling pass + bias/activation/error/feedback-error "
+                   "epilogue (pc_tc_kernel<0,256,...> CTA pairs)",
+         "launch_ms": k_ms, "layers_per_launch": n - 2,
+         "algorithmic_flops_per_launch": k_flops, "algorithmic_bytes_per_launch": k_bytes,
+         "tensor_passes": passes,
+         "tflops_at_algorithmic_flops": tflops, "frac_of_bf16_peak": tflops / peak_tf,
+         "frac_of_bf16_peak_counting_passes": passes * tflops / peak_tf,
+         "hbm_gbs_at_algorithmic_bytes": gbs, "frac_of_hbm_peak": gbs / hbm,
+         "tensor_floor_ms": tensor_floor_ms, "hbm_floor_ms": hbm_floor_ms,
+         "frac_of_binding_floor": max(tensor_floor_ms, hbm_floor_ms) / k_ms}
+    return r
+
+
+def plan_paths(lib, net, n_layers):
+    """Which kernels a plan runs: the tensor-core run and what falls to the CUDA cores."""
+    import ctypes
+    first, count = ctypes.c_int(), ctypes.c_int()
+    plan = lib.dpcn_plan(net._h)
+    lib.dpc_plan_tensor_run(plan, ctypes.byref(first), ctypes.byref(count))
+    buf = ctypes.create_string_buffer(256)
+    lib.dpc_plan_describe(plan, buf, 256)
+    return {"tensor_core_layers": [first.value, first.value + count.value],
+            "cuda_core_weight_layers": (n_layers - 1) - count.value,
+            "kernels": buf.value.decode()}
+
+
+def dist_setup():
+    import torch
+    import torch.distributed as dist
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def timed_ranks(fn, steps, stream):
+    """K calls bracketed by barrier + synchronize, CUDA events on `stream`, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(steps):
+        fn()
+    b.record(stream)
+    b.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b) / steps], device="cuda", dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def layer_sharded_main(args, w, sizes, config):
+    """The N>1 arm: layer-sharded deep stack, strong scaling (the same network and batch at
+    every N), timed on the device with CUDA events, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from deepity_b200.sharded import ShardedDKPPCN
+
+    rank, world, local = dist_setup()
+    net = ShardedDKPPCN(sizes, w["batch"], HYPER, act=w["act"], precision=args.precision)
+    x, y, params = synth(w, sizes)
+    for l, p in enumerate(params):
+        for nm, v in p.items():
+            net.set_param(l, nm, v)
+    del params
+    xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+    xh, yh = torch.from_numpy(x).pin_memory(), torch.from_numpy(y).pin_memory()
+    T, B = w["T"], w["batch"]
+    for _ in range(args.warmup):
+        energy = net.train_step(xd, yd, T)
+    with ClockSampler(local) as clk:
+        n0 = net.eng.launch_count
+        ms = timed_ranks(lambda: net.train_step(xd, yd, T, read_energy=False), args.steps,
+                         net.eng.stream)
+        launches = net.eng.launch_count - n0
+        energy = net.train_step(xd, yd, T)
+        e2e_ms = timed_ranks(lambda: net.train_step(xh, yh, T), args.steps, net.eng.stream)
+    lc = torch.tensor([launches], device="cuda", dtype=torch.int64)
+    dist.all_reduce(lc)
+    flops = net.train_step_flops(T)
+    ranges = net.ranges
+    net.close()
+    del net
+    side = None if args.no_side else batch_sharded_measure(args, dict(WORKLOADS["c4"]))
+    if rank == 0:
+        peaks = load_peaks()
+        peak = (peaks.get("bf16_tflops_sustained") or 1590.0) * world
+        config = dict(config, parallelism=f"layer-sharded x{world}",
+                      layers_per_rank=[e - b for b, e in ranges])
+        line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": DTYPES[args.precision], "data": "synthetic",
+                "config": config, "energy": energy, "algorithmic_flops_per_step": flops,
+                "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
+                "frac_of_gemm_peak_step": flops / (ms * 1e-3) / 1e12 / peak,
+                "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8},
+                "gpu_launches": int(lc.item()), "clocks": clk.summary(),
+                "roofline": None, "cpu_baseline": None, "batch_sharded_c4": side}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def batch_sharded_measure(args, w, steps=None):
+    """The wide FullPCN workload batch-sharded over the ranks of the job (strong scaling: the
+    same network and GLOBAL batch at every N); returns the measurement on every rank."""
+    import torch
+    import torch.distributed as dist
+    from deepity_b200.sharded import BatchSharded
+
+    rank, world, local = dist_setup()
+    sizes = sizes_of(w)
+    x, y, params = synth(w, sizes)
+    T, B = w["T"], w["batch"]
+    steps = steps or max(3, min(args.steps, 10))
+
+    def build(local_batch):
+        net = build_net(dict(w, batch=local_batch), sizes, args.precision)
+        for l, p in enumerate(params):
+            for nm, v in p.items():
+                net.set_tensor(l, nm, v)
+        return net
+    net = BatchSharded(build, B)
+    lib = net.net._lib
+    stream = torch.cuda.ExternalStream(lib.dpc_stream(lib.dpcn_context(net.net._h)))
+    xd = torch.from_numpy(np.ascontiguousarray(net.rows(x))).cuda()
+    yd = torch.from_numpy(np.ascontiguousarray(net.rows(y))).cuda()
+    for _ in range(max(2, min(args.warmup, 3))):
+        energy = net.train_step_device(xd, yd, T)
+    n0 = net.net.launch_count
+    ms = timed_ranks(lambda: net.train_step_device(xd, yd, T, read_energy=False), steps, stream)
+    launches = net.net.launch_count - n0
+    energy = net.train_step_device(xd, yd, T)
+    e2e_ms = timed_ranks(lambda: net.train_step(x, y, T), steps, stream)
+    lc = torch.tensor([launches], device="cuda", dtype=torch.int64)
+    dist.all_reduce(lc)
+    flops = algorithmic_flops(w["kind"], sizes, B, T)
+    return {"workload": w["desc"], "parallelism": f"batch-sharded x{world}",
+            "rows_per_rank": B // world, "value": B / (ms * 1e-3), "unit": "samples/s",
+            "ms_per_step": ms, "steps": steps, "scaling": "strong", "energy": energy,
+            "algorithmic_flops_per_step": flops, "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
+            "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int((x.nbytes + y.nbytes) // world),
+                    "d2h_bytes_per_step": 8},
+            "gpu_launches": int(lc.item())}
+
+
+def batch_sharded_main(args, w, sizes, config):
+    """--workload c4 at N>1: the batch-sharded measurement as the headline of the line."""
+    import torch.distributed as dist
+    rank, world, local = dist_setup()
+    with ClockSampler(local) as clk:
+        m = batch_sharded_measure(args, w, steps=args.steps)
+    if rank == 0:
+        config = dict(config, parallelism=m["parallelism"], rows_per_rank=m["rows_per_rank"])
+        line = {"metric": "train_step samples/sec", "value": m["value"], "unit": "samples/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": DTYPES[args.precision], "data": "synthetic",
+                "config": config, "energy": m["energy"],
+                "algorithmic_flops_per_step": m["algorithmic_flops_per_step"],
+                "achieved_tflops_step": m["achieved_tflops_step"], "e2e": m["e2e"],
+                "gpu_launches": m["gpu_launches"], "clocks": clk.summary(),
+                "roofline": None, "cpu_baseline": None}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+DTYPES = {"fp32": "f32 (tensor-core layers: 3xBF16 operand split for SGD networks, 3xTF32 otherwise)",
+          "tf32": "tf32", "mixed": "f32 state path, tf32 gradient path"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -387,6 +677,10 @@ def main():
     ap.add_argument("--depth", type=int, default=None, help="override the hidden-layer count")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "mixed"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-side", action="store_true",
+                    help="skip the batch-sharded C4 measurement that rides along with C3")
+    ap.add_argument("--sample-depth", type=int, default=None,
+                    help="hidden layers of the CPU arm's bounded sample (default: calibrated)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", 0))
@@ -403,35 +697,42 @@ def main():
     B, T = w["batch"], w["T"]
     config = {"workload": w["desc"], "global_batch": B, "T": T, "layers": len(sizes) - 1,
               "hyper": HYPER, "precision": args.precision,
+              "parity_bound": "1e-4 relative per tensor for SGD networks; 5e-4 where an Adam-type "
+                              "optimizer is on; 1e-2 in tf32 mode; 1e-3 in mixed mode",
               "l2": "working set (z,e,preact,mu,fe,W of every layer) is far larger than the 126 MB L2"
               if args.workload in ("c3", "c4") else "L2 flushed between timed steps"}
 
     if args.impl == "reference":
         if rank != 0:
             return
-        leg = cpu_reference_leg(w, max(1, min(args.steps, 3)), min(args.warmup, 1))
+        # K steps and W warm-up steps of a bounded sample (see the module docstring)
+        leg = cpu_reference_leg(w, max(1, args.steps), max(1, args.warmup), budget_s=90.0,
+                                sample_hidden=args.sample_depth)
         line = {"impl": "reference", "metric": "train_step samples/sec", "value": leg["value"],
                 "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": B / leg["value"] * 1e3,
+                "warmup": args.warmup, "ms_per_step": leg["ms_per_step_sample"],
+                "ms_per_step_is": "one train step of the bounded sample (measured)",
+                "extrapolated": leg["extrapolated"],
+                "sample_hidden_layers": leg["sample_hidden_layers"],
+                "scale_to_full_depth": leg["scale_to_full_depth"],
+                "ms_per_step_full_depth_extrapolated": B / leg["value"] * 1e3,
+                "cpu_gflops": leg["cpu_gflops"],
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": config,
-                "cpu_baseline": {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "data": "synthetic", "config": config, "cpu_baseline": cpu_keys(leg),
                 "e2e": {"value": leg["value"], "unit": "samples/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return
 
     import torch
-    import torch.distributed as dist
     from deepity_b200 import _lib
 
     if world > 1:
-        from deepity_b200 import sharded
         # deep stacks shard by layers; wide, shallow networks by batch rows
         if w["kind"] == "dkp" and len(sizes) - 1 >= world:
-            sharded.bench_main(args, w, sizes, config)
+            layer_sharded_main(args, w, sizes, config)
         else:
-            sharded.batch_bench_main(args, w, sizes, config)
+            batch_sharded_main(args, w, sizes, config)
         return
 
     torch.cuda.set_device(0)
@@ -441,6 +742,7 @@ def main():
     for l, p in enumerate(params):
         for nm, v in p.items():
             net.set_tensor(l, nm, v)
+    del params
     xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
     xh, yh = x.ravel().copy(), y.ravel().copy()
     torch.cuda.synchronize()
@@ -465,6 +767,7 @@ def main():
         return total / steps
 
     flops = net.train_step_flops(T)
+    paths = plan_paths(lib, net, len(sizes))
     for _ in range(args.warmup):
         energy = net.train_step_device(xd, yd, T)
     lib.dpc_sync(lib.dpcn_context(net._h))
@@ -485,61 +788,98 @@ def main():
         plan = lib.dpcn_plan(net._h)
         n = len(sizes)
         fwd_flags = 2 | 8 | 256  # DPC_FWD_ERR_NEXT | DPC_FWD_FE | DPC_FWD_TRANSIENT
-        for _ in range(2):
+        for _ in range(3):
             lib.dpc_forward(plan, 1, n - 2, fwd_flags)
         k_ms = timed(lambda: lib.dpc_forward(plan, 1, n - 2, fwd_flags), max(args.steps, 5))
     clocks = clk.summary()
 
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
-    peak_tf = peaks.get("bf16_tflops_sustained") or 1590.0
-    peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback 1.59 PF"
-    hbm_peak = peaks.get("hbm_gbs") or 6650.0
-    # per layer: read z, W and z of the layer above, write e of the layer above and fe
-    k_flops = sum(2.0 * B * sizes[i] * sizes[i + 1] for i in range(1, n - 1))
-    k_bytes = sum(4.0 * (B * sizes[i] + sizes[i] * sizes[i + 1] + 3 * B * sizes[i + 1])
-                  for i in range(1, n - 1))
-    tflops = k_flops / (k_ms * 1e-3) / 1e12
-    gbs = k_bytes / (k_ms * 1e-3) / 1e9
-    # ncu (profiles/pc_tc_kernel_forward_ncu.md): 438.7 MB of DRAM traffic for the 63 layers of
-    # the captured small case = 6.96 MB per 1024x512x512 layer; it grows with the layer count
-    traffic = 6.96e6 * (n - 2) if (w["batch"], w["width"]) == (1024, 512) else None
-    if args.precision == "tf32":
-        # one TF32 pass: 57 FLOP per algorithmic byte, below the machine balance -> HBM-bound
-        roofline = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
-                    "frac": gbs / hbm_peak,
-                    "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback"}
-    else:
-        # fp32 mode: three tensor passes per product (3xBF16 on SGD networks, else 3xTF32) ->
-        # tensor-bound; the denominator is the measured bf16 peak, of which fp32-accurate
-        # arithmetic can reach at most 1/3 (3xBF16) or 1/6 (3xTF32)
-        roofline = {"bound": "tensor", "achieved": tflops, "peak": peak_tf, "unit": "TFLOP/s",
-                    "frac": tflops / peak_tf, "peak_source": peak_src}
-    roofline.update({"kernel": "grouped forward GEMM of a settling pass + error + feedback-error "
-                               "epilogue (pc_tc_kernel<0,256,*,128,1>)",
-                     "traffic": traffic, "launch_ms": k_ms,
-                     "algorithmic_flops_per_launch": k_flops,
-                     "algorithmic_bytes_per_launch": k_bytes,
-                     "tflops_at_algorithmic_flops": tflops, "tensor_peak_tflops_bf16": peak_tf,
-                     "hbm_gbs_at_algorithmic_bytes": gbs, "hbm_peak_gbs": hbm_peak})
+    peaks = load_peaks()
+    peak_tf = peaks.get("bf16_tflops_sustained") or 1400.0
+    # tensor passes per product: one TF32 pass = 2 bf16-rate passes; 3xBF16 = 3; 3xTF32 = 6
+    sgd = w["kind"] != "full"
+    passes = 2 if args.precision == "tf32" else (3 if sgd else 6)
+    roofline = forward_roofline(B, sizes, k_ms, args.precision, passes, peaks)
     line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": {"fp32": "f32", "tf32": "tf32", "mixed": "f32 state path, tf32 gradient path"}[
-                args.precision], "data": "synthetic",
-            "config": config, "energy": energy,
+            "dtype": DTYPES[args.precision], "data": "synthetic",
+            "config": config, "energy": energy, "paths": paths,
             "algorithmic_flops_per_step": flops, "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
             "frac_of_gemm_peak_step": flops / (ms * 1e-3) / 1e12 / peak_tf,
+            "gemm_peak_step_source": "bf16_tflops_sustained (kernel timed inside a long step)",
             "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(xh.nbytes + yh.nbytes), "d2h_bytes_per_step": 8},
             "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks}
+    if paths["cuda_core_weight_layers"] > 1 and args.workload in ("c3", "c4"):
+        print(f"bench: {paths['cuda_core_weight_layers']} weight layers of this workload run on the "
+              f"CUDA-core kernels ({paths['kernels']})", file=sys.stderr)
     if not args.no_cpu:
-        leg = cpu_reference_leg(w, 2, 1)
-        line["cpu_baseline"] = {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        leg = cpu_reference_leg(w, 5, 1, budget_s=25.0, sample_hidden=args.sample_depth)
+        line["cpu_baseline"] = cpu_keys(leg)
+        if args.workload == "c3" and leg["kind"] == "reference":
+            # the same cut on the GPU, same seeds and step count: the energies must agree
+            line["cpu_baseline"]["energy_check"] = sample_energy_check(w, leg, args.precision)
+    if args.workload == "c3" and not args.no_side and not args.depth:
+        del net, xd, yd
+        torch.cuda.empty_cache()
+        line["c4_single_gpu"] = single_gpu_side(dict(WORKLOADS["c4"]), args)
     print(json.dumps(line))
+
+
+def sample_energy_check(w, leg, precision):
+    """Runs the CPU arm's sample (same cut, seeds and number of steps) on the GPU and reports
+    the relative difference of the last step's energy."""
+    hidden = leg["sample_hidden_layers"]
+    sizes = sizes_of(w, hidden)
+    net = build_net(w, sizes, precision)
+    x, y, params = synth(w, sizes)
+    for l, p in enumerate(params):
+        for nm, v in p.items():
+            net.set_tensor(l, nm, v)
+    e = None
+    for _ in range(leg["steps_run"] + leg["warmup_run"]):
+        e = net.train_step(x, y, w["T"])
+    ref = leg["last_energy"]
+    return {"hidden_layers": hidden, "steps": leg["steps_run"] + leg["warmup_run"],
+            "cpu_energy": ref, "gpu_energy": e, "relative_difference": abs(e - ref) / max(1.0, abs(ref))}
+
+
+def single_gpu_side(w, args):
+    """The wide FullPCN workload on one GPU (rides along with the headline line so that the
+    batch-sharded figures of the multi-GPU lines have their N=1 point)."""
+    import torch
+    from deepity_b200 import _lib
+    lib = _lib.load()
+    sizes = sizes_of(w)
+    net = build_net(w, sizes, args.precision)
+    x, y, params = synth(w, sizes)
+    for l, p in enumerate(params):
+        for nm, v in p.items():
+            net.set_tensor(l, nm, v)
+    xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+    stream = torch.cuda.ExternalStream(lib.dpc_stream(lib.dpcn_context(net._h)))
+    T, B = w["T"], w["batch"]
+    steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        energy = net.train_step_device(xd, yd, T)
+
+    def timed(fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            fn()
+        b.record(stream)
+        b.synchronize()
+        return a.elapsed_time(b) / steps
+    ms = timed(lambda: net.train_step_device(xd, yd, T, read_energy=False))
+    energy = net.train_step_device(xd, yd, T)
+    e2e_ms = timed(lambda: net.train_step(x, y, T))
+    flops = net.train_step_flops(T)
+    return {"workload": w["desc"], "value": B / (ms * 1e-3), "unit": "samples/s", "ms_per_step": ms,
+            "steps": steps, "energy": energy, "algorithmic_flops_per_step": flops,
+            "achieved_tflops_step": flops / (ms * 1e-3) / 1e12, "paths": plan_paths(lib, net, len(sizes)),
+            "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8}}
 
 
 if __name__ == "__main__":

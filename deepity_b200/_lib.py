@@ -46,6 +46,10 @@ SIGNATURES = {
     "dpc_plan_set_terminal_error": (_i, [_vp, _vp]),
     "dpc_plan_set_chain_trace": (_i, [_vp, _vp]),
     "dpc_plan_tensor_run": (_i, [_vp, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
+    "dpc_plan_describe": (_i, [_vp, _cp, _i]),
+    "dpc_plan_invalidate": (_i, [_vp, _i, _i, _i]),
+    "dpc_plan_sync_operands": (_i, [_vp]),
+    "dpc_plan_set_wait_limit": (_i, [_vp, ctypes.c_double, _i]),
     "dpc_forward": (_i, [_vp, _i, _i, _i]),
     "dpc_project_forward": (_i, [_vp, _i, _i, _i]),
     "dpc_project_forward_ex": (_i, [_vp, _i, _i, _i, _i]),

@@ -447,7 +447,64 @@ int dpc_plan_tensor_run(dpc_plan* p, int* first, int* count)
   return DPC_OK;
 }
 
+int dpc_plan_describe(dpc_plan* p, char* buf, int buf_bytes)
+{
+  if (!p || !buf || buf_bytes <= 0)
+    return fail(DPC_ERR_INVALID, "dpc_plan_describe: null argument");
+  const std::string d = tc_describe(p);
+  snprintf(buf, (size_t)buf_bytes, "%s", d.c_str());
+  return DPC_OK;
+}
+
+int dpc_plan_invalidate(dpc_plan* p, int first, int count, int what)
+{
+  int rc = check_range(p, first, count);
+  if (rc != DPC_OK)
+    return rc;
+  if (what & DPC_WROTE_Z)
+    tc_touch(p, 0, first, count);
+  if (what & DPC_WROTE_FE)
+    tc_touch(p, 1, first, count);
+  if (what & DPC_WROTE_W)
+    tc_touch(p, 2, first, count);
+  return DPC_OK;
+}
+
+int dpc_plan_sync_operands(dpc_plan* p)
+{
+  if (!p)
+    return fail(DPC_ERR_INVALID, "null plan");
+  return tc_sync_planes(p);
+}
+
+int dpc_plan_set_wait_limit(dpc_plan* p, double milliseconds, int sweep_target_bias)
+{
+  if (!p)
+    return fail(DPC_ERR_INVALID, "null plan");
+  cudaDeviceProp prop;
+  DPC_CUDA(cudaGetDeviceProperties(&prop, p->ctx->device));
+  // clock64() counts SM clocks; take the maximum clock so the limit is never shorter than asked
+  const long long cycles =
+      milliseconds > 0.0 ? (long long)(milliseconds * 1e-3 * (double)prop.clockRate * 1e3) : 0;
+  tc_set_wait_limit(p, cycles, sweep_target_bias);
+  return DPC_OK;
+}
+
 // ------------------------------------------------------------------------------ phases
+// The CUDA-core kernels write the fp32 tensors only: tell the tensor-core path which of its
+// operand planes have gone stale.
+static void wrote(dpc_plan* p, int kind, int first, int count)
+{
+  if (p->run.count > 0 && count > 0)
+    tc_touch(p, kind, first, count);
+}
+enum
+{
+  K_Z = 0,
+  K_FE = 1,
+  K_W = 2
+};
+
 static int forward_simt(dpc_plan* p, int first, int count, int flags)
 {
   cudaStream_t st = p->ctx->stream;
@@ -476,6 +533,10 @@ static int forward_simt(dpc_plan* p, int first, int count, int flags)
     if (rc != DPC_OK)
       return rc;
   }
+  if (flags & DPC_FWD_FE)
+    wrote(p, K_FE, first, count);
+  if (flags & DPC_FWD_COPY_NEXT)
+    wrote(p, K_Z, first + 1, count);
   return DPC_OK;
 }
 
@@ -594,12 +655,14 @@ int dpc_feedback_error(dpc_plan* p, int first, int count)
     if ((rc = check_launch(p->ctx, "feedback_error kernel")) != DPC_OK)
       return rc;
   }
+  wrote(p, K_FE, first, count);
   return DPC_OK;
 }
 
 static int update_state_simt(dpc_plan* p, int first, int count)
 {
   cudaStream_t st = p->ctx->stream;
+  wrote(p, K_Z, first, count);
   for (int f = first; f < first + count; f += kMaxZ)
   {
     const int c = std::min(kMaxZ, first + count - f);
@@ -655,6 +718,7 @@ int dpc_epc_reconstruct(dpc_plan* p, int layer)
     return rc;
   if (layer == 0)
     return fail(DPC_ERR_INVALID, "dpc_epc_reconstruct: the input layer has nothing below it");
+  wrote(p, K_Z, layer, 1);
   epc_reconstruct_kernel<<<elem_blocks(p, (size_t)p->batch * p->h[layer].size), NTHREADS, 0,
                            p->ctx->stream>>>(p->d, layer, p->batch);
   return check_launch(p->ctx, "epc_reconstruct kernel");
@@ -673,6 +737,7 @@ int dpc_epc_adjoint(dpc_plan* p, int layer, int from_terminal, float scale, int 
   if (!src)
     return fail(DPC_ERR_INVALID, "dpc_epc_adjoint: the layer above has no adjoint buffer");
   cudaStream_t st = p->ctx->stream;
+  wrote(p, K_FE, layer, 1);
   epc_source_kernel<<<elem_blocks(p, (size_t)p->batch * L.next_size), NTHREADS, 0, st>>>(
       p->d, layer, p->batch, src);
   if ((rc = check_launch(p->ctx, "epc_source kernel")) != DPC_OK)
@@ -698,12 +763,15 @@ int dpc_relax(dpc_plan* p, int layer)
   if (rc != DPC_OK)
     return rc;
   dim3 grid(elem_blocks(p, (size_t)p->batch * p->h[layer].size), 1);
+  wrote(p, K_Z, layer, 1);
   relax_kernel<<<grid, NTHREADS, 0, p->ctx->stream>>>(p->d, layer, p->n, p->batch, 0);
   return check_launch(p->ctx, "relax kernel");
 }
 
 static int weight_gemm_simt(dpc_plan* p, int first, int count, int mode, int flags)
 {
+  if (!(mode & WG_GRAD_ONLY))
+    wrote(p, K_W, first, count);
   for (int f = first; f < first + count; f += kMaxZ)
   {
     const int c = std::min(kMaxZ, first + count - f);
@@ -726,6 +794,7 @@ static int weight_gemm_simt(dpc_plan* p, int first, int count, int mode, int fla
 static int launch_dfa_proj(dpc_plan* p, int first, int count, int from_output)
 {
   cudaStream_t st = p->ctx->stream;
+  wrote(p, K_FE, first, count);
   auto vec_ok = [&](int i)
   {
     const dpc_layer& L = p->h[i];
@@ -844,6 +913,7 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
         {
           const int cc = std::min(kMaxZ, f + c - g);
           dim3 grid(elem_blocks(p, max_w), cc);
+          wrote(p, K_W, g, cc);
           apply_gradients_kernel<<<grid, NTHREADS, 0, p->ctx->stream>>>(p->d, g, p->n, p->batch, 2, 0);
           if ((r = check_launch(p->ctx, "apply_gradients kernel")) != DPC_OK)
             return r;
@@ -870,6 +940,7 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
     if (center_rows)
     {
       dim3 gc(std::min(max_next, 1024), c);
+      wrote(p, K_W, f, c);
       center_rows_kernel<<<gc, 256, 0, st>>>(p->d, f, p->n);
       if ((rc = check_launch(p->ctx, "center_rows kernel")) != DPC_OK)
         return rc;
@@ -981,6 +1052,7 @@ int dpc_apply_gradients(dpc_plan* p, int first, int count, int which, int global
   {
     const int c = std::min(kMaxZ, first + count - f);
     dim3 grid(elem_blocks(p, max_w), c);
+    wrote(p, K_W, f, c);
     apply_gradients_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, global_batch, which, option ? 1 : 0);
     if ((rc = check_launch(p->ctx, "apply_gradients kernel")) != DPC_OK)
       return rc;

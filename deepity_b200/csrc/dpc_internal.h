@@ -77,4 +77,14 @@ int tc_weight_gemm(dpc_plan* plan, int first, int count, int mode, int decay_w =
 // out; DPC_ERR_TIMEOUT if it was raised.
 int tc_check_error(dpc_plan* plan);
 void tc_set_chain_trace(dpc_plan* plan, unsigned long long* buf);
+// Operand planes (bf16 hi/mid copies of the run's beliefs, feedback errors and weights that the
+// 3xBF16 kernels read).  tc_touch: something outside dpc_tc.cu wrote the fp32 tensors `kind`
+// (0 beliefs, 1 feedback errors, 2 weights) of layers [first, first+count); tc_sync_planes:
+// re-split everything that is stale now (before a CUDA graph of a step is recorded or replayed).
+void tc_touch(dpc_plan* plan, int kind, int first, int count);
+int tc_sync_planes(dpc_plan* plan);
+// Limit of every bounded device-side wait in clock cycles (<= 0: the default, ~2 s) and a bias
+// on the forward sweep's publication target (test hook: a target nothing reaches).
+void tc_set_wait_limit(dpc_plan* plan, long long cycles, int chain_target_bias);
+std::string tc_describe(dpc_plan* plan);
 } // namespace dpc

@@ -9,6 +9,8 @@
 // library holds that array (a little over 8 KB) until the process exits.
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include <cstdint>
 #include <string>
 
@@ -63,8 +65,9 @@ __global__ void __launch_bounds__(kStaticThreads)
   {
     __threadfence();
     double total = 0.0;
+    // The partial sums were written by other blocks: read them from L2, past this SM's L1.
     for (unsigned int b = 0; b < gridDim.x; ++b) // fixed order: the result is reproducible
-      total += scratch[b];
+      total += __ldcg(&scratch[b]);
     *energy_out = (float)(0.5 * total);
     *reinterpret_cast<unsigned int*>(&scratch[kStaticMaxBlocks]) = 0u; // ready for the next call
   }
@@ -72,7 +75,7 @@ __global__ void __launch_bounds__(kStaticThreads)
 
 // Device address of the scratch array, looked up once per device.
 constexpr int kMaxDevices = 64;
-double* g_scratch_addr[kMaxDevices] = {};
+std::atomic<double*> g_scratch_addr[kMaxDevices] = {};
 } // namespace
 
 int dpc_error_energy_static(void* stream, const float* z_dev, const float* mu_dev, float* e_dev,
@@ -92,7 +95,8 @@ int dpc_error_energy_static(void* stream, const float* z_dev, const float* mu_de
     return dpc::cuda_fail(err, "cudaGetDevice");
   if (device < 0 || device >= kMaxDevices)
     return dpc::fail(DPC_ERR_INVALID, "dpc_error_energy_static: device index out of range");
-  if (!g_scratch_addr[device])
+  double* scratch = g_scratch_addr[device].load(std::memory_order_acquire);
+  if (!scratch)
   {
     // Set-up, once per device, with that device current: the array's name is not a device
     // address in host code, so ask the runtime for it.
@@ -100,9 +104,10 @@ int dpc_error_energy_static(void* stream, const float* z_dev, const float* mu_de
     err = cudaGetSymbolAddress(&p, dpc_static_scratch);
     if (err != cudaSuccess || !p)
       return dpc::cuda_fail(err, "cudaGetSymbolAddress(dpc_static_scratch)");
-    g_scratch_addr[device] = static_cast<double*>(p);
+    // (two threads racing here store the same address)
+    scratch = static_cast<double*>(p);
+    g_scratch_addr[device].store(scratch, std::memory_order_release);
   }
-  double* scratch = g_scratch_addr[device];
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The ticket must start at zero even if an earlier call never completed.
   err = cudaMemsetAsync(scratch + kStaticMaxBlocks, 0, sizeof(double), st);

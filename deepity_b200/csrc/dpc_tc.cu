@@ -14,6 +14,11 @@
 //     operand layouts (K-major 64-byte swizzle, MN-major 128-byte swizzle), and each k-step
 //     issues hi*mid + mid*hi + hi*hi: half the tensor-pipe time and power of scheme 1 at a
 //     per-product error of 2^-16, used when every weight optimizer is SGD;
+//   * fp32 mode, scheme 3 = 3xBF16 from PRE-SPLIT operands: every kernel of this file that writes a
+//     belief, a feedback error or a weight of the run also writes its bf16 "hi" and "mid" planes
+//     (same bytes as the fp32 tensor), so the grouped kernels load tensor-core-ready tiles by TMA
+//     (128-byte rows of 64 bf16, 128-byte swizzle) and run the one-ring pipeline of the TF32 mode
+//     with three MMAs per k-step: same arithmetic as scheme 2, no split warps, no second ring;
 //   * the predictive-coding elementwise work runs in the epilogue straight out of tensor
 //     memory: bias + activation + error + energy + feedback error (forward), the state
 //     update (feedback), the SGD weight update (weight-shaped product).
@@ -32,6 +37,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <string>
+#include <vector>
 
 #include <cuda_bf16.h>
 
@@ -45,7 +52,13 @@ namespace
 constexpr int TBM = 128;  // UMMA M (rows of D per tile)
 constexpr int TBK = 32;   // fp32 elements per pipeline stage along K = one 128-byte swizzle row
 constexpr int UMMA_K = 8; // K of one tcgen05.mma.kind::tf32
-constexpr long long kWaitCycles = 4000000000LL; // ~2 s at 1.9 GHz
+constexpr long long kWaitCyclesDefault = 4000000000LL; // ~2 s at 1.9 GHz
+// The limit of every bounded wait of a launch: abort_flag[0] is the abort flag of the CTA,
+// abort_flag[2..3] hold the limit in clock cycles (written once by thread 0 at start-up).
+__device__ __forceinline__ long long wait_limit(volatile int* abort_flag)
+{
+  return *reinterpret_cast<volatile long long*>(abort_flag + 2);
+}
 
 enum
 {
@@ -68,6 +81,22 @@ struct TcState
   int* error_flag = nullptr; // device
   int* error_host = nullptr; // pinned
   int max_smem = 0;
+  long long wait_cycles = kWaitCyclesDefault;
+  int chain_target_bias = 0; // test hook: added to the sweep's publication target
+  // Pre-split operand planes (bf16 hi/mid) of the run's beliefs (count+1 layers), feedback
+  // errors and weights, their tensor maps (layer coordinate 2l + plane) and, per layer, whether
+  // the planes lag behind the fp32 tensor (1 = must be re-split before a kernel reads them).
+  __nv_bfloat16 *zp = nullptr, *fep = nullptr, *wp = nullptr;
+  CUtensorMap zp_km, zp_mn, fep_km, fep_mn, wp_km128, wp_km64, wp_mn;
+  std::vector<uint8_t> dirty[3];
+  bool planes = false;
+  bool warned_fallback = false;
+};
+enum
+{
+  PL_Z = 0,
+  PL_FE = 1,
+  PL_W = 2
 };
 
 struct TcParams
@@ -94,6 +123,12 @@ struct TcParams
   // (tensor map mapU covers the z arena), 2 = its stored error (mapU covers the e arena); the
   // tile is then brought into shared memory by TMA instead of per-lane global loads.
   int stage_in;
+  // Pre-split operand planes of the run (NULL: not maintained by this launch).  Layer r of the
+  // run (r = layer - run_first) has its "hi" plane at base + 2r * elems and its "mid" plane at
+  // base + (2r+1) * elems; beliefs have one layer more than the run (the layer above it).
+  __nv_bfloat16 *zp, *fep, *wp;
+  long long act_elems, w_elems; // elements per plane: batch x width, width x width
+  long long wait_cycles;        // limit of every bounded wait of this launch
 };
 
 // ------------------------------------------------------------------------------ PTX
@@ -140,7 +175,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         return true;
     if (*abort_flag)
       return false;
-    if (clock64() - t0 > kWaitCycles)
+    if (clock64() - t0 > wait_limit(abort_flag))
     {
       *abort_flag = 1;
       return false;
@@ -205,7 +240,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
         return true;
     if (*abort_flag)
       return false;
-    if (clock64() - t0 > kWaitCycles)
+    if (clock64() - t0 > wait_limit(abort_flag))
     {
       *abort_flag = 1;
       return false;
@@ -342,7 +377,7 @@ __device__ __forceinline__ bool chain_wait(const int* ctr, int target, volatile 
       break;
     if (*abort_flag)
       return false;
-    if (clock64() - t0 > kWaitCycles)
+    if (clock64() - t0 > wait_limit(abort_flag))
     {
       *abort_flag = 1;
       return false;
@@ -396,6 +431,15 @@ __device__ __forceinline__ void split8(const float4& a, const float4& b, uint4& 
   two(a.z, a.w, hi.y, mid.y);
   two(b.x, b.y, hi.z, mid.z);
   two(b.z, b.w, hi.w, mid.w);
+}
+// Eight consecutive elements of a tensor into its two operand planes (16-byte stores).
+__device__ __forceinline__ void st_planes8(__nv_bfloat16* hi, long long plane_elems, size_t off,
+                                           const float* v)
+{
+  uint4 h, m;
+  split8(make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]), h, m);
+  *reinterpret_cast<uint4*>(hi + off) = h;
+  *reinterpret_cast<uint4*>(hi + plane_elems + off) = m;
 }
 // K-major.  Raw: ROWS rows of 32 floats, 128 bytes per row, 16-byte chunks xor-ed with (row & 7)
 // (what TMA's 128-byte swizzle wrote).  Out: ROWS rows of 32 bf16, 64 bytes per row, atoms of 8
@@ -476,6 +520,7 @@ struct FwdMeta
   const float* b;
   const float* z;
   float *preact, *mu, *fe, *up_z, *up_e;
+  __nv_bfloat16 *fe_hi, *upz_hi; // operand planes of fe[l] and z[l+1], or NULL
 };
 
 __device__ __forceinline__ void load_fwd_meta(const TcParams& P, int li, FwdMeta& M)
@@ -490,6 +535,9 @@ __device__ __forceinline__ void load_fwd_meta(const TcParams& P, int li, FwdMeta
   }
   else
     M.up_z = M.up_e = nullptr, M.up_flags = 0;
+  const long long r = li - P.run_first;
+  M.fe_hi = P.fep ? P.fep + 2 * r * P.act_elems : nullptr;
+  M.upz_hi = P.zp ? P.zp + 2 * (r + 1) * P.act_elems : nullptr;
 }
 
 // Where the staged operand of the layer above sits (pair-mode forward only).
@@ -623,7 +671,11 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
           st8(L.mu + o + k, mu);
       }
       if (do_copy && active)
+      {
         st8(up_z + o + k, mu);
+        if (L.upz_hi)
+          st_planes8(L.upz_hi, P.act_elems, o + k, mu);
+      }
       if (do_err)
       {
 #pragma unroll
@@ -647,7 +699,11 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
         for (int q = 0; q < 8; ++q)
           e[q] *= d[q];
         if (active)
+        {
           st8(L.fe + o + k, e);
+          if (L.fe_hi)
+            st_planes8(L.fe_hi, P.act_elems, o + k, e);
+        }
       }
       if (tl >= 0 && c == grp && k == 0 && threadIdx.x == 64)
         trace_stamp(P, tl, 6);
@@ -689,11 +745,17 @@ struct Cfg
   static constexpr bool B_MN = (OP != TC_FWD);
   static constexpr int BN_LOCAL = PAIR ? BN / 2 : BN; // rows of B this CTA stages
   static constexpr int TILE_M = PAIR ? 2 * BM : BM;   // rows of D per work item
-  static constexpr int A_BYTES = BM * TBK * 4;
-  static constexpr int B_BYTES = BN_LOCAL * TBK * 4;
   // THREE_X: 0 one TF32 pass; 1 three TF32 passes over (x, x - tf32(x)); 2 three BF16 passes over
-  // (bf16(x), bf16(x - bf16(x))) at twice the tensor rate.
+  // (bf16(x), bf16(x - bf16(x))) split in the kernel, at twice the tensor rate; 3 the same three
+  // BF16 passes over operand planes that were split when the tensors were written.
   static constexpr bool B16 = THREE_X == 2;
+  static constexpr bool PRE = THREE_X == 3;
+  static constexpr bool BF = B16 || PRE;                  // bf16 MMAs (K = 16 per instruction)
+  static constexpr bool SPLITW = THREE_X == 1 || THREE_X == 2; // four operand-split warps
+  static constexpr int KB = PRE ? 64 : TBK; // elements of K per pipeline stage (128-byte rows)
+  // PRE: [hi plane][mid plane] of each operand, 2 bytes per element
+  static constexpr int A_BYTES = PRE ? BM * 64 * 2 * 2 : BM * TBK * 4;
+  static constexpr int B_BYTES = PRE ? BN_LOCAL * 64 * 2 * 2 : BN_LOCAL * TBK * 4;
   static constexpr int RAWB = A_BYTES + B_BYTES;
   // B16: two rings of RAWB-byte slots.  NR raw slots (TMA -> split warps) are held only while a
   // load is in flight and being split; NB slots of [A hi][A mid][B hi][B mid] (split warps ->
@@ -701,7 +763,7 @@ struct Cfg
   static constexpr int SLOTS_RAW = (196608 - RX_BYTES) / RAWB;
   static constexpr int NB = 2; // (3 + 3 slots measured the same as 4 + 2)
   static constexpr int NR = SLOTS_RAW - NB > 6 ? 6 : (SLOTS_RAW - NB < 2 ? 2 : SLOTS_RAW - NB);
-  static constexpr int STAGE_BYTES = B16 ? RAWB : RAWB * (THREE_X ? 2 : 1);
+  static constexpr int STAGE_BYTES = B16 ? RAWB : RAWB * (THREE_X == 1 ? 2 : 1);
   // at most 8 stages: the barrier block after the ring is sized for that
   static constexpr int STAGES_RAW =
       (196608 - ((PAIR && OP == TC_FWD && !THREE_X) ? 4 * BM * 32 * 4 : 0) - RX_BYTES) / STAGE_BYTES;
@@ -709,7 +771,7 @@ struct Cfg
   static constexpr int RING_BYTES = B16 ? (NR + NB) * RAWB : STAGES * STAGE_BYTES;
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS =
-      (2 + EPI_WARPS + (THREE_X ? 4 : 0) + ((PAIR && OP == TC_FWD) ? 1 : 0)) * 32;
+      (2 + EPI_WARPS + (SPLITW ? 4 : 0) + ((PAIR && OP == TC_FWD) ? 1 : 0)) * 32;
   // (Spreading the k-steps of a narrow tile over several accumulators was measured: it does not
   // shorten the main loop, whose per-k-block cost is the barrier/TMA handshake.)
   static constexpr int KSPLIT = 1;
@@ -722,7 +784,7 @@ struct Cfg
   static constexpr int SMEM_BYTES =
       RING_BYTES + IN_BUFS * IN_BYTES + RX_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static_assert(SMEM_BYTES <= 232448, "more than the 227 KB of shared memory a CTA can have");
-  static constexpr uint32_t FMT = B16 ? 1u : 2u; // operand format: 1 = BF16, 2 = TF32
+  static constexpr uint32_t FMT = BF ? 1u : 2u; // operand format: 1 = BF16, 2 = TF32
   static constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1u : 0u) << 15) |
                                     ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TILE_M >> 4) << 24);
@@ -754,7 +816,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
   uint64_t* in_empty = in_full + 4;
   uint64_t* rx_full = in_empty + 4;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(rx_full + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  // 8-byte aligned: [0] the abort flag, [2..3] the wait limit in cycles (see wait_limit())
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_per_layer = P.tiles_m * P.tiles_n;
@@ -767,7 +830,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
   const int t_begin = P.chain ? 0 : (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x);
   const int t_end = P.chain ? P.count : total_tiles;
   const int t_step = P.chain ? 1 : (PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x);
-  const int kblocks = P.K / TBK / KS;
+  const int kblocks = P.K / C::KB / KS;
 
   if (threadIdx.x == 0)
   {
@@ -790,6 +853,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
     }
     mbar_init(rx_full, 1);
     *abort_flag = 0;
+    *reinterpret_cast<volatile long long*>(abort_flag + 2) = P.wait_cycles;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -860,32 +924,49 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           uint8_t* a_dst = stage_base + s * C::STAGE_BYTES;
           uint8_t* b_dst = a_dst + C::A_BYTES;
-          const int k0 = ((int)krank * kblocks + kb) * TBK;
-          if (PAIR && !THREE_X)
+          const int k0 = ((int)krank * kblocks + kb) * C::KB;
+          // One operand of one stage: fp32 tiles are one box (K-major) or slabs of 32 columns
+          // (MN-major); pre-split operands are the "hi" and "mid" planes (layer coordinates 2l and
+          // 2l+1), each one box of 64 k-columns (K-major) or slabs of 64 columns (MN-major).
+          auto load_operand = [&](uint8_t* dst, const CUtensorMap* map, bool mn, int rows, int r0,
+                                  int bytes, uint64_t* bar_local, uint32_t bar_pair, bool pair) {
+            auto one = [&](uint8_t* d, int c0, int c1, int c2) {
+              if (pair)
+                tma_load_3d_pair(d, map, bar_pair, c0, c1, c2);
+              else
+                tma_load_3d(d, map, bar_local, c0, c1, c2);
+            };
+            if (C::PRE)
+            {
+              for (int pl = 0; pl < 2; ++pl)
+              {
+                uint8_t* d = dst + pl * (bytes / 2);
+                if (!mn)
+                  one(d, k0, r0, 2 * lcoord + pl);
+                else
+                  for (int i = 0; i < rows / 64; ++i)
+                    one(d + i * (C::KB * 128), r0 + 64 * i, k0, 2 * lcoord + pl);
+              }
+            }
+            else if (!mn)
+              one(dst, k0, r0, lcoord);
+            else
+              for (int i = 0; i < rows / 32; ++i)
+                one(dst + i * (TBK * 128), r0 + 32 * i, k0, lcoord);
+          };
+          if (PAIR && !C::SPLITW)
           {
-            // One pass of TF32: the MMA thread of the leader waits on ITS full[s] for the tiles
-            // of both CTAs, so both CTAs' copies count their bytes there.
+            // No in-kernel operand transform: the MMA thread of the leader waits on ITS full[s]
+            // for the tiles of both CTAs, so both CTAs' copies count their bytes there.
             if (leader)
               mbar_expect_tx(&full[s], 2 * (C::A_BYTES + C::B_BYTES));
             const uint32_t bar = lead_full + (uint32_t)(s * 8);
-            if (!C::B_MN)
-              tma_load_3d_pair(b_dst, &mapB, bar, k0, n0, lcoord);
-            else
-              for (int i = 0; i < C::BN_LOCAL / 32; ++i)
-                tma_load_3d_pair(b_dst + i * (TBK * 128), &mapB, bar, n0 + 32 * i, k0, lcoord);
-            if (!C::A_MN)
-              tma_load_3d_pair(a_dst, &mapA, bar, k0, m0, lcoord);
-            else
-              for (int i = 0; i < BM / 32; ++i)
-                tma_load_3d_pair(a_dst + i * (TBK * 128), &mapA, bar, m0 + 32 * i, k0, lcoord);
+            load_operand(b_dst, &mapB, C::B_MN, C::BN_LOCAL, n0, C::B_BYTES, nullptr, bar, true);
+            load_operand(a_dst, &mapA, C::A_MN, BM, m0, C::A_BYTES, nullptr, bar, true);
             continue;
           }
           mbar_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
-          if (!C::B_MN)
-            tma_load_3d(b_dst, &mapB, &full[s], k0, n0, lcoord);
-          else
-            for (int i = 0; i < C::BN_LOCAL / 32; ++i)
-              tma_load_3d(b_dst + i * (TBK * 128), &mapB, &full[s], n0 + 32 * i, k0, lcoord);
+          load_operand(b_dst, &mapB, C::B_MN, C::BN_LOCAL, n0, C::B_BYTES, &full[s], 0, false);
           if (P.chain && kb == 0 && t > 0)
           {
             // The rows of this layer's input are the previous layer's output: wait until every
@@ -896,11 +977,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
               alive = false; // the A copy below still runs so the stage's byte count completes
             trace_stamp(P, t, 0);
           }
-          if (!C::A_MN)
-            tma_load_3d(a_dst, &mapA, &full[s], k0, m0, lcoord);
-          else
-            for (int i = 0; i < BM / 32; ++i)
-              tma_load_3d(a_dst + i * (TBK * 128), &mapA, &full[s], m0 + 32 * i, k0, lcoord);
+          load_operand(a_dst, &mapA, C::A_MN, BM, m0, C::A_BYTES, &full[s], 0, false);
           if (!alive)
             break;
         }
@@ -926,23 +1003,26 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
       int s = 0, tile_iter = 0;
       uint32_t phase = 0; // parity to wait for on full[s] / xf[s]
       bool alive = true;
-      const uint32_t a_lbo = C::A_MN ? TBK * 128 : 16, b_lbo = C::B_MN ? TBK * 128 : 16;
       // 32-bit tiles, MN-major: 4 k-rows of 128 bytes per swizzle atom (512 B between k-groups),
       // slabs of 32 columns TBK*128 bytes apart; K-major: 8 rows per atom (1024 B between groups).
-      // BF16 tiles, MN-major: blocks of 64 columns TBK*128 bytes apart, 8 k-rows of 128 bytes per
-      // atom, 16 k-rows per instruction; K-major: 64-byte rows, 8 per atom (512 B between groups).
-      const uint32_t a_adv = C::B16 ? (C::A_MN ? 2048 : 32) : (C::A_MN ? 1024 : UMMA_K * 4);
-      const uint32_t b_adv = C::B16 ? (C::B_MN ? 2048 : 32) : (C::B_MN ? 1024 : UMMA_K * 4);
-      const uint32_t a_sbo = C::B16 ? (C::A_MN ? 1024 : 512) : (C::A_MN ? 512 : 1024);
-      const uint32_t b_sbo = C::B16 ? (C::B_MN ? 1024 : 512) : (C::B_MN ? 512 : 1024);
-      const uint32_t a_lay = C::B16 ? (C::A_MN ? 2 : 4) : (C::A_MN ? 1 : 2);
-      const uint32_t b_lay = C::B16 ? (C::B_MN ? 2 : 4) : (C::B_MN ? 1 : 2);
+      // BF16 tiles split in the kernel (32 k per stage): MN-major blocks of 64 columns TBK*128
+      // bytes apart, 8 k-rows of 128 bytes per atom, 16 k-rows per instruction; K-major 64-byte
+      // rows, 8 per atom (512 B between groups).  Pre-split BF16 tiles (64 k per stage) are what
+      // TMA's 128-byte swizzle writes: K-major 128-byte rows, 8 per atom (1024 B between groups);
+      // MN-major blocks of 64 columns KB*128 bytes apart.
+      const uint32_t a_lbo = C::A_MN ? C::KB * 128 : 16, b_lbo = C::B_MN ? C::KB * 128 : 16;
+      const uint32_t a_adv = C::BF ? (C::A_MN ? 2048 : 32) : (C::A_MN ? 1024 : UMMA_K * 4);
+      const uint32_t b_adv = C::BF ? (C::B_MN ? 2048 : 32) : (C::B_MN ? 1024 : UMMA_K * 4);
+      const uint32_t a_sbo = C::PRE ? 1024 : C::B16 ? (C::A_MN ? 1024 : 512) : (C::A_MN ? 512 : 1024);
+      const uint32_t b_sbo = C::PRE ? 1024 : C::B16 ? (C::B_MN ? 1024 : 512) : (C::B_MN ? 512 : 1024);
+      const uint32_t a_lay = C::PRE ? 2 : C::B16 ? (C::A_MN ? 2 : 4) : (C::A_MN ? 1 : 2);
+      const uint32_t b_lay = C::PRE ? 2 : C::B16 ? (C::B_MN ? 2 : 4) : (C::B_MN ? 1 : 2);
       // BF16 split: the slots of [A hi][A mid][B hi][B mid] follow the NR raw slots
       constexpr uint32_t OPB = C::B16 ? C::NR * C::RAWB : 0;
       constexpr int MS = C::B16 ? C::NB : C::STAGES; // slots the tensor core cycles through
       const uint64_t da0 = make_desc(smem_u32(stage_base) + OPB, a_lbo, a_sbo, a_lay);
       const uint64_t db0 = make_desc(smem_u32(stage_base) + OPB + C::A_BYTES, b_lbo, b_sbo, b_lay);
-      constexpr int KSTEPS = C::B16 ? TBK / 16 : TBK / UMMA_K;
+      constexpr int KSTEPS = C::BF ? C::KB / 16 : TBK / UMMA_K;
       for (int t = t_begin; t < t_end && alive; t += t_step, ++tile_iter)
       {
         const int acc = tile_iter & 1;
@@ -953,7 +1033,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         const uint32_t d_tmem0 = tmem_base + acc * (BN * C::KSPLIT);
         for (int kb = 0; kb < kblocks; ++kb)
         {
-          uint64_t* ready = THREE_X ? &xf[s] : &full[s];
+          uint64_t* ready = C::SPLITW ? &xf[s] : &full[s];
           if (!(PAIR ? mbar_wait_cluster(ready, phase, abort_flag)
                      : mbar_wait(ready, phase, abort_flag)))
           {
@@ -974,7 +1054,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
             const uint64_t db = sb + (uint64_t)(ks * (b_adv >> 4));
             const uint32_t d_tmem = d_tmem0 + (ks % C::KSPLIT) * BN;
             const uint32_t first = C::KSPLIT > 1 ? (kb != 0) : ((kb | ks) != 0);
-            if (C::B16)
+            if (C::BF)
             {
               const uint64_t dam = da + (uint64_t)((C::A_BYTES / 2) >> 4);
               const uint64_t dbm = db + (uint64_t)((C::B_BYTES / 2) >> 4);
@@ -991,7 +1071,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
                 tc_mma_bf16(d_tmem, da, db, C::IDESC, 1);
               }
             }
-            else if (THREE_X)
+            else if (THREE_X == 1)
             {
               const uint64_t dal = da + (uint64_t)((C::A_BYTES + C::B_BYTES) >> 4);
               const uint64_t dbl = db + (uint64_t)((C::A_BYTES + C::B_BYTES) >> 4);
@@ -1088,7 +1168,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
 
       if (OP == TC_FWD)
       {
-        constexpr bool PF = !THREE_X;
+        constexpr bool PF = THREE_X == 0;
         constexpr bool SI = C::STAGE_IN;
         constexpr bool KSUM = KS == 2;
         InStage in;
@@ -1141,6 +1221,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
       {
         const dpc_layer L = P.layers[li];
         const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
+        __nv_bfloat16* z_hi = P.zp ? P.zp + 2 * (long long)(li - P.run_first) * P.act_elems : nullptr;
         for (int c = grp; c < BN / 32; c += GROUPS)
         {
           const size_t o = (size_t)m * P.N + n0 + c * 32;
@@ -1186,6 +1267,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
                 zz[k + q] += L.ir * uu[q];
             }
             st8(L.z + o + k, &zz[k]);
+            if (z_hi)
+              st_planes8(z_hi, P.act_elems, o + k, &zz[k]);
           }
         }
       }
@@ -1222,6 +1305,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           }
         }
         else
+        {
+        __nv_bfloat16* w_hi = P.wp ? P.wp + 2 * (long long)(li - P.run_first) * P.w_elems : nullptr;
         for (int c = grp; c < BN / 32; c += GROUPS)
         {
           const size_t o = (size_t)m * P.N + n0 + c * 32;
@@ -1241,7 +1326,10 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
               w[k + q] = fmaf(alpha, v[k + q], w[k + q]);
             }
             st8(L.W + o + k, &w[k]);
+            if (w_hi)
+              st_planes8(w_hi, P.w_elems, o + k, &w[k]);
           }
+        }
         }
       }
       if (P.chain && warp == 2 && lane == 0)
@@ -1277,7 +1365,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         atomicAdd(P.energy, (double)(0.5f * esum));
     }
   }
-  else if (C::STAGE_IN && warp == 2 + C::EPI_WARPS + (THREE_X ? 4 : 0))
+  else if (C::STAGE_IN && warp == 2 + C::EPI_WARPS + (C::SPLITW ? 4 : 0))
   {
     // ---------------------------------------------------------------- staged-operand loader
     // Brings this CTA's 128 rows of the layer above (belief or error) into shared memory, one
@@ -1309,7 +1397,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
       }
     }
   }
-  else if (THREE_X)
+  else if (C::SPLITW)
   {
     // ---------------------------------------------------------------- remainder transform
     // lo = x - (x with the low 13 mantissa bits cleared): exactly what the tensor core drops
@@ -1452,6 +1540,44 @@ bool make_map(CUtensorMap* map, const float* base, int cols, int rows, int layer
   return r == CUDA_SUCCESS;
 }
 
+// bf16 operand planes [planes][rows][cols] (cols contiguous) with a (64 x box_rows x 1) box:
+// 128-byte rows under the 128-byte swizzle, for K-major and MN-major operands alike.
+bool make_map_bf16(CUtensorMap* map, const __nv_bfloat16* base, int cols, int rows, int planes,
+                   int64_t plane_elems, int box_rows)
+{
+  EncodeTiledFn fn = encode_fn();
+  if (!fn)
+    return false;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)planes};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)plane_elems * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Re-splits the operand planes of `kind` for layers [first, first + gridDim.y) from the fp32
+// tensors (after something other than a kernel of this file wrote them).
+__global__ void split_planes_kernel(const dpc_layer* __restrict__ layers, int first, int run_first,
+                                    int kind, __nv_bfloat16* base, long long elems)
+{
+  const dpc_layer& L = layers[first + blockIdx.y];
+  const float* src = kind == PL_Z ? L.z : (kind == PL_FE ? L.fe : L.W);
+  __nv_bfloat16* hi = base + 2 * (long long)(first + (int)blockIdx.y - run_first) * elems;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < elems;
+       i += (long long)gridDim.x * blockDim.x * 8)
+  {
+    const float4 a = *reinterpret_cast<const float4*>(src + i);
+    const float4 b = *reinterpret_cast<const float4*>(src + i + 4);
+    uint4 h, m;
+    split8(a, b, h, m);
+    *reinterpret_cast<uint4*>(hi + i) = h;
+    *reinterpret_cast<uint4*>(hi + elems + i) = m;
+  }
+}
+
 template <int OP, int BN, int THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
 int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P,
            const CUtensorMap* up = nullptr)
@@ -1509,6 +1635,54 @@ bool range_in_run(const dpc_plan* p, int first, int count)
          first + count <= p->run.first + p->run.count;
 }
 } // namespace
+
+static bool pair_ok(int rows, int cols);
+static int split_scheme(const dpc_plan* p);
+
+// Operand planes for the run (see TcState): allocated when the plan will use the 3xBF16 scheme on
+// CTA-pair tiles.  DPC_DISABLE_PLANES keeps the in-kernel split (used to compare the two).
+static bool planes_init(dpc_plan* plan, TcState* st, int first, int count, int H)
+{
+  const int B = plan->batch;
+  if (getenv("DPC_DISABLE_PLANES") || split_scheme(plan) != 2 || !pair_ok(B, H))
+    return true;
+  const size_t act = (size_t)B * H, w = (size_t)H * H;
+  if (cudaMalloc(&st->zp, 2 * (size_t)(count + 1) * act * sizeof(__nv_bfloat16)) != cudaSuccess ||
+      cudaMalloc(&st->fep, 2 * (size_t)count * act * sizeof(__nv_bfloat16)) != cudaSuccess ||
+      cudaMalloc(&st->wp, 2 * (size_t)count * w * sizeof(__nv_bfloat16)) != cudaSuccess)
+  {
+    cudaGetLastError();
+    return false;
+  }
+  bool ok = true;
+  ok &= make_map_bf16(&st->zp_km, st->zp, H, B, 2 * (count + 1), (int64_t)act, TBM);
+  ok &= make_map_bf16(&st->zp_mn, st->zp, H, B, 2 * (count + 1), (int64_t)act, 64);
+  ok &= make_map_bf16(&st->fep_km, st->fep, H, B, 2 * count, (int64_t)act, TBM);
+  ok &= make_map_bf16(&st->fep_mn, st->fep, H, B, 2 * count, (int64_t)act, 64);
+  ok &= make_map_bf16(&st->wp_km128, st->wp, H, H, 2 * count, (int64_t)w, 128);
+  ok &= make_map_bf16(&st->wp_km64, st->wp, H, H, 2 * count, (int64_t)w, 64);
+  ok &= make_map_bf16(&st->wp_mn, st->wp, H, H, 2 * count, (int64_t)w, 64);
+  if (!ok)
+    return false;
+  st->dirty[PL_Z].assign(count + 1, 1);
+  st->dirty[PL_FE].assign(count, 1);
+  st->dirty[PL_W].assign(count, 1);
+  st->planes = true;
+  (void)first;
+  return true;
+}
+
+static void planes_free(TcState* st)
+{
+  if (st->zp)
+    cudaFree(st->zp);
+  if (st->fep)
+    cudaFree(st->fep);
+  if (st->wp)
+    cudaFree(st->wp);
+  st->zp = st->fep = st->wp = nullptr;
+  st->planes = false;
+}
 
 int tc_plan_init(dpc_plan* plan)
 {
@@ -1615,6 +1789,13 @@ int tc_plan_init(dpc_plan* plan)
   plan->run.first = best_first;
   plan->run.count = best_count;
   plan->run.width = H;
+  if (!planes_init(plan, st, best_first, best_count, H))
+  {
+    // no memory (or no tensor map) for the planes: the kernels split the operands themselves
+    planes_free(st);
+    fprintf(stderr, "deepity_b200: operand planes unavailable for this plan, using the in-kernel "
+                    "operand split\n");
+  }
   return DPC_OK;
 }
 
@@ -1629,6 +1810,7 @@ void tc_plan_free(dpc_plan* plan)
     cudaFree(st->chain_counters);
   if (st->error_host)
     cudaFreeHost(st->error_host);
+  planes_free(st);
   delete st;
   plan->tc = nullptr;
   plan->run = TensorRun();
@@ -1695,10 +1877,78 @@ static int split_scheme(const dpc_plan* p)
   return all_sgd(p) ? 2 : 1;
 }
 
+// ---- operand planes: which layers lag behind their fp32 tensors -----------------------------
+// Indices are relative to the run; beliefs have one entry more (the layer above the run).
+static void planes_mark(TcState* st, int kind, int r0, int r1, uint8_t v)
+{
+  if (!st->planes)
+    return;
+  auto& d = st->dirty[kind];
+  r0 = std::max(r0, 0);
+  r1 = std::min(r1, (int)d.size());
+  for (int i = r0; i < r1; ++i)
+    d[i] = v;
+}
+
+// Brings the planes of layers [r0, r1) up to date (one split launch per maximal stale sub-range).
+static int planes_need(dpc_plan* p, TcState* st, int kind, int r0, int r1)
+{
+  if (!st->planes)
+    return DPC_OK;
+  auto& d = st->dirty[kind];
+  r0 = std::max(r0, 0);
+  r1 = std::min(r1, (int)d.size());
+  const long long H = p->run.width;
+  const long long elems = kind == PL_W ? H * H : (long long)p->batch * H;
+  __nv_bfloat16* base = kind == PL_Z ? st->zp : (kind == PL_FE ? st->fep : st->wp);
+  int i = r0;
+  while (i < r1)
+  {
+    if (!d[i])
+    {
+      ++i;
+      continue;
+    }
+    int j = i;
+    while (j < r1 && d[j] && j - i < 32768)
+      ++j;
+    dim3 grid((unsigned)std::min<long long>((elems / 8 + 255) / 256, 1024), (unsigned)(j - i));
+    split_planes_kernel<<<grid, 256, 0, p->ctx->stream>>>(p->d, p->run.first + i, p->run.first,
+                                                          kind, base, elems);
+    p->ctx->launches += 1;
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess)
+      return cuda_fail(cudaGetLastError(), "split_planes kernel launch");
+    for (int k = i; k < j; ++k)
+      d[k] = 0;
+    i = j;
+  }
+  return DPC_OK;
+}
+
+// Pre-split operands are read when the plan runs the 3xBF16 scheme in an fp32-accurate mode.
+static bool planes_on(const dpc_plan* p, const TcState* st)
+{
+  return st->planes && p->ctx->precision != DPC_PRECISION_TF32 && split_scheme(p) == 2;
+}
+// ... and every kernel of this file then writes the planes of what it produces (in the pure
+// TF32 mode nobody reads them: they are left to go stale and marked so).
+static bool planes_kept(const dpc_plan* p, const TcState* st)
+{
+  return planes_on(p, st);
+}
+
 static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int M, int N, int K,
                             int BN, int flags, int mode, int BM = TBM)
 {
   TcParams P;
+  const bool keep = planes_kept(p, st);
+  P.zp = keep ? st->zp : nullptr;
+  P.fep = keep ? st->fep : nullptr;
+  P.wp = keep ? st->wp : nullptr;
+  P.act_elems = (long long)p->batch * p->run.width;
+  P.w_elems = (long long)p->run.width * p->run.width;
+  P.wait_cycles = st->wait_cycles;
   P.layers = p->d;
   P.first = first;
   P.count = count;
@@ -1731,6 +1981,8 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
       (flags & DPC_FWD_FE) && !(flags & DPC_FWD_ERR_NEXT) && (flags & DPC_FWD_TRANSIENT);
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || (refresh && fast_grad(p));
   const int scheme = split_scheme(p);
+  const int r0 = first - p->run.first;
+  int rc;
   if (pair_ok(B, H))
   {
     TcParams P = base_params(p, st, first, count, B, H, H, 256, flags, 0, 256);
@@ -1747,16 +1999,37 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
       else if ((flags & DPC_FWD_FE) && !(flags & DPC_FWD_ERR_NEXT))
         P.stage_in = 2, up = &st->eup_km;
     }
-    return tf32 ? launch<TC_FWD, 256, 0, 128, true>(p, st, st->z_km, st->w_km128, P, up)
+    if (!tf32 && planes_on(p, st))
+    {
+      if ((rc = planes_need(p, st, PL_Z, r0, r0 + count)) != DPC_OK ||
+          (rc = planes_need(p, st, PL_W, r0, r0 + count)) != DPC_OK)
+        return rc;
+      rc = launch<TC_FWD, 256, 3, 128, true>(p, st, st->zp_km, st->wp_km128, P, up);
+    }
+    else
+      rc = tf32 ? launch<TC_FWD, 256, 0, 128, true>(p, st, st->z_km, st->w_km128, P, up)
          : scheme == 2 ? launch<TC_FWD, 256, 2, 128, true>(p, st, st->z_km, st->w_km128, P, up)
                        : launch<TC_FWD, 256, 1, 128, true>(p, st, st->z_km, st->w_km128, P, up);
   }
-  if (tf32)
-    return launch<TC_FWD, 256, 0>(p, st, st->z_km, st->w_km256,
-                                      base_params(p, st, first, count, B, H, H, 256, flags, 0));
-  TcParams P = base_params(p, st, first, count, B, H, H, 128, flags, 0);
-  return scheme == 2 ? launch<TC_FWD, 128, 2>(p, st, st->z_km, st->w_km128, P)
+  else if (tf32)
+    rc = launch<TC_FWD, 256, 0>(p, st, st->z_km, st->w_km256,
+                                base_params(p, st, first, count, B, H, H, 256, flags, 0));
+  else
+  {
+    TcParams P = base_params(p, st, first, count, B, H, H, 128, flags, 0);
+    rc = scheme == 2 ? launch<TC_FWD, 128, 2>(p, st, st->z_km, st->w_km128, P)
                      : launch<TC_FWD, 128, 1>(p, st, st->z_km, st->w_km128, P);
+  }
+  if (rc == DPC_OK)
+  {
+    // every variant's epilogue keeps the planes of what it writes (when the plan has planes)
+    const uint8_t stale = planes_kept(p, st) ? 0 : 1;
+    if (flags & DPC_FWD_FE)
+      planes_mark(st, PL_FE, r0, r0 + count, stale);
+    if (flags & DPC_FWD_COPY_NEXT)
+      planes_mark(st, PL_Z, r0 + 1, r0 + count + 1, stale);
+  }
+  return rc;
 }
 
 // The sequential forward sweep over layers [first, first+count) of the run as ONE persistent
@@ -1777,11 +2050,17 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   const int BNC = ((B / TBM) * (H / 32) <= p->ctx->sm_count) ? 32 : 64;
   const int tiles = (B / TBM) * (H / BNC);
   if (tiles > p->ctx->sm_count)
+  {
+    if (!st->warned_fallback)
+      fprintf(stderr, "deepity_b200: the forward sweep of this plan needs %d resident CTAs (> %d "
+                      "SMs): falling back to one launch per layer\n", tiles, p->ctx->sm_count);
+    st->warned_fallback = true;
     return 1;
+  }
   TcParams P = base_params(p, st, first, count, B, H, H, BNC, flags, 0);
   P.chain = 1;
   P.chain_counters = st->chain_counters;
-  P.chain_target = (H / BNC) * 8; // column tiles x epilogue warps
+  P.chain_target = (H / BNC) * 8 + st->chain_target_bias; // column tiles x epilogue warps
   P.trace = st->trace;
   cudaError_t e = cudaMemsetAsync(st->chain_counters, 0, sizeof(int) * (size_t)count * (B / TBM),
                                   p->ctx->stream);
@@ -1789,32 +2068,46 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
     return cuda_fail(e, "cudaMemsetAsync(chain counters)");
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
   const int scheme = split_scheme(p);
+  const int r0 = first - p->run.first;
+  int rc;
   // K-split variant: 128 x 64 tiles, two CTAs (one cluster) per tile with half of K each.
   // Summing K in two halves rounds differently from the settling passes' single accumulation,
   // so right after the sweep e = z - mu is ~1e-7 where it is exactly 0 with matching orders
   // (as in the reference, which uses one GEMM routine for both).  Harmless for SGD; Adam-type
   // updates normalise such noise up to a full step, so they keep the single-accumulation sweep.
-  bool sgd_only = true;
-  for (int i = 0; i < p->n; ++i)
-    sgd_only &= p->h[i].next_size <= 0 || p->h[i].opt == DPC_OPT_SGD;
   const int ks_tiles = (B / TBM) * (H / 64);
-  if (sgd_only && 2 * ks_tiles <= p->ctx->sm_count && (H / TBK) % 2 == 0 &&
+  if (all_sgd(p) && 2 * ks_tiles <= p->ctx->sm_count && (H / 64) % 2 == 0 &&
       !getenv("DPC_DISABLE_KSPLIT"))
   {
     TcParams Q = base_params(p, st, first, count, B, H, H, 64, flags, 0);
     Q.chain = 1, Q.chain_counters = st->chain_counters, Q.trace = st->trace;
-    Q.chain_target = (H / 64) * 2 * 8; // column tiles x CTAs per tile x epilogue warps
-    return tf32 ? launch<TC_FWD, 64, 0, 128, false, 2>(p, st, st->z_km, st->w_km64, Q)
+    // column tiles x CTAs per tile x epilogue warps
+    Q.chain_target = (H / 64) * 2 * 8 + st->chain_target_bias;
+    if (!tf32 && planes_on(p, st))
+    {
+      // the first layer's input and every layer's weights must be split; the sweep itself
+      // writes the planes of every belief it produces
+      if ((rc = planes_need(p, st, PL_Z, r0, r0 + 1)) != DPC_OK ||
+          (rc = planes_need(p, st, PL_W, r0, r0 + count)) != DPC_OK)
+        return rc;
+      rc = launch<TC_FWD, 64, 3, 128, false, 2>(p, st, st->zp_km, st->wp_km64, Q);
+    }
+    else
+      rc = tf32 ? launch<TC_FWD, 64, 0, 128, false, 2>(p, st, st->z_km, st->w_km64, Q)
          : scheme == 2 ? launch<TC_FWD, 64, 2, 128, false, 2>(p, st, st->z_km, st->w_km64, Q)
                        : launch<TC_FWD, 64, 1, 128, false, 2>(p, st, st->z_km, st->w_km64, Q);
   }
-  if (BNC == 32)
-    return tf32 ? launch<TC_FWD, 32, 0>(p, st, st->z_km, st->w_km32, P)
-         : scheme == 2 ? launch<TC_FWD, 32, 2>(p, st, st->z_km, st->w_km32, P)
-                       : launch<TC_FWD, 32, 1>(p, st, st->z_km, st->w_km32, P);
-  return tf32 ? launch<TC_FWD, 64, 0>(p, st, st->z_km, st->w_km64, P)
-         : scheme == 2 ? launch<TC_FWD, 64, 2>(p, st, st->z_km, st->w_km64, P)
-                       : launch<TC_FWD, 64, 1>(p, st, st->z_km, st->w_km64, P);
+  else if (BNC == 32)
+    rc = tf32 ? launch<TC_FWD, 32, 0>(p, st, st->z_km, st->w_km32, P)
+       : scheme == 2 ? launch<TC_FWD, 32, 2>(p, st, st->z_km, st->w_km32, P)
+                     : launch<TC_FWD, 32, 1>(p, st, st->z_km, st->w_km32, P);
+  else
+    rc = tf32 ? launch<TC_FWD, 64, 0>(p, st, st->z_km, st->w_km64, P)
+       : scheme == 2 ? launch<TC_FWD, 64, 2>(p, st, st->z_km, st->w_km64, P)
+                     : launch<TC_FWD, 64, 1>(p, st, st->z_km, st->w_km64, P);
+  if (rc == DPC_OK && (flags & DPC_FWD_COPY_NEXT))
+    planes_mark(st, PL_Z, r0 + 1, r0 + count + 1, planes_kept(p, st) ? 0 : 1);
+  return rc;
 }
 
 int tc_update_state(dpc_plan* p, int first, int count)
@@ -1825,19 +2118,35 @@ int tc_update_state(dpc_plan* p, int first, int count)
   const int H = p->run.width, B = p->batch;
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
   const int scheme = split_scheme(p);
+  const int r0 = first - p->run.first;
+  int rc;
   if (pair_ok(B, H))
   {
     TcParams P = base_params(p, st, first, count, B, H, H, 256, 0, 0, 256);
-    return tf32 ? launch<TC_FB, 256, 0, 128, true>(p, st, st->fe_km, st->w_mn, P)
+    if (!tf32 && planes_on(p, st))
+    {
+      if ((rc = planes_need(p, st, PL_FE, r0, r0 + count)) != DPC_OK ||
+          (rc = planes_need(p, st, PL_W, r0, r0 + count)) != DPC_OK)
+        return rc;
+      rc = launch<TC_FB, 256, 3, 128, true>(p, st, st->fep_km, st->wp_mn, P);
+    }
+    else
+      rc = tf32 ? launch<TC_FB, 256, 0, 128, true>(p, st, st->fe_km, st->w_mn, P)
          : scheme == 2 ? launch<TC_FB, 256, 2, 128, true>(p, st, st->fe_km, st->w_mn, P)
                        : launch<TC_FB, 256, 1, 128, true>(p, st, st->fe_km, st->w_mn, P);
   }
-  if (tf32)
-    return launch<TC_FB, 256, 0>(p, st, st->fe_km, st->w_mn,
-                                     base_params(p, st, first, count, B, H, H, 256, 0, 0));
-  TcParams P = base_params(p, st, first, count, B, H, H, 128, 0, 0);
-  return scheme == 2 ? launch<TC_FB, 128, 2>(p, st, st->fe_km, st->w_mn, P)
+  else if (tf32)
+    rc = launch<TC_FB, 256, 0>(p, st, st->fe_km, st->w_mn,
+                               base_params(p, st, first, count, B, H, H, 256, 0, 0));
+  else
+  {
+    TcParams P = base_params(p, st, first, count, B, H, H, 128, 0, 0);
+    rc = scheme == 2 ? launch<TC_FB, 128, 2>(p, st, st->fe_km, st->w_mn, P)
                      : launch<TC_FB, 128, 1>(p, st, st->fe_km, st->w_mn, P);
+  }
+  if (rc == DPC_OK)
+    planes_mark(st, PL_Z, r0, r0 + count, planes_kept(p, st) ? 0 : 1);
+  return rc;
 }
 
 int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
@@ -1858,19 +2167,89 @@ int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
   const int H = p->run.width, B = p->batch;
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || fast_grad(p);
   const int scheme = split_scheme(p);
+  const int r0 = first - p->run.first;
+  int rc;
   if (pair_ok(H, H))
   {
     TcParams P = base_params(p, st, first, count, H, H, B, 256, decay_w ? 1 : 0, mode, 256);
-    return tf32 ? launch<TC_WG, 256, 0, 128, true>(p, st, st->fe_mn, st->z_mn, P)
+    if (!tf32 && planes_on(p, st))
+    {
+      if ((rc = planes_need(p, st, PL_FE, r0, r0 + count)) != DPC_OK ||
+          (rc = planes_need(p, st, PL_Z, r0, r0 + count)) != DPC_OK)
+        return rc;
+      rc = launch<TC_WG, 256, 3, 128, true>(p, st, st->fep_mn, st->zp_mn, P);
+    }
+    else
+      rc = tf32 ? launch<TC_WG, 256, 0, 128, true>(p, st, st->fe_mn, st->z_mn, P)
          : scheme == 2 ? launch<TC_WG, 256, 2, 128, true>(p, st, st->fe_mn, st->z_mn, P)
                        : launch<TC_WG, 256, 1, 128, true>(p, st, st->fe_mn, st->z_mn, P);
   }
-  if (tf32)
-    return launch<TC_WG, 256, 0>(
+  else if (tf32)
+    rc = launch<TC_WG, 256, 0>(
         p, st, st->fe_mn, st->z_mn,
         base_params(p, st, first, count, H, H, B, 256, decay_w ? 1 : 0, mode));
-  TcParams P = base_params(p, st, first, count, H, H, B, 128, decay_w ? 1 : 0, mode);
-  return scheme == 2 ? launch<TC_WG, 128, 2>(p, st, st->fe_mn, st->z_mn, P)
+  else
+  {
+    TcParams P = base_params(p, st, first, count, H, H, B, 128, decay_w ? 1 : 0, mode);
+    rc = scheme == 2 ? launch<TC_WG, 128, 2>(p, st, st->fe_mn, st->z_mn, P)
                      : launch<TC_WG, 128, 1>(p, st, st->fe_mn, st->z_mn, P);
+  }
+  if (rc == DPC_OK && !(mode & WG_GRAD_MODE))
+    planes_mark(st, PL_W, r0, r0 + count, planes_kept(p, st) ? 0 : 1);
+  return rc;
+}
+
+// ---- operand planes: what the rest of the library tells this file ---------------------------
+// kind: 0 beliefs, 1 feedback errors, 2 weights.  Something outside this file wrote the fp32
+// tensors of layers [first, first+count): their planes must be re-split before the next use.
+void tc_touch(dpc_plan* p, int kind, int first, int count)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (!st || !st->planes || kind < 0 || kind > 2)
+    return;
+  planes_mark(st, kind, first - p->run.first, first + count - p->run.first, 1);
+}
+
+int tc_sync_planes(dpc_plan* p)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (!st || !st->planes || !planes_on(p, st))
+    return DPC_OK;
+  for (int kind = 0; kind < 3; ++kind)
+  {
+    int rc = planes_need(p, st, kind, 0, (int)st->dirty[kind].size());
+    if (rc != DPC_OK)
+      return rc;
+  }
+  return DPC_OK;
+}
+
+void tc_set_wait_limit(dpc_plan* p, long long cycles, int chain_target_bias)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (!st)
+    return;
+  st->wait_cycles = cycles > 0 ? cycles : kWaitCyclesDefault;
+  st->chain_target_bias = chain_target_bias;
+}
+
+// One line on which kernels the plan's weight layers run.
+std::string tc_describe(dpc_plan* p)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  const int weight_layers = p->n - 1;
+  if (!st || !st->ok || p->run.count <= 0)
+    return "all " + std::to_string(weight_layers) + " weight layers on CUDA cores";
+  const bool pair = pair_ok(p->batch, p->run.width);
+  std::string mode = p->ctx->precision == DPC_PRECISION_TF32 ? "1xTF32"
+                     : split_scheme(p) == 2 ? (planes_on(p, st) ? "3xBF16 from pre-split planes"
+                                                               : "3xBF16 split in the kernel")
+                                            : "3xTF32";
+  if (p->ctx->precision == DPC_PRECISION_MIXED)
+    mode += " (gradient path 1xTF32)";
+  return "layers " + std::to_string(p->run.first) + ".." +
+         std::to_string(p->run.first + p->run.count - 1) + " on tcgen05 (" +
+         (pair ? "CTA pairs 256x256" : "single-CTA tiles") + ", " + mode + "); " +
+         std::to_string(weight_layers - p->run.count) + " weight layers on CUDA cores";
 }
 } // namespace dpc

@@ -433,18 +433,26 @@ void PCNetwork::RandomizeWeights(std::mt19937& rng, const char* distribution)
       Check(dpc_copy_h2d_sync(ctx, l->d.Psi, psi.data(), psi.size() * sizeof(float)));
     }
   }
+  Check(dpc_plan_invalidate(plan, 0, (int)layers.size(), DPC_WROTE_W));
 }
 
 // ------------------------------------------------------------------------------- state
-void PCNetwork::ResetState()
+void PCNetwork::ResetState(bool beliefsOverwritten)
 {
   RequireCompiled();
   const size_t B = (size_t)batchSize;
   // z of every layer lives in one arena: one memset covers them all (the reference's
-  // batched run does the same for its flat buffer, DirectKPPCNetwork.cpp:38-55).
-  float* z0 = layers.front()->d.z;
-  float* zend = layers.back()->d.z + Pad64(B * layers.back()->d.size);
-  Check(dpc_zero(ctx, z0, (size_t)(zend - z0) * sizeof(float)));
+  // batched run does the same for its flat buffer, DirectKPPCNetwork.cpp:38-55).  A train step
+  // or prediction that opens with the full forward sweep overwrites every belief (the clamped
+  // ends by the clamp copies, the rest by the sweep) before anything reads one, so there the
+  // memset would only cost 4 bytes of HBM traffic per belief: it is skipped.
+  if (!beliefsOverwritten)
+  {
+    float* z0 = layers.front()->d.z;
+    float* zend = layers.back()->d.z + Pad64(B * layers.back()->d.size);
+    Check(dpc_zero(ctx, z0, (size_t)(zend - z0) * sizeof(float)));
+    Check(dpc_plan_invalidate(plan, 0, (int)layers.size(), DPC_WROTE_Z));
+  }
   if (kind == NetworkKind::FULL) // FullPCLayer::ResetState, src/layers/FullPCLayer.cpp:664-671
   {
     float* e0 = layers.front()->d.e;
@@ -481,6 +489,7 @@ void PCNetwork::ClampHost(int layer, const float* data, size_t n)
     std::memcpy(stage, data, count * sizeof(float));
     Check(dpc_copy_h2d(ctx, l->d.z, stage, count * sizeof(float)));
   }
+  Check(dpc_plan_invalidate(plan, layer, 1, DPC_WROTE_Z));
   l->clamped = true;
   l->cacheValid = false;
 }
@@ -491,6 +500,7 @@ void PCNetwork::ClampDevice(int layer, const float* data, size_t n)
   PCLayer* l = layers.at(layer).get();
   const size_t count = std::min(n, (size_t)batchSize * l->d.size);
   Check(dpc_copy_d2d(ctx, l->d.z, data, count * sizeof(float)));
+  Check(dpc_plan_invalidate(plan, layer, 1, DPC_WROTE_Z));
   l->clamped = true;
   l->cacheValid = false;
 }
@@ -837,7 +847,12 @@ float PCNetwork::TrainStepRaw(int mode, const float* x, size_t nx, const float* 
   SyncPlan();
   const int n = (int)layers.size();
   predictionsStale = false; // everything is recomputed from here on
-  ResetState();
+  // DirectKP / Full steps open with the forward sweep over the whole stack; x and y must then
+  // cover their layers completely (a short buffer leaves the rest at zero, as the memset would)
+  const bool sweepOverwrites = kind != NetworkKind::SIMPLE &&
+                               nx >= (size_t)batchSize * layers.front()->d.size &&
+                               ny >= (size_t)batchSize * layers.back()->d.size;
+  ResetState(sweepOverwrites);
   if (onDevice)
   {
     ClampDevice(0, x, nx);
@@ -850,6 +865,9 @@ float PCNetwork::TrainStepRaw(int mode, const float* x, size_t nx, const float* 
   }
   for (int i = 1; i + 1 < n; ++i)
     layers[i]->clamped = false;
+  // A recorded step holds no host logic: whatever operand copies are stale now are rebuilt
+  // before the graph runs, so that recording and every replay start from the same state.
+  Check(dpc_plan_sync_operands(plan));
 
   if (useGraph && !gradSync)
   {
@@ -934,10 +952,12 @@ void PCNetwork::PredictRaw(const float* x, size_t nx, int steps, bool withProjec
   if (kind != NetworkKind::SIMPLE)
     withProjection = true;
   predictionsStale = false;
-  ResetState();
+  ResetState(withProjection && kind != NetworkKind::SIMPLE &&
+             nx >= (size_t)batchSize * layers.front()->d.size);
   ClampHost(0, x, nx);
   for (int i = 1; i < n; ++i)
     layers[i]->clamped = false;
+  Check(dpc_plan_sync_operands(plan));
   if (useGraph)
   {
     const long key = (long)steps * 2 + (withProjection ? 1 : 0);
@@ -1394,6 +1414,9 @@ int dpcn_set_tensor(dpcn_net* net, int layer, const char* name, const float* hos
     return DPC_ERR_INVALID;
   }
   dpc_ctx* ctx = net->net->Context();
+  const std::string nm(name);
+  if (nm == "z" || nm == "W")
+    dpc_plan_invalidate(net->net->Plan(), layer, 1, nm == "z" ? DPC_WROTE_Z : DPC_WROTE_W);
   if (st == c)
     return dpc_copy_h2d_sync(ctx, p, host_in, r * c * sizeof(float));
   std::vector<float> tmp(r * st, 0.0f);

@@ -104,7 +104,7 @@ public:
   void Compile();
   void RandomizeWeights(std::mt19937& rng, const char* distribution = "normal");
 
-  void ResetState();
+  void ResetState(bool beliefsOverwritten = false);
   void Clamp(const std::vector<float>& input);
   void ClampHost(int layer, const float* data, size_t n);
   void ClampDevice(int layer, const float* data, size_t n);

@@ -163,6 +163,18 @@ class GpuEngine:
     def mark_clamped(self, layer: int):
         """The kernels take clamping from the ranges the schedule passes; nothing to record."""
 
+    def wrote_belief(self, layer: int):
+        """The schedule wrote z of `layer` itself (a copy or an NCCL receive into the library's
+        memory): the tensor-core kernels' operand copies of it must be rebuilt."""
+        self.check(self.lib.dpc_plan_invalidate(self.plan, layer, 1, 1))  # DPC_WROTE_Z
+
+    def close(self):
+        """Free the block's device memory (the network, its plan and context)."""
+        if self.h:
+            self._views.clear()
+            self.lib.dpcn_destroy(self.h)
+            self.h = None
+
     def comm_stream(self):
         return self.torch.cuda.stream(self.stream)
 
@@ -244,6 +256,7 @@ class ShardedDKPPCN:
         # forward sweep, rank after rank
         if not self.is_first:
             self._exchange(recv=(eng.tensor(0, "z"), down))
+            eng.wrote_belief(0)
         eng.project_forward(skip_last_copy=self.is_last)
         if not self.is_last:
             self._exchange(send=(eng.tensor(n - 1, "z"), up))
@@ -292,9 +305,15 @@ class ShardedDKPPCN:
             np.ascontiguousarray(value, dtype=np.float32))
         with self.eng.comm_stream():
             t.copy_(src.reshape(-1).to(t.device, non_blocking=True))
+        if name == "z":
+            self.eng.wrote_belief(layer)
+
+    def close(self):
+        if hasattr(self.eng, "close"):
+            self.eng.close()
 
     def train_step_flops(self, steps: int) -> float:
-        from bench import algorithmic_flops  # the same formula the benchmark reports
+        from .flops import algorithmic_flops
         return algorithmic_flops("dkp", self.sizes, self.batch, steps)
 
 
@@ -355,155 +374,3 @@ class BatchSharded:
         """x_local, y_local: this rank's rows, already on its GPU."""
         return self._energy(self.net.train_step_device(x_local, y_local, inference_steps,
                                                        read_energy))
-
-
-# ------------------------------------------------------------------------------------------
-def bench_main(args, w, sizes, config):
-    """The N>1 arm of bench.py: layer-sharded C3, strong scaling (the same network and batch
-    at every N), timed on the device with CUDA events, max over ranks."""
-    import json
-    import time
-
-    import torch
-    import torch.distributed as dist
-
-    from bench import HYPER, ClockSampler, synth
-
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    net = ShardedDKPPCN(sizes, w["batch"], HYPER, act=w["act"], precision=args.precision)
-    x, y, params = synth(w, sizes)
-    for l, p in enumerate(params):
-        for nm, v in p.items():
-            net.set_param(l, nm, v)
-    xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
-    xh, yh = torch.from_numpy(x).pin_memory(), torch.from_numpy(y).pin_memory()
-    T, B = w["T"], w["batch"]
-    for _ in range(args.warmup):
-        energy = net.train_step(xd, yd, T)
-
-    def timed(fn, steps):
-        dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(net.eng.stream)
-        for _ in range(steps):
-            fn()
-        b.record(net.eng.stream)
-        b.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        ms = torch.tensor([a.elapsed_time(b) / steps], device="cuda", dtype=torch.float64)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    with ClockSampler(local) as clk:
-        n0 = net.eng.launch_count
-        ms = timed(lambda: net.train_step(xd, yd, T, read_energy=False), args.steps)
-        launches = net.eng.launch_count - n0
-        energy = net.train_step(xd, yd, T)
-        e2e_ms = timed(lambda: net.train_step(xh, yh, T), args.steps)
-    lc = torch.tensor([launches], device="cuda", dtype=torch.int64)
-    dist.all_reduce(lc)
-    if rank == 0:
-        flops = net.train_step_flops(T)
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(os.path.dirname(os.path.dirname(
-                os.path.abspath(__file__))), "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        peak = (peaks.get("bf16_tflops_sustained") or 1590.0) * world
-        config = dict(config, parallelism=f"layer-sharded x{world}",
-                      layers_per_rank=[e - b for b, e in net.ranges])
-        line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
-                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
-                "config": config, "energy": energy, "algorithmic_flops_per_step": flops,
-                "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
-                "frac_of_gemm_peak_step": flops / (ms * 1e-3) / 1e12 / peak,
-                "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8},
-                "gpu_launches": int(lc.item()), "clocks": clk.summary(),
-                "roofline": None, "cpu_baseline": None}
-        print(json.dumps(line))
-    dist.barrier()
-    dist.destroy_process_group()
-
-
-def batch_bench_main(args, w, sizes, config):
-    """The N>1 arm of bench.py for the wide, shallow workloads: batch-sharded, strong scaling
-    (the same network and GLOBAL batch at every N), CUDA events on the library's stream, max
-    over ranks."""
-    import json
-
-    import torch
-    import torch.distributed as dist
-
-    from bench import ClockSampler, build_net, synth
-
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    x, y, params = synth(w, sizes)
-    T, B = w["T"], w["batch"]
-
-    def build(local_batch):
-        net = build_net(dict(w, batch=local_batch), sizes, args.precision)
-        for l, p in enumerate(params):
-            for nm, v in p.items():
-                net.set_tensor(l, nm, v)
-        return net
-    net = BatchSharded(build, B)
-    lib = net.net._lib
-    stream = torch.cuda.ExternalStream(lib.dpc_stream(lib.dpcn_context(net.net._h)))
-    xd = torch.from_numpy(np.ascontiguousarray(net.rows(x))).cuda()
-    yd = torch.from_numpy(np.ascontiguousarray(net.rows(y))).cuda()
-    for _ in range(args.warmup):
-        energy = net.train_step_device(xd, yd, T)
-
-    def timed(fn, steps):
-        dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream)
-        for _ in range(steps):
-            fn()
-        b.record(stream)
-        b.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        ms = torch.tensor([a.elapsed_time(b) / steps], device="cuda", dtype=torch.float64)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    with ClockSampler(local) as clk:
-        n0 = net.net.launch_count
-        ms = timed(lambda: net.train_step_device(xd, yd, T, read_energy=False), args.steps)
-        launches = net.net.launch_count - n0
-        energy = net.train_step_device(xd, yd, T)
-        e2e_ms = timed(lambda: net.train_step(x, y, T), args.steps)
-    lc = torch.tensor([launches], device="cuda", dtype=torch.int64)
-    dist.all_reduce(lc)
-    if rank == 0:
-        from bench import algorithmic_flops
-        flops = algorithmic_flops(w["kind"], sizes, B, T)
-        config = dict(config, parallelism=f"batch-sharded x{world}", rows_per_rank=B // world)
-        line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
-                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
-                "config": config, "energy": energy, "algorithmic_flops_per_step": flops,
-                "achieved_tflops_step": flops / (ms * 1e-3) / 1e12,
-                "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": int((x.nbytes + y.nbytes) // world),
-                        "d2h_bytes_per_step": 8},
-                "gpu_launches": int(lc.item()), "clocks": clk.summary(),
-                "roofline": None, "cpu_baseline": None}
-        print(json.dumps(line))
-    dist.barrier()
-    dist.destroy_process_group()

@@ -189,6 +189,35 @@ DPC_API int dpc_plan_set_terminal_error(dpc_plan* plan, const float* e_terminal_
 DPC_API int dpc_plan_set_chain_trace(dpc_plan* plan, void* trace_dev);
 /* Layers [first, first+count) that the tensor-core path covers (0 if none). */
 DPC_API int dpc_plan_tensor_run(dpc_plan* plan, int* first, int* count);
+/* One line of text on which kernels the plan's weight layers run (tcgen05 tile shape and
+ * arithmetic scheme of the run, how many layers stay on the CUDA-core kernels), the
+ * counterpart of asking the reference which GEMM path a shape took
+ * (src/backend/cuda/CUDABackendGemm.cu:435-445).  Truncated to buf_bytes. */
+DPC_API int dpc_plan_describe(dpc_plan* plan, char* buf, int buf_bytes);
+/* The tensor-core kernels of an SGD network in FP32 mode read bf16 "hi"/"mid" operand copies of
+ * z, fe and W of the run's layers, which every kernel of this library keeps up to date.  A
+ * caller that writes one of these tensors ITSELF through a device pointer (dpcn_tensor_ptr, a
+ * memcpy, an NCCL receive into z of a boundary layer) must say so before the next phase call;
+ * the copies of those layers are then rebuilt on next use.  what: bit set of DPC_WROTE_*.
+ * dpc_plan_sync_operands rebuilds everything stale now (stream-ordered); the network classes
+ * call it before a step is recorded into, or replayed from, a CUDA graph.  No counterpart in
+ * the reference, whose GEMMs read the fp32 tensors directly. */
+enum
+{
+  DPC_WROTE_Z = 1,
+  DPC_WROTE_FE = 2,
+  DPC_WROTE_W = 4
+};
+DPC_API int dpc_plan_invalidate(dpc_plan* plan, int first, int count, int what);
+DPC_API int dpc_plan_sync_operands(dpc_plan* plan);
+/* Every device-side wait of the tensor-core kernels (pipeline barriers, the forward sweep's
+ * row-block publications) gives up after this long; the kernel then drains, frees its tensor
+ * memory and returns, and the next dpc_energy_read reports DPC_ERR_TIMEOUT.  milliseconds <= 0
+ * restores the default (about 2 s).  sweep_target_bias is added to the number of publications
+ * the forward sweep waits for per row block: a positive value makes that wait impossible to
+ * satisfy (the host-side way to exercise the time-out path; 0 in normal use).  The reference
+ * has no device-side waits (src/backend/cuda/CUDACommon.cuh:16-25 only logs CUDA errors). */
+DPC_API int dpc_plan_set_wait_limit(dpc_plan* plan, double milliseconds, int sweep_target_bias);
 
 /* ---- phases.  Layer ranges are [first, first+count) over the plan's table. ---------- */
 enum

@@ -73,7 +73,7 @@ def build(verbose: bool = True) -> str | None:
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
     cmd = [
-        "g++", "-std=c++20", "-O2", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared",
+        "g++", "-std=c++20", "-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared",
         "-I", os.path.join(HERE, "shim"),
         "-I", os.path.join(root, "include"),
         "-I", os.path.join(root, "src", "backend"),

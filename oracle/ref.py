@@ -59,6 +59,8 @@ def lib():
         L.ref_omp_threads.restype = ctypes.c_int
         L.ref_num_procs.restype = ctypes.c_int
         L.ref_blas_config.restype = ctypes.c_char_p
+        L.ref_blas_threads.restype = ctypes.c_int
+        L.ref_set_threads.argtypes = [ctypes.c_int]
         _lib = L
     return _lib
 
@@ -153,7 +155,13 @@ class RefNet:
 def host_info() -> dict:
     L = lib()
     return {"omp_threads": L.ref_omp_threads(), "nproc": L.ref_num_procs(),
-            "blas": L.ref_blas_config().decode()}
+            "blas_threads": L.ref_blas_threads(), "blas": L.ref_blas_config().decode()}
+
+
+def set_threads(n: int) -> None:
+    """Cap the OpenMP / OpenBLAS thread count of the compiled reference (after its own
+    DynamicThread policy has run once, i.e. after the first train step)."""
+    lib().ref_set_threads(int(n))
 
 
 class RefConvNet:

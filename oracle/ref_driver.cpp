@@ -415,4 +415,18 @@ const char* ref_blas_config(void)
 {
   return scipy_openblas_get_config();
 }
+int ref_blas_threads(void)
+{
+  return scipy_openblas_get_num_threads();
+}
+// Caps the thread count below what DynamicThread picked (a host whose CPU quota or affinity
+// mask is smaller than omp_get_num_procs() reports would otherwise be oversubscribed).
+// DynamicThread is memoised on its own target, so the cap holds until the batch size changes.
+void ref_set_threads(int n)
+{
+  if (n < 1)
+    n = 1;
+  omp_set_num_threads(n);
+  scipy_openblas_set_num_threads(n);
+}
 }

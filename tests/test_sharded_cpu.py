@@ -51,6 +51,9 @@ class OracleEngine:
         for L in self.o.layers:
             L.clamped = False
 
+    def wrote_belief(self, layer):
+        pass
+
     def mark_clamped(self, layer):
         self.o.layers[layer].clamped = True
         self.o.layers[layer].cache_valid = False
