@@ -75,6 +75,11 @@ SIGNATURES = {
     "dpcn_tensor_size": (_i64, [_vp, _i, _cp]),
     "dpcn_get_tensor": (_i, [_vp, _i, _cp, c_f32p, _i64]),
     "dpcn_set_tensor": (_i, [_vp, _i, _cp, c_f32p, _i64]),
+    "dpcn_get_counter": (_i, [_vp, _i, _cp, ctypes.POINTER(ctypes.c_int32)]),
+    "dpcn_set_counter": (_i, [_vp, _i, _cp, ctypes.c_int32]),
+    "dpcn_state_dict_size": (_i, [_vp]),
+    "dpcn_state_dict_entry": (_i, [_vp, _i, ctypes.POINTER(_i), _cp, _i, ctypes.POINTER(_i64),
+                                   ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i)]),
     "dpcn_tensor_ptr": (_i, [_vp, _i, _cp, ctypes.POINTER(_vp), ctypes.POINTER(_i64)]),
     "dpcn_randomize": (_i, [_vp, ctypes.c_uint32]),
     "dpcn_train_step": (_i, [_vp, c_f32p, _i64, c_f32p, _i64, _i, c_f32p]),

@@ -505,6 +505,15 @@ enum
   K_W = 2
 };
 
+static FePlanes fe_planes(dpc_plan* p)
+{
+  FePlanes P;
+  void* base = nullptr;
+  tc_fe_planes(p, &base, &P.run_first, &P.run_count, &P.elems, &P.only);
+  P.fe = static_cast<__nv_bfloat16*>(base);
+  return P;
+}
+
 static int forward_simt(dpc_plan* p, int first, int count, int flags)
 {
   cudaStream_t st = p->ctx->stream;
@@ -795,6 +804,7 @@ static int launch_dfa_proj(dpc_plan* p, int first, int count, int from_output)
 {
   cudaStream_t st = p->ctx->stream;
   wrote(p, K_FE, first, count);
+  const FePlanes planes = fe_planes(p);
   auto vec_ok = [&](int i)
   {
     const dpc_layer& L = p->h[i];
@@ -821,13 +831,13 @@ static int launch_dfa_proj(dpc_plan* p, int first, int count, int from_output)
       dim3 grid(cdiv(mxn, 256), cdiv(p->batch, rpb), c);
       const int ts4 = cdiv(std::max(p->h[i].terminal_size, 1), 4);
       if (ts4 <= 1)
-        dfa_proj4_kernel<1><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb);
+        dfa_proj4_kernel<1><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb, planes);
       else if (ts4 == 2)
-        dfa_proj4_kernel<2><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb);
+        dfa_proj4_kernel<2><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb, planes);
       else if (ts4 == 3)
-        dfa_proj4_kernel<3><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb);
+        dfa_proj4_kernel<3><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb, planes);
       else
-        dfa_proj4_kernel<4><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb);
+        dfa_proj4_kernel<4><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb, planes);
     }
     else
     {
@@ -837,6 +847,8 @@ static int launch_dfa_proj(dpc_plan* p, int first, int count, int from_output)
     int rc = check_launch(p->ctx, "dfa_proj kernel");
     if (rc != DPC_OK)
       return rc;
+    if (v && planes.fe)
+      tc_fe_written(p, i, c); // this kernel wrote the operand copies itself
     i = j;
   }
   return DPC_OK;
@@ -927,7 +939,9 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
   {
     const int c = std::min(kMaxZ, first + count - f);
     dim3 gb(std::max(1, cdiv(max_next, 128)), c);
-    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch, 0);
+    if ((rc = tc_fe_need(p, f, c)) != DPC_OK)
+      return rc;
+    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch, 0, fe_planes(p));
     if ((rc = check_launch(p->ctx, "bias_update kernel")) != DPC_OK)
       return rc;
     if (any_psi)
@@ -1004,7 +1018,9 @@ int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
   {
     const int c = std::min(kMaxZ, first + count - f);
     dim3 gb(std::max(1, cdiv(max_next, 128)), c);
-    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch, 1);
+    if ((rc = tc_fe_need(p, f, c)) != DPC_OK)
+      return rc;
+    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch, 1, fe_planes(p));
     if ((rc = check_launch(p->ctx, "bias gradient kernel")) != DPC_OK)
       return rc;
     if (any_psi)

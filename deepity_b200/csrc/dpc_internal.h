@@ -82,6 +82,14 @@ void tc_set_chain_trace(dpc_plan* plan, unsigned long long* buf);
 // (0 beliefs, 1 feedback errors, 2 weights) of layers [first, first+count); tc_sync_planes:
 // re-split everything that is stale now (before a CUDA graph of a step is recorded or replayed).
 void tc_touch(dpc_plan* plan, int kind, int first, int count);
+// The feedback-error planes for kernels outside dpc_tc.cu that write or read them: device
+// base (NULL: none), the run they cover, elements per plane, and whether the run's fp32 feedback
+// errors are not kept at all.  tc_fe_written: such a kernel wrote planes of layers
+// [first, first+count) itself; tc_fe_need: bring the planes of those layers up to date.
+void tc_fe_planes(dpc_plan* plan, void** base, int* run_first, int* run_count, long long* elems,
+                  int* only);
+void tc_fe_written(dpc_plan* plan, int first, int count);
+int tc_fe_need(dpc_plan* plan, int first, int count);
 int tc_sync_planes(dpc_plan* plan);
 // Limit of every bounded device-side wait in clock cycles (<= 0: the default, ~2 s) and a bias
 // on the forward sweep's publication target (test hook: a target nothing reaches).

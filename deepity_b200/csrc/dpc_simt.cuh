@@ -4,6 +4,7 @@
 // of layers: blockIdx.z selects the layer, blockIdx.x/y the output tile; CTAs outside a
 // layer's own tile grid return at once.
 #pragma once
+#include <cuda_bf16.h>
 #include "dpc_math.cuh"
 
 namespace dpc
@@ -668,6 +669,23 @@ __global__ void dfa_proj_kernel(const dpc_layer* __restrict__ layers, int first,
   }
 }
 
+// The tensor-core path's bf16 "hi"/"mid" operand copies of the feedback errors of the layers
+// [run_first, run_first + run_count): layer l has its hi plane at fe + 2 (l - run_first) * elems
+// and its mid plane elems further on.  fe == NULL: no copies.  only != 0: the fp32 tensor of
+// those layers is not kept at all (nothing reads it), the copies are the feedback error.
+struct FePlanes
+{
+  __nv_bfloat16* fe;
+  int run_first, run_count, only;
+  long long elems;
+};
+__device__ __forceinline__ __nv_bfloat16* fe_plane_of(const FePlanes& P, int li)
+{
+  return (P.fe && li >= P.run_first && li < P.run_first + P.run_count)
+             ? P.fe + 2 * (long long)(li - P.run_first) * P.elems
+             : nullptr;
+}
+
 // The same projection, four output units per thread with 128-bit accesses, for the common
 // Rows per block of the aligned kernel: its per-thread rows of Psi are strided 4-byte loads that
 // cost as much L2 traffic as 32 rows of useful data, so a block amortises them over up to 128 rows
@@ -677,7 +695,8 @@ constexpr int DFA4_ROWS = 128;
 template <int TS4>
 __global__ void __launch_bounds__(64)
     dfa_proj4_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
-                     const float* __restrict__ eT, int from_output, int rows_per_block)
+                     const float* __restrict__ eT, int from_output, int rows_per_block,
+                     FePlanes planes)
 {
   const int li = first + blockIdx.z;
   if (li + 1 >= n_layers)
@@ -709,6 +728,8 @@ __global__ void __launch_bounds__(64)
   const bool out_d = from_output && act_has_output_deriv(L.act);
   const float* src = out_d ? Lup.z : L.preact;
   const int rows = min(rows_per_block, batch - b0);
+  __nv_bfloat16* hi = fe_plane_of(planes, li);
+  const bool keep_fp32 = !(hi && planes.only);
 #pragma unroll 8
   for (int r = 0; r < rows; ++r)
   {
@@ -733,7 +754,22 @@ __global__ void __launch_bounds__(64)
 #pragma unroll
     for (int c = 0; c < 4; ++c)
       out[c] = acc[c] * (out_d ? act_deriv_from_output(L.act, sv[c]) : act_deriv(L.act, sv[c]));
-    *reinterpret_cast<float4*>(L.fe + o) = make_float4(out[0], out[1], out[2], out[3]);
+    if (keep_fp32)
+      *reinterpret_cast<float4*>(L.fe + o) = make_float4(out[0], out[1], out[2], out[3]);
+    if (hi)
+    {
+      const __nv_bfloat162 h0 = __floats2bfloat162_rn(out[0], out[1]);
+      const __nv_bfloat162 h1 = __floats2bfloat162_rn(out[2], out[3]);
+      const __nv_bfloat162 m0 =
+          __floats2bfloat162_rn(out[0] - __low2float(h0), out[1] - __high2float(h0));
+      const __nv_bfloat162 m1 =
+          __floats2bfloat162_rn(out[2] - __low2float(h1), out[3] - __high2float(h1));
+      uint2 hv, mv;
+      hv.x = *reinterpret_cast<const uint32_t*>(&h0), hv.y = *reinterpret_cast<const uint32_t*>(&h1);
+      mv.x = *reinterpret_cast<const uint32_t*>(&m0), mv.y = *reinterpret_cast<const uint32_t*>(&m1);
+      *reinterpret_cast<uint2*>(hi + o) = hv;
+      *reinterpret_cast<uint2*>(hi + planes.elems + o) = mv;
+    }
   }
 }
 
@@ -757,7 +793,7 @@ __global__ void bump_counters_kernel(const dpc_layer* __restrict__ layers, int f
 // Bias update from the column sums of the local gradient: one thread per output unit,
 // summing the batch in row order like CPUBackend::SumRows (CPUBackend.cpp:243-248).
 __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
-                                   int batch, int grad_only)
+                                   int batch, int grad_only, FePlanes planes)
 {
   const int li = first + blockIdx.y;
   if (li + 1 >= n_layers)
@@ -768,11 +804,18 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
   const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
   const float* g = simple ? layers[li + 1].e : L.fe;
   const int n = L.next_size;
+  // where the fp32 feedback error is not kept, its two bf16 planes are (hi + mid = fe to 2^-17)
+  const __nv_bfloat16* hi = (!simple && planes.only) ? fe_plane_of(planes, li) : nullptr;
   for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x)
   {
     float s = 0.0f;
-    for (int b = 0; b < batch; ++b)
-      s += g[(size_t)b * n + j];
+    if (hi)
+      for (int b = 0; b < batch; ++b)
+        s += __bfloat162float(hi[(size_t)b * n + j]) +
+             __bfloat162float(hi[planes.elems + (size_t)b * n + j]);
+    else
+      for (int b = 0; b < batch; ++b)
+        s += g[(size_t)b * n + j];
     if (grad_only)
       L.g_b[j] = s;
     else if (L.opt == DPC_OPT_SGD)

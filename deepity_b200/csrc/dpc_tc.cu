@@ -90,6 +90,9 @@ struct TcState
   CUtensorMap zp_km, zp_mn, fep_km, fep_mn, wp_km128, wp_km64, wp_mn;
   std::vector<uint8_t> dirty[3];
   bool planes = false;
+  // The run's feedback errors exist only as planes: every reader of them is a kernel that takes
+  // the planes (feedback and weight-shaped products of this file, the bias column sums).
+  bool fe_only = false;
   bool warned_fallback = false;
 };
 enum
@@ -129,6 +132,7 @@ struct TcParams
   __nv_bfloat16 *zp, *fep, *wp;
   long long act_elems, w_elems; // elements per plane: batch x width, width x width
   long long wait_cycles;        // limit of every bounded wait of this launch
+  int fe_only;                  // the fp32 feedback error of the run's layers is not written
 };
 
 // ------------------------------------------------------------------------------ PTX
@@ -700,7 +704,8 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
           e[q] *= d[q];
         if (active)
         {
-          st8(L.fe + o + k, e);
+          if (!P.fe_only)
+            st8(L.fe + o + k, e);
           if (L.fe_hi)
             st_planes8(L.fe_hi, P.act_elems, o + k, e);
         }
@@ -1668,7 +1673,12 @@ static bool planes_init(dpc_plan* plan, TcState* st, int first, int count, int H
   st->dirty[PL_FE].assign(count, 1);
   st->dirty[PL_W].assign(count, 1);
   st->planes = true;
-  (void)first;
+  // fp32 feedback errors can be dropped when nothing but the plane-reading kernels consumes
+  // them: no ePC adjoint chain (it keeps its source in fe), feedback weights above every layer
+  // of the run (else the direct-feedback product falls to the CUDA-core kernel, which reads fp32).
+  st->fe_only = !getenv("DPC_KEEP_FE_FP32");
+  for (int i = first; i < first + count && st->fe_only; ++i)
+    st->fe_only = !plan->h[i].adj && i + 1 < plan->n && plan->h[i + 1].Psi != nullptr;
   return true;
 }
 
@@ -1938,6 +1948,13 @@ static bool planes_kept(const dpc_plan* p, const TcState* st)
   return planes_on(p, st);
 }
 
+// The fp32 feedback errors of the run are dropped only in the plain FP32 mode: the mixed mode's
+// one-pass gradient products read the fp32 tensor.
+static bool fe_only_now(const dpc_plan* p, const TcState* st)
+{
+  return planes_kept(p, st) && st->fe_only && p->ctx->precision == DPC_PRECISION_FP32;
+}
+
 static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int M, int N, int K,
                             int BN, int flags, int mode, int BM = TBM)
 {
@@ -1949,6 +1966,7 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
   P.act_elems = (long long)p->batch * p->run.width;
   P.w_elems = (long long)p->run.width * p->run.width;
   P.wait_cycles = st->wait_cycles;
+  P.fe_only = fe_only_now(p, st) ? 1 : 0;
   P.layers = p->d;
   P.first = first;
   P.count = count;
@@ -2157,12 +2175,22 @@ int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
   for (int i = first; i < first + count; ++i)
   {
     const dpc_layer& L = p->h[i];
+    bool eligible = true;
     if (mode == WG_LEARN_MODE && L.opt != DPC_OPT_SGD)
-      return 1; // Adam-type updates go through the staging buffer (mode | WG_GRAD_MODE)
+      eligible = false; // Adam-type updates go through the staging buffer (mode | WG_GRAD_MODE)
     if ((mode & WG_GRAD_MODE) && (!L.g_W || ((uintptr_t)L.g_W % 32) != 0))
-      return 1;
+      eligible = false;
     if ((mode & 1) == WG_DFA_MODE && (i + 1 >= p->n || !p->h[i + 1].Psi))
+      eligible = false;
+    if (!eligible)
+    {
+      if (fe_only_now(p, st))
+        return fail(DPC_ERR_STATE, "weight-shaped product of a tensor-core layer is not eligible "
+                                   "for the tensor-core kernel, and the fp32 feedback errors the "
+                                   "CUDA-core kernel would read are not kept (DPC_KEEP_FE_FP32=1 "
+                                   "keeps them)");
       return 1;
+    }
   }
   const int H = p->run.width, B = p->batch;
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || fast_grad(p);
@@ -2208,6 +2236,33 @@ void tc_touch(dpc_plan* p, int kind, int first, int count)
   if (!st || !st->planes || kind < 0 || kind > 2)
     return;
   planes_mark(st, kind, first - p->run.first, first + count - p->run.first, 1);
+}
+
+void tc_fe_planes(dpc_plan* p, void** base, int* run_first, int* run_count, long long* elems,
+                  int* only)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  const bool on = st && st->planes && planes_on(p, st);
+  *base = on ? st->fep : nullptr;
+  *run_first = p->run.first;
+  *run_count = on ? p->run.count : 0;
+  *elems = (long long)p->batch * p->run.width;
+  *only = (on && fe_only_now(p, st)) ? 1 : 0;
+}
+
+void tc_fe_written(dpc_plan* p, int first, int count)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (st && st->planes)
+    planes_mark(st, PL_FE, first - p->run.first, first + count - p->run.first, 0);
+}
+
+int tc_fe_need(dpc_plan* p, int first, int count)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  if (!st || !st->planes || !planes_on(p, st))
+    return DPC_OK;
+  return planes_need(p, st, PL_FE, first - p->run.first, first + count - p->run.first);
 }
 
 int tc_sync_planes(dpc_plan* p)

@@ -1155,6 +1155,55 @@ double PCNetwork::TrainStepFlops(int T) const
   return total;
 }
 
+int32_t* PCNetwork::Counter(int layer, const std::string& name)
+{
+  if (layer < 0 || layer >= (int)layers.size() || !plan)
+    return nullptr;
+  SyncPlan(); // an optimizer chosen after Compile() gets its state here
+  const dpc_layer& d = layers[layer]->d;
+  if (d.next_size <= 0)
+    return nullptr;
+  if (name == "step")
+    return d.opt != DPC_OPT_SGD ? d.t : nullptr;
+  if (name == "psi_step")
+    return (d.Psi && d.opt_psi != DPC_OPT_SGD) ? d.t_Psi : nullptr;
+  return nullptr;
+}
+
+// What Layer::GetStateDict() and GetOptimizerStateDict() list for every weight layer
+// (src/layers/DirectKPPCLayer.cpp:219-235, src/layers/SimplePCLayer.cpp, FullPCLayer.cpp).
+std::vector<PCNetwork::StateEntry> PCNetwork::StateDict()
+{
+  std::vector<StateEntry> out;
+  if (!plan)
+    return out;
+  SyncPlan();
+  for (int i = 0; i < (int)layers.size(); ++i)
+  {
+    const dpc_layer& d = layers[i]->d;
+    if (d.next_size <= 0)
+      continue;
+    const size_t s = d.size, n = d.next_size, ts = d.terminal_size, ps = d.psi_stride;
+    out.push_back({i, "W", n, s, s, false});
+    out.push_back({i, "b", 1, n, n, false});
+    if (d.Psi)
+      out.push_back({i, "Psi", s, ts, ps, false});
+    if (d.opt != DPC_OPT_SGD && d.m_W)
+    {
+      out.push_back({i, "weight.m", n, s, s, true});
+      out.push_back({i, "weight.v", n, s, s, true});
+      out.push_back({i, "bias.m", 1, n, n, true});
+      out.push_back({i, "bias.v", 1, n, n, true});
+    }
+    if (d.Psi && d.opt_psi != DPC_OPT_SGD && d.m_Psi)
+    {
+      out.push_back({i, "psi.m", s, ts, ps, true});
+      out.push_back({i, "psi.v", s, ts, ps, true});
+    }
+  }
+  return out;
+}
+
 bool PCNetwork::FindTensor(int layer, const std::string& name, float** ptr, size_t* rows,
                            size_t* cols, size_t* stride)
 {
@@ -1365,6 +1414,86 @@ int64_t dpcn_tensor_size(dpcn_net* net, int layer, const char* name)
   return (int64_t)(r * c);
 }
 
+// Device address of an optimizer step counter, or NULL (no such layer / SGD).
+static int32_t* CounterPtr(dpcn_net* net, int layer, const char* name)
+{
+  if (!net || !name)
+    return nullptr;
+  return net->net->Counter(layer, name);
+}
+
+int dpcn_get_counter(dpcn_net* net, int layer, const char* name, int32_t* out)
+{
+  if (!net || !name || !out)
+    return DPC_ERR_INVALID;
+  std::string nm(name);
+  if (nm != "step" && nm != "psi_step")
+  {
+    dpc::set_error("dpcn_get_counter: the counters are \"step\" and \"psi_step\"");
+    return DPC_ERR_INVALID;
+  }
+  int32_t* p = CounterPtr(net, layer, name);
+  if (!p)
+  {
+    dpc::set_error("dpcn_get_counter: this layer has no such counter (SGD, or no weights)");
+    return DPC_ERR_STATE;
+  }
+  return dpc_copy_d2h_sync(net->net->Context(), out, p, sizeof(int32_t));
+}
+
+int dpcn_set_counter(dpcn_net* net, int layer, const char* name, int32_t value)
+{
+  if (!net || !name)
+    return DPC_ERR_INVALID;
+  std::string nm(name);
+  if (nm != "step" && nm != "psi_step")
+  {
+    dpc::set_error("dpcn_set_counter: the counters are \"step\" and \"psi_step\"");
+    return DPC_ERR_INVALID;
+  }
+  int32_t* p = CounterPtr(net, layer, name);
+  if (!p)
+  {
+    dpc::set_error("dpcn_set_counter: this layer has no such counter (SGD, or no weights)");
+    return DPC_ERR_STATE;
+  }
+  return dpc_copy_h2d_sync(net->net->Context(), p, &value, sizeof(int32_t));
+}
+
+int dpcn_state_dict_size(dpcn_net* net)
+{
+  if (!net)
+    return DPC_ERR_INVALID;
+  return (int)net->net->StateDict().size();
+}
+
+int dpcn_state_dict_entry(dpcn_net* net, int index, int* layer, char* name, int name_bytes,
+                          int64_t* rows, int64_t* cols, int64_t* row_stride, int* optimizer_state)
+{
+  if (!net)
+    return DPC_ERR_INVALID;
+  const auto dict = net->net->StateDict();
+  if (index < 0 || index >= (int)dict.size())
+  {
+    dpc::set_error("dpcn_state_dict_entry: index out of range");
+    return DPC_ERR_INVALID;
+  }
+  const auto& e = dict[index];
+  if (layer)
+    *layer = e.layer;
+  if (name && name_bytes > 0)
+    snprintf(name, (size_t)name_bytes, "%s", e.name.c_str());
+  if (rows)
+    *rows = (int64_t)e.rows;
+  if (cols)
+    *cols = (int64_t)e.cols;
+  if (row_stride)
+    *row_stride = (int64_t)e.stride;
+  if (optimizer_state)
+    *optimizer_state = e.optimizer ? 1 : 0;
+  return DPC_OK;
+}
+
 int dpcn_tensor_ptr(dpcn_net* net, int layer, const char* name, void** out, int64_t* row_stride)
 {
   float* p;
@@ -1415,8 +1544,9 @@ int dpcn_set_tensor(dpcn_net* net, int layer, const char* name, const float* hos
   }
   dpc_ctx* ctx = net->net->Context();
   const std::string nm(name);
-  if (nm == "z" || nm == "W")
-    dpc_plan_invalidate(net->net->Plan(), layer, 1, nm == "z" ? DPC_WROTE_Z : DPC_WROTE_W);
+  if (nm == "z" || nm == "W" || nm == "fe")
+    dpc_plan_invalidate(net->net->Plan(), layer, 1,
+                        nm == "z" ? DPC_WROTE_Z : (nm == "W" ? DPC_WROTE_W : DPC_WROTE_FE));
   if (st == c)
     return dpc_copy_h2d_sync(ctx, p, host_in, r * c * sizeof(float));
   std::vector<float> tmp(r * st, 0.0f);

@@ -181,6 +181,18 @@ public:
   // Tensor lookup for the binding layer; returns false when the layer has no such tensor.
   bool FindTensor(int layer, const std::string& name, float** ptr, size_t* rows, size_t* cols,
                   size_t* stride);
+  // Device address of an Adam / AdamW step counter ("step", "psi_step":
+  // Layer::GetOptimizerCounters) or nullptr when the layer has none.
+  int32_t* Counter(int layer, const std::string& name);
+  // One entry per tensor of Layer::GetStateDict() / GetOptimizerStateDict() of every weight layer.
+  struct StateEntry
+  {
+    int layer;
+    std::string name;
+    size_t rows, cols, stride;
+    bool optimizer;
+  };
+  std::vector<StateEntry> StateDict();
 
 private:
   void Check(int rc) const;

@@ -304,6 +304,76 @@ class _Network:
         _lib.check(lib.dpcn_set_gradient_sync(self._h, ctypes.cast(self._sync_cb, ctypes.c_void_p),
                                               None, int(global_batch)))
 
+    # -- checkpoint surface: the reference's tensor names (docs/model-format.md:104-117) ------
+    _PUBLIC = {"W": "weight", "b": "bias", "Psi": "psi"}
+
+    def _state_entries(self):
+        lib, out = self._lib, []
+        layer, rows, cols, stride, opt = (ctypes.c_int(), ctypes.c_int64(), ctypes.c_int64(),
+                                          ctypes.c_int64(), ctypes.c_int())
+        name = ctypes.create_string_buffer(32)
+        for i in range(_lib.check(lib.dpcn_state_dict_size(self._h))):
+            _lib.check(lib.dpcn_state_dict_entry(self._h, i, ctypes.byref(layer), name, 32,
+                                                 ctypes.byref(rows), ctypes.byref(cols),
+                                                 ctypes.byref(stride), ctypes.byref(opt)))
+            out.append((layer.value, name.value.decode(), rows.value, cols.value, bool(opt.value)))
+        return out
+
+    def state_dict(self) -> dict:
+        """``layers.{i}.weight|bias|psi`` -> numpy array, the names and shapes the reference's
+        ``save()`` writes (``Layer::GetStateDict``)."""
+        self._require_configured()
+        out = {}
+        for layer, name, rows, cols, opt in self._state_entries():
+            if not opt:
+                a = self.get_tensor(layer, name)
+                out[f"layers.{layer}.{self._PUBLIC[name]}"] = a.reshape(cols) if rows == 1 \
+                    else a.reshape(rows, cols)
+        return out
+
+    def optimizer_state_dict(self) -> dict:
+        """``optimizer.layers.{i}.{weight,bias,psi}.{m,v}`` plus the step counters
+        ``optimizer.layers.{i}.step`` / ``psi_step`` (int32, shape [1]): what the reference's
+        ``save_checkpoint`` adds to the weights (``Layer::GetOptimizerStateDict`` and
+        ``GetOptimizerCounters``)."""
+        self._require_configured()
+        out, layers = {}, set()
+        for layer, name, rows, cols, opt in self._state_entries():
+            layers.add(layer)
+            if opt:
+                a = self.get_tensor(layer, name)
+                out[f"optimizer.layers.{layer}.{name}"] = a.reshape(cols) if rows == 1 \
+                    else a.reshape(rows, cols)
+        for layer in sorted(layers):
+            for counter in ("step", "psi_step"):
+                v = ctypes.c_int32()
+                if self._lib.dpcn_get_counter(self._h, layer, counter.encode(), ctypes.byref(v)) == 0:
+                    out[f"optimizer.layers.{layer}.{counter}"] = np.asarray([v.value], dtype=np.int32)
+        return out
+
+    def load_state_dict(self, state: dict, strict: bool = True) -> None:
+        """Inverse of ``state_dict()`` + ``optimizer_state_dict()`` (either or both merged into
+        one mapping).  ``strict``: every tensor this network owns must be present."""
+        self._require_configured()
+        back = {v: k for k, v in self._PUBLIC.items()}
+        seen = set()
+        for key, value in state.items():
+            parts = key.split(".")
+            if parts[0] == "optimizer":
+                layer, name = int(parts[2]), ".".join(parts[3:])
+                if name in ("step", "psi_step"):
+                    _lib.check(self._lib.dpcn_set_counter(self._h, layer, name.encode(),
+                                                          int(np.asarray(value).ravel()[0])))
+                    continue
+            else:
+                layer, name = int(parts[1]), back[parts[2]]
+            self.set_tensor(layer, name, value)
+            seen.add((layer, name))
+        if strict:
+            missing = [f"{l}.{n}" for l, n, _, _, _ in self._state_entries() if (l, n) not in seen]
+            if missing:
+                raise KeyError(f"load_state_dict: missing tensors {missing[:6]}")
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.dpcn_launch_count(self._h))

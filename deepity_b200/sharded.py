@@ -222,6 +222,39 @@ class ShardedDKPPCN:
     def get_local(self, layer: int, name: str):
         return self.eng.get(layer - self.begin, name)
 
+    # ---- checkpoint surface: global tensor names, one shard per rank ------------------------
+    def local_state_dict(self) -> dict:
+        """This rank's parameters under the names a single-process network gives them
+        (``layers.{global index}.weight|bias|psi``, docs/model-format.md:104-117 of the
+        reference): the shard a per-rank checkpoint file holds."""
+        out = {}
+        for g in range(self.begin, self.end):
+            s, n = self.sizes[g], self.sizes[g + 1]
+            out[f"layers.{g}.weight"] = np.asarray(self.get_local(g, "W")).reshape(n, s)
+            out[f"layers.{g}.bias"] = np.asarray(self.get_local(g, "b")).reshape(n)
+            out[f"layers.{g}.psi"] = np.asarray(self.get_local(g, "Psi")).reshape(s, self.ts)
+        return out
+
+    def gather_state_dict(self, dst: int = 0):
+        """The whole network's state dict on rank ``dst`` (None elsewhere)."""
+        parts = [None] * self.world if self.rank == dst else None
+        self.dist.gather_object(self.local_state_dict(), parts, dst=dst, group=self.group)
+        if parts is None:
+            return None
+        merged = {}
+        for part in parts:
+            merged.update(part)
+        return merged
+
+    def load_state_dict(self, state: dict) -> None:
+        """Takes the tensors of the layers this rank owns from a whole-network (or per-rank)
+        state dict; names of other ranks' layers are ignored."""
+        names = {"weight": "W", "bias": "b", "psi": "Psi"}
+        for key, value in state.items():
+            _, index, kind = key.split(".")
+            if self.owns(int(index)):
+                self.set_param(int(index), names[kind], value)
+
     # ---- communication helpers -------------------------------------------------------------
     def _exchange(self, send=None, recv=None):
         """send/recv: (tensor, peer rank) or None; both are posted before either is waited on."""

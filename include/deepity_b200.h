@@ -352,6 +352,22 @@ DPC_API int dpcn_get_tensor(dpcn_net* net, int layer, const char* name, float* h
                             int64_t count);
 DPC_API int dpcn_set_tensor(dpcn_net* net, int layer, const char* name, const float* host_in,
                             int64_t count);
+/* Adam / AdamW step counters of a weight layer by the reference's names: "step" (W and b) and
+ * "psi_step" (Psi) (Layer::GetOptimizerCounters, include/deepity/layers/Layer.h:100-134,
+ * src/layers/DirectKPPCLayer.cpp:237-241; IComputeBackend::CopyCounterToHost/FromHost).  They
+ * live on the device; get is synchronous.  DPC_ERR_STATE when the optimizer is SGD (no counter). */
+DPC_API int dpcn_get_counter(dpcn_net* net, int layer, const char* name, int32_t* out);
+DPC_API int dpcn_set_counter(dpcn_net* net, int layer, const char* name, int32_t value);
+/* Enumeration of everything a checkpoint of the reference holds for this network
+ * (Layer::GetStateDict + GetOptimizerStateDict of every weight layer,
+ * src/layers/DirectKPPCLayer.cpp:219-235): entry `index` in [0, dpcn_state_dict_size) gives the
+ * layer, the tensor name as dpcn_get_tensor takes it ("W" "b" "Psi" "weight.m" ...), its logical
+ * shape rows x cols (rows = 1 for vectors), the element stride between rows on the device
+ * (TensorDescriptor::rowStride) and whether it is optimizer state. */
+DPC_API int dpcn_state_dict_size(dpcn_net* net);
+DPC_API int dpcn_state_dict_entry(dpcn_net* net, int index, int* layer, char* name, int name_bytes,
+                                  int64_t* rows, int64_t* cols, int64_t* row_stride,
+                                  int* optimizer_state);
 /* Device pointer of a tensor (zero-copy consumers; FullPCNetwork::TrainStepDevice idea). */
 DPC_API int dpcn_tensor_ptr(dpcn_net* net, int layer, const char* name, void** out,
                             int64_t* row_stride);

@@ -60,6 +60,39 @@ def rel_err(ref, got):
     return float(np.abs(ref - got).max() / max(1.0, np.abs(ref).max()))
 
 
+def rel_err_of_update(ref, got, init):
+    """Error of the UPDATE (after - initial) relative to the largest update element.  Weights
+    are of order 0.1 and their per-step updates of order lr, so a bound relative to
+    max(1, |W|) alone would also pass when the update is missing altogether."""
+    init = np.asarray(init, dtype=np.float64).ravel()
+    ref = np.asarray(ref, dtype=np.float64).ravel()
+    d_ref = ref - init
+    d_got = np.asarray(got, dtype=np.float64).ravel() - init
+    if d_ref.size == 0:
+        return 0.0
+    # both sides store the parameter in fp32: a few ulps of the parameter itself are not an
+    # error of the update
+    slack = 4 * np.finfo(np.float32).eps * np.abs(ref).max()
+    err = max(0.0, float(np.abs(d_ref - d_got).max()) - slack)
+    scale = np.abs(d_ref).max()
+    return err if scale == 0.0 else err / scale
+
+
+# Bounds on the error of the parameter UPDATES (see rel_err_of_update), SGD cases only: an
+# Adam-type step m/(sqrt(v)+eps) can flip by a whole step on a near-zero gradient element.
+DELTA_TOL = 2e-3        # fp32 mode (CUDA cores, 3xTF32, 3xBF16)
+DELTA_TOL_MIXED = 3e-2  # gradient products in one TF32 pass
+DELTA_TOL_TF32 = 1e-1   # everything in one TF32 pass
+
+
+def initial_parameters(case):
+    """The seeded W, b, Psi a case starts from, keyed like the outputs ("t.<layer>.<name>")."""
+    params, _, _ = make_case(case["kind"], case["sizes"], case["batch"], seed=case.get("seed", 0),
+                             x_dist=case.get("x_dist", "normal"))
+    return {f"t.{l}.{name}": np.asarray(v, dtype=np.float32).ravel()
+            for l, p in enumerate(params) for name, v in p.items()}
+
+
 def state_names(kind):
     return ["z", "e", "W", "b"] + ([] if kind == "simple" else ["Psi"])
 
@@ -167,11 +200,21 @@ def run_gpu(case, precision="fp32", use_graph=True, staged_gradients=False):
     return out
 
 
-def compare_outputs(ref, got, tol, what="", energy_tol=None):
+def compare_outputs(ref, got, tol, what="", energy_tol=None, init=None, delta_tol=None):
     """ref may hold full tensors (t.*) or statistics (stat.*).  energy_tol: a separate bound
-    for the energies where the reference's own fp32 accumulation is the limit."""
+    for the energies where the reference's own fp32 accumulation is the limit.  init (from
+    initial_parameters) with delta_tol: the parameter updates themselves are compared too."""
     worst = 0.0
     bad = []
+    if init is not None:
+        worst_delta = 0.0
+        for k, w0 in init.items():
+            if k in ref and k in got:
+                err = rel_err_of_update(ref[k], got[k], w0)
+                worst_delta = max(worst_delta, err)
+                if not err <= delta_tol:
+                    bad.append((k + " (update)", err))
+        print(f"{what}: worst relative error of a parameter update {worst_delta:.2e}")
     for k, r in ref.items():
         if k == "energies":
             err = float(np.max(np.abs(r - got[k]) / np.maximum(1.0, np.abs(r))))

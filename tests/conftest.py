@@ -2,6 +2,11 @@ import os
 import sys
 import warnings
 
+# The compiled reference runs OpenMP regions and OpenBLAS's own thread pool side by side; with
+# OpenMP's default active spinning the two oversubscribe a small host (6x slower measured).
+# Must be set before anything loads libgomp.
+os.environ.setdefault("OMP_WAIT_POLICY", "PASSIVE")
+
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

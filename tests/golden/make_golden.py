@@ -60,6 +60,11 @@ CASES = {
     "full_ipc": dict(kind="full", sizes=[30, 40, 40, 10], batch=16, T=3, steps=2,
                      hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="tanh"),
                      options=dict(ipc=1)),
+    # a shape the tensor-core kernels take (square layers of width 512, batch 1024: CTA-pair
+    # tiles, the persistent forward sweep), so that path meets reference output directly
+    "dkp_tensor_run_shape": dict(kind="dkp", sizes=[512] + [512] * 12 + [10], batch=1024, T=2,
+                                 steps=2, stats_only=True,
+                                 hyper=dict(lr=1e-2, ir=0.1, fl=1e-2, lmbda=0.0, act="tanh")),
 }
 
 
@@ -117,7 +122,10 @@ def run_reference(case):
 
 
 def main():
+    only = set(sys.argv[1:])  # optional: names of the fixtures to (re)generate
     for name, case in CASES.items():
+        if only and name not in only:
+            continue
         out = run_reference(case)
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
         print(name, "energies", out["energies"])

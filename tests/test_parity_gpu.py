@@ -12,7 +12,8 @@ import os
 import numpy as np
 import pytest
 
-from common import (ADAM_TOL, TF32_TOL, TOL, compare_outputs, run_gpu, run_oracle)
+from common import (ADAM_TOL, DELTA_TOL, DELTA_TOL_MIXED, DELTA_TOL_TF32, TF32_TOL, TOL,
+                    compare_outputs, initial_parameters, run_gpu, run_oracle)
 
 pytestmark = pytest.mark.gpu
 
@@ -133,14 +134,16 @@ def test_tensor_core_path_fp32_parity(name, built_library):
     """3xTF32 on the tensor cores is held to the same 1e-4 bound as the CUDA-core path."""
     case = TENSOR[name]
     assert _tensor_run_of(case, "fp32")[1] >= 3, "the tensor-core run was not detected"
-    compare_outputs(run_oracle(case), run_gpu(case, precision="fp32"), TOL, name)
+    compare_outputs(run_oracle(case), run_gpu(case, precision="fp32"), TOL, name,
+                    init=initial_parameters(case), delta_tol=DELTA_TOL)
 
 
 @pytest.mark.parametrize("name", sorted(TENSOR))
 def test_tensor_core_path_tf32_bound(name, built_library):
     """One TF32 pass: the reference's own 1e-2 CPU-vs-GPU bound."""
     case = TENSOR[name]
-    compare_outputs(run_oracle(case), run_gpu(case, precision="tf32"), TF32_TOL, name)
+    compare_outputs(run_oracle(case), run_gpu(case, precision="tf32"), TF32_TOL, name,
+                    init=initial_parameters(case), delta_tol=DELTA_TOL_TF32)
 
 
 def test_adam_on_tensor_core_layers(built_library):
@@ -160,8 +163,11 @@ def test_mixed_precision_mode_bound(built_library):
     case = dict(kind="dkp", sizes=[512] + [512] * 24 + [10], batch=1024, T=2, steps=3, seed=3,
                 hyper=dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.0, act="tanh"))
     ref = run_oracle(case)
-    mixed = compare_outputs(ref, run_gpu(case, precision="mixed"), 1e-3, "mixed")
-    tf32 = compare_outputs(ref, run_gpu(case, precision="tf32"), TF32_TOL, "tf32")
+    init = initial_parameters(case)
+    mixed = compare_outputs(ref, run_gpu(case, precision="mixed"), 1e-3, "mixed", init=init,
+                            delta_tol=DELTA_TOL_MIXED)
+    tf32 = compare_outputs(ref, run_gpu(case, precision="tf32"), TF32_TOL, "tf32", init=init,
+                           delta_tol=DELTA_TOL_TF32)
     assert mixed < tf32
 
 
@@ -172,9 +178,12 @@ def test_both_fp32_operand_splits(built_library, monkeypatch):
     case = dict(kind="dkp", sizes=[512] + [512] * 12 + [10], batch=1024, T=2, steps=3, seed=5,
                 hyper=dict(lr=1e-2, ir=0.1, fl=1e-3, lmbda=0.0, act="tanh"))
     ref = run_oracle(case)
-    bf16 = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "3xBF16 split")
+    init = initial_parameters(case)
+    bf16 = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "3xBF16 split", init=init,
+                           delta_tol=DELTA_TOL)
     monkeypatch.setenv("DPC_FP32_SCHEME", "tf32x3")
-    tf32 = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "3xTF32 split")
+    tf32 = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "3xTF32 split", init=init,
+                           delta_tol=DELTA_TOL)
     print(f"worst relative error: 3xBF16 {bf16:.2e}, 3xTF32 {tf32:.2e}")
     assert tf32 <= bf16
 
@@ -186,8 +195,11 @@ def test_deep_stack_at_benchmark_layer_shape(built_library):
     case = dict(kind="dkp", sizes=[512] + [512] * 48 + [10], batch=1024, T=2, steps=2, seed=3,
                 hyper=dict(lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.0, act="tanh"))
     ref = run_oracle(case)
-    compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "deep stack fp32")
-    compare_outputs(ref, run_gpu(case, precision="tf32"), TF32_TOL, "deep stack tf32")
+    init = initial_parameters(case)
+    compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "deep stack fp32", init=init,
+                    delta_tol=DELTA_TOL)
+    compare_outputs(ref, run_gpu(case, precision="tf32"), TF32_TOL, "deep stack tf32", init=init,
+                    delta_tol=DELTA_TOL_TF32)
 
 
 def test_training_continues_to_track_the_oracle(built_library):

@@ -126,6 +126,17 @@ def _worker(rank, world, port, out):
     if net.is_last:
         res[f"{net.end}.z"] = net.get_local(net.end, "z")
         res[f"{net.end}.e"] = net.get_local(net.end, "e")
+    # checkpoint surface: the whole network's tensors by global name on rank 0, and back
+    gathered = net.gather_state_dict(dst=0)
+    if rank == 0:
+        res["state_dict"] = {k: np.array(v) for k, v in gathered.items()}
+    else:
+        assert gathered is None
+    state = [gathered]
+    dist.broadcast_object_list(state, src=0)
+    net.load_state_dict(state[0])
+    for l in range(net.begin, net.end):
+        assert np.array_equal(np.asarray(net.get_local(l, "W")).ravel(), res[f"{l}.W"].ravel())
     out[rank] = res
     dist.destroy_process_group()
 
@@ -150,10 +161,17 @@ def test_sharded_schedule_matches_single_process_oracle(world):
     for r in range(world):
         for a, b in zip(out[r]["energies"], ref_e):
             assert abs(a - b) <= TOL * max(1.0, abs(b)), (r, a, b)
+    sd = out[0]["state_dict"]
+    n_w = len(CASE["sizes"]) - 1
+    assert sorted(sd) == sorted(f"layers.{l}.{n}" for l in range(n_w) for n in ("weight", "bias", "psi"))
+    for l in range(n_w):
+        assert sd[f"layers.{l}.weight"].shape == (CASE["sizes"][l + 1], CASE["sizes"][l])
+        assert rel_err(ref.get(l, "W"), sd[f"layers.{l}.weight"]) <= TOL
+        assert rel_err(ref.get(l, "Psi"), sd[f"layers.{l}.psi"]) <= TOL
     seen = set()
     for r in range(world):
         for key, val in out[r].items():
-            if key == "energies":
+            if key in ("energies", "state_dict"):
                 continue
             l, nm = key.split(".")
             assert rel_err(ref.get(int(l), nm), val) <= TOL, key
