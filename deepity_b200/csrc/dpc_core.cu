@@ -938,10 +938,13 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
   for (int f = first; f < first + count; f += kMaxZ)
   {
     const int c = std::min(kMaxZ, first + count - f);
-    dim3 gb(std::max(1, cdiv(max_next, 128)), c);
     if ((rc = tc_fe_need(p, f, c)) != DPC_OK)
       return rc;
-    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch, 0, fe_planes(p));
+    const FePlanes fp = fe_planes(p);
+    // 256 threads: blocks of 64 columns where the feedback error is read from its planes,
+    // one column per thread (grid-stride) elsewhere
+    dim3 gb(std::max(1, cdiv(max_next, fp.only ? 64 : 256)), c);
+    bias_update_kernel<<<gb, 256, 0, st>>>(p->d, f, p->n, p->batch, 0, fp);
     if ((rc = check_launch(p->ctx, "bias_update kernel")) != DPC_OK)
       return rc;
     if (any_psi)
@@ -1017,10 +1020,11 @@ int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
   for (int f = first; f < first + count; f += kMaxZ)
   {
     const int c = std::min(kMaxZ, first + count - f);
-    dim3 gb(std::max(1, cdiv(max_next, 128)), c);
     if ((rc = tc_fe_need(p, f, c)) != DPC_OK)
       return rc;
-    bias_update_kernel<<<gb, 128, 0, st>>>(p->d, f, p->n, p->batch, 1, fe_planes(p));
+    const FePlanes fp = fe_planes(p);
+    dim3 gb(std::max(1, cdiv(max_next, fp.only ? 64 : 256)), c);
+    bias_update_kernel<<<gb, 256, 0, st>>>(p->d, f, p->n, p->batch, 1, fp);
     if ((rc = check_launch(p->ctx, "bias gradient kernel")) != DPC_OK)
       return rc;
     if (any_psi)

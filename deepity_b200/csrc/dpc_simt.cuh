@@ -790,8 +790,27 @@ __global__ void bump_counters_kernel(const dpc_layer* __restrict__ layers, int f
     *L.t_Psi += 1;
 }
 
+// b (+)= rate * s for one output unit (or s into the staging buffer): what follows the column sum.
+__device__ __forceinline__ void bias_apply(const dpc_layer& L, int j, float s, int batch, int grad_only)
+{
+  if (grad_only)
+    L.g_b[j] = s;
+  else if (L.opt == DPC_OPT_SGD)
+    L.b[j] += (L.lr / (float)batch) * s;
+  else
+  {
+    float m = L.m_b[j], v = L.v_b[j];
+    L.b[j] = adam_update(L.b[j], -s, m, v, adam_step_size(L.lr, *L.t), -1.0f);
+    L.m_b[j] = m;
+    L.v_b[j] = v;
+  }
+}
+
 // Bias update from the column sums of the local gradient: one thread per output unit,
 // summing the batch in row order like CPUBackend::SumRows (CPUBackend.cpp:243-248).
+// Layers whose feedback error exists only as bf16 planes (see FePlanes) are summed by whole
+// blocks instead: 32 row groups x 8 threads of 8 columns each (16-byte loads of both planes,
+// hi + mid = fe to 2^-17), then a fixed-order reduction over the row groups in shared memory.
 __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
                                    int batch, int grad_only, FePlanes planes)
 {
@@ -804,8 +823,43 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
   const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
   const float* g = simple ? layers[li + 1].e : L.fe;
   const int n = L.next_size;
-  // where the fp32 feedback error is not kept, its two bf16 planes are (hi + mid = fe to 2^-17)
   const __nv_bfloat16* hi = (!simple && planes.only) ? fe_plane_of(planes, li) : nullptr;
+  if (hi && n % 64 == 0 && blockDim.x == 256)
+  {
+    __shared__ float part[32][65];
+    const int rg = threadIdx.x >> 3, c8 = (threadIdx.x & 7) * 8;
+    for (int j0 = blockIdx.x * 64; j0 < n; j0 += gridDim.x * 64)
+    {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int b = rg; b < batch; b += 32)
+      {
+        const size_t o = (size_t)b * n + j0 + c8;
+        const uint4 h = *reinterpret_cast<const uint4*>(hi + o);
+        const uint4 m = *reinterpret_cast<const uint4*>(hi + planes.elems + o);
+        const uint32_t hw[4] = {h.x, h.y, h.z, h.w}, mw[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+        {
+          // a bf16 is the upper half of the fp32 with the same value
+          acc[2 * q] += __uint_as_float(hw[q] << 16) + __uint_as_float(mw[q] << 16);
+          acc[2 * q + 1] += __uint_as_float(hw[q] & 0xffff0000u) + __uint_as_float(mw[q] & 0xffff0000u);
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        part[rg][c8 + q] = acc[q];
+      __syncthreads();
+      if (threadIdx.x < 64)
+      {
+        float s = 0.0f;
+        for (int r = 0; r < 32; ++r)
+          s += part[r][threadIdx.x];
+        bias_apply(L, j0 + threadIdx.x, s, batch, grad_only);
+      }
+    }
+    return;
+  }
   for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x)
   {
     float s = 0.0f;
@@ -816,17 +870,7 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
     else
       for (int b = 0; b < batch; ++b)
         s += g[(size_t)b * n + j];
-    if (grad_only)
-      L.g_b[j] = s;
-    else if (L.opt == DPC_OPT_SGD)
-      L.b[j] += (L.lr / (float)batch) * s;
-    else
-    {
-      float m = L.m_b[j], v = L.v_b[j];
-      L.b[j] = adam_update(L.b[j], -s, m, v, adam_step_size(L.lr, *L.t), -1.0f);
-      L.m_b[j] = m;
-      L.v_b[j] = v;
-    }
+    bias_apply(L, j, s, batch, grad_only);
   }
 }
 

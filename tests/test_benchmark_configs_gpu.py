@@ -9,9 +9,11 @@ live on the host cores of the GPU box (oracle/_ref, the reference's own CPU code
 * on request (DEEPITY_FULL_DEPTH_PARITY=1 and at least 128 GB of host memory) the energies of the
   full 2048-layer stack.
 
-Compared like the benchmark-shaped golden fixtures: the energy of every step, the float64 sum
-and sum of squares of every layer's z, e, W, b and Psi after the last step, and a prediction.
-Bounds: common.TOL (1e-4) for the SGD stack, common.ADAM_TOL (5e-4) for the Adam network.
+Compared: the energy of every step, every layer's z, e, W, b and Psi after the last step and a
+prediction -- element by element for the deep stack (plus the parameter updates themselves,
+relative to the largest update), as float64 sums and sums of squares per tensor for the wide
+network.  Bounds: common.TOL (1e-4) for the SGD stack, common.ADAM_TOL (5e-4) for the Adam
+network, common.DELTA_TOL on the updates.
 The pattern is the reference's own CPU-vs-GPU differential test
 (tests/tDirectKPBatchedGPUVerify.cpp:47-58,127-262), at a 100x tighter bound.
 """
@@ -22,7 +24,7 @@ import time
 import numpy as np
 import pytest
 
-from common import ADAM_TOL, TOL, compare_outputs, run_gpu
+from common import ADAM_TOL, DELTA_TOL, TOL, compare_outputs, initial_parameters, run_gpu
 
 pytestmark = pytest.mark.gpu
 
@@ -56,7 +58,7 @@ def test_wide_fullpcn_at_its_benchmark_shape(built_library):
 
 def _deep_case(depth, steps=2):
     return dict(kind="dkp", sizes=[512] + [512] * depth + [10], batch=1024, T=2, steps=steps,
-                stats_only=True, hyper=dict(act="tanh", **HYPER))
+                hyper=dict(act="tanh", **HYPER))
 
 
 @pytest.fixture(scope="module")
@@ -75,19 +77,21 @@ def deep_reference():
     out = run_reference(case)
     print(f"deep stack: depth {depth} ({per_layer * 1e3:.0f} ms per layer in the calibration run, "
           f"reference took {time.perf_counter() - t0:.1f} s)")
-    return case, out
+    return case, out, initial_parameters(case)
 
 
 def test_deep_stack_default_fp32_scheme(built_library, deep_reference):
-    case, ref = deep_reference
-    worst = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "deep stack 3xBF16")
+    case, ref, init = deep_reference
+    worst = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "deep stack 3xBF16",
+                            init=init, delta_tol=DELTA_TOL)
     print(f"depth {len(case['sizes']) - 2}, 3xBF16 split: worst relative error {worst:.2e}")
 
 
 def test_deep_stack_tf32x3_scheme(built_library, deep_reference, monkeypatch):
-    case, ref = deep_reference
+    case, ref, init = deep_reference
     monkeypatch.setenv("DPC_FP32_SCHEME", "tf32x3")
-    worst = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "deep stack 3xTF32")
+    worst = compare_outputs(ref, run_gpu(case, precision="fp32"), TOL, "deep stack 3xTF32",
+                            init=init, delta_tol=DELTA_TOL)
     print(f"depth {len(case['sizes']) - 2}, 3xTF32 split: worst relative error {worst:.2e}")
 
 
