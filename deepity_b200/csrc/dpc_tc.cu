@@ -44,6 +44,7 @@
 
 #include "dpc_internal.h"
 #include "dpc_math.cuh"
+#include "dpc_tcgen05.cuh"
 
 namespace dpc
 {
@@ -52,13 +53,7 @@ namespace
 constexpr int TBM = 128;  // UMMA M (rows of D per tile)
 constexpr int TBK = 32;   // fp32 elements per pipeline stage along K = one 128-byte swizzle row
 constexpr int UMMA_K = 8; // K of one tcgen05.mma.kind::tf32
-constexpr long long kWaitCyclesDefault = 4000000000LL; // ~2 s at 1.9 GHz
-// The limit of every bounded wait of a launch: abort_flag[0] is the abort flag of the CTA,
-// abort_flag[2..3] hold the limit in clock cycles (written once by thread 0 at start-up).
-__device__ __forceinline__ long long wait_limit(volatile int* abort_flag)
-{
-  return *reinterpret_cast<volatile long long*>(abort_flag + 2);
-}
+using namespace ptx; // mbarriers, TMA, tcgen05, descriptors: dpc_tcgen05.cuh
 
 enum
 {
@@ -135,239 +130,6 @@ struct TcParams
   int fe_only;                  // the fp32 feedback error of the run's layers is not written
 };
 
-// ------------------------------------------------------------------------------ PTX
-__device__ __forceinline__ uint32_t smem_u32(const void* p)
-{
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
-{
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
-{
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
-{
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity)
-{
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-               "selp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok)
-               : "r"(smem_u32(bar)), "r"(parity)
-               : "memory");
-  return ok;
-}
-// Bounded wait: false when the wait was abandoned (own clock ran out, or another role
-// already gave up).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
-{
-  if (mbar_try_wait(bar, parity))
-    return true;
-  const long long t0 = clock64();
-  for (;;)
-  {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity))
-        return true;
-    if (*abort_flag)
-      return false;
-    if (clock64() - t0 > wait_limit(abort_flag))
-    {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0,
-                                            int c1, int c2)
-{
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-               " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
-               "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
-// ---- CTA-pair (cta_group::2) helpers: two CTAs of a cluster share one 256-row tile ---------
-__device__ __forceinline__ uint32_t cluster_ctarank()
-{
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// Address of the same shared-memory location in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank)
-{
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all()
-{
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Arrive on a barrier given by its shared::cluster address (own CTA or the peer).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr)
-{
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr)
-               : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint64_t* bar, uint32_t parity)
-{
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-               "selp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok)
-               : "r"(smem_u32(bar)), "r"(parity)
-               : "memory");
-  return ok;
-}
-// Bounded wait on a barrier that CTAs of the cluster other than this one arrive on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity,
-                                                  volatile int* abort_flag)
-{
-  if (mbar_try_wait_cluster(bar, parity))
-    return true;
-  const long long t0 = clock64();
-  for (;;)
-  {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait_cluster(bar, parity))
-        return true;
-    if (*abort_flag)
-      return false;
-    if (clock64() - t0 > wait_limit(abort_flag))
-    {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
-// TMA load whose completion bytes are counted on a barrier of either CTA of the pair
-// (bar_addr is a shared::cluster address).  Each CTA fetches its own tiles.
-__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map,
-                                                 uint32_t bar_addr, int c0, int c1, int c2)
-{
-  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-               " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
-               "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar_addr)
-{
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar_addr)
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                                 uint32_t idesc, uint32_t accumulate)
-{
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "setp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before()
-{
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after()
-{
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint64_t* bar)
-{
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate)
-{
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "setp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate)
-{
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "setp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                                 uint32_t idesc, uint32_t accumulate)
-{
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "setp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32])
-{
-  uint32_t r[32];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
-               "[%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                 "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-                 "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-                 "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                 "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-                 "=r"(r[31])
-               : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i)
-    v[i] = __uint_as_float(r[i]);
-}
-
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16])
-{
-  uint32_t r[16];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                 "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-                 "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i)
-    v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor (descriptor version 1).  layout: 2 = 128-byte swizzle of
-// 16-byte chunks (K-major tiles), 1 = 128-byte swizzle of 32-byte chunks, the only layout the
-// tensor core accepts for MN-major 32-bit operands.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                              uint32_t layout)
-{
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)layout << 61;
-  return d;
-}
-
 // Chain mode: wait (bounded) until `target` epilogue warps have published one row block of the
 // previous layer's output, then order the TMA (async proxy) reads after that observation.
 __device__ __forceinline__ bool chain_wait(const int* ctr, int target, volatile int* abort_flag)
@@ -399,28 +161,6 @@ __device__ __forceinline__ void trace_stamp(const TcParams& P, int layer, int sl
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     P.trace[layer * 8 + slot] = t;
   }
-}
-
-__device__ __forceinline__ void trace_stamp_raw(unsigned long long* trace, int layer, int slot)
-{
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  trace[layer * 8 + slot] = t;
-}
-
-// 256-bit global accesses: eight consecutive floats, 32-byte aligned (one full sector).
-__device__ __forceinline__ void ld8(const float* p, float* r)
-{
-  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]),
-                 "=f"(r[7])
-               : "l"(p));
-}
-__device__ __forceinline__ void st8(float* p, const float* r)
-{
-  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(r[0]),
-               "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7])
-               : "memory");
 }
 
 // Forward epilogue of one 128 x BN tile for the 32 rows of one warp.  ACT >= 0 fixes the
@@ -779,7 +519,12 @@ struct Cfg
   // at most 8 stages: the barrier block after the ring is sized for that
   static constexpr int STAGES_RAW =
       (196608 - ((PAIR && OP == TC_FWD && !THREE_X) ? 4 * BM * 32 * 4 : 0) - RX_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = B16 ? NR : (STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW));
+  // The K-split sweep on pre-split operands has four k-blocks per layer: with four stages all of a
+  // layer's operands are in flight at once (three stages left the fourth k-block waiting for a
+  // stage to drain: one more load latency on the dependent path of every layer).
+  static constexpr int STAGES = B16 ? NR
+                                : (PRE && KS == 2) ? 4
+                                : (STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW));
   static constexpr int RING_BYTES = B16 ? (NR + NB) * RAWB : STAGES * STAGE_BYTES;
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS =
@@ -1514,386 +1259,6 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
 }
 
 
-// =====================================================================================
-// Sequential forward sweep, cluster-resident variant (3xBF16 from pre-split planes).
-//
-// A cluster of CL = width / 64 CTAs owns 64 batch rows for the WHOLE sweep.  Every CTA keeps
-// a complete copy of the row block's current belief z[l] (64 x width, bf16 hi and mid planes,
-// K-major with the 128-byte swizzle: CL slabs of 64 k-columns per plane) in its own shared
-// memory as the A operand, streams its 64 output columns of W[l] from HBM through a small TMA
-// ring, and accumulates z[l] * W[l]^T over the full K in one go -- the same order as the
-// grouped kernels, so the errors right after the sweep vanish exactly as in the reference.
-// The epilogue turns the 64 x 64 accumulator into z[l+1] (bias, activation), writes it to
-// global memory (fp32 + planes, for the later phases), writes its hi/mid planes into slab
-// `rank` of its own copy, and pushes that slab into the same slab of the other CL-1 CTAs with
-// bulk shared-memory-to-shared-memory copies that complete on the receivers' mbarriers.  No
-// global-memory flag, no L2 round trip and no re-read of z between layers; clusters are
-// independent of each other (rows are), so any number of them may be resident.
-//
-// Barriers per CTA: zfull[j] (slab j of the next input has landed: one arrive + 16 KB of
-// copy bytes per layer), wfull/wempty (weight ring), tfull/tempty (two accumulators), zfree
-// (all CL CTAs have finished the MMAs that read the current input: its slabs, and the local
-// slab the pushes read from, may be overwritten).  Every wait is bounded.
-// =====================================================================================
-struct SweepParams
-{
-  const dpc_layer* layers;
-  int first, count, n_layers, run_first;
-  int flags;
-  __nv_bfloat16* zp; // belief planes of the run (+ the layer above it)
-  long long act_elems;
-  int width;
-  int* error_flag;
-  long long wait_cycles;
-  unsigned long long* trace;
-};
-
-constexpr int SW_ROWS = 64;     // batch rows per cluster = UMMA M
-constexpr int SW_COLS = 64;     // output columns per CTA = UMMA N = k-columns per slab
-constexpr int SW_SLAB = SW_ROWS * 128;  // one plane of one slab: 64 rows of 128 bytes
-constexpr int SW_WSTAGE = 2 * SW_COLS * 128; // hi + mid planes of 64 weight rows x 64 k
-constexpr int SW_EPI_WARPS = 16;
-constexpr int SW_THREADS = (2 + SW_EPI_WARPS) * 32;
-
-template <int CL>
-struct SweepCfg
-{
-  static constexpr int Z_BYTES = 2 * CL * SW_SLAB;
-  static constexpr int WST = (CL == 8) ? 5 : 8; // weight stages that fit beside the beliefs
-  static constexpr int SMEM_BYTES = Z_BYTES + WST * SW_WSTAGE + 1024 /*align*/ + 512 /*barriers*/;
-  static_assert(SMEM_BYTES <= 232448, "more than the 227 KB of shared memory a CTA can have");
-  static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) |
-                                    ((uint32_t)(SW_COLS >> 3) << 17) | ((uint32_t)(SW_ROWS >> 4) << 24);
-};
-
-__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, const void* src,
-                                                  uint32_t bytes, uint32_t bar_cluster_addr)
-{
-  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes "
-               "[%0], [%1], %2, [%3];" ::"r"(dst_cluster_addr),
-               "r"(smem_u32(src)), "r"(bytes), "r"(bar_cluster_addr)
-               : "memory");
-}
-
-template <int CL>
-__global__ void __launch_bounds__(SW_THREADS, 1)
-    pc_sweep_kernel(const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapW,
-                    const SweepParams P)
-{
-  using C = SweepCfg<CL>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~(uintptr_t)1023);
-  uint8_t* zbuf = smem;                 // [plane][slab][64 rows x 128 B]
-  uint8_t* wring = smem + C::Z_BYTES;   // [stage][plane][64 rows x 128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(wring + C::WST * SW_WSTAGE);
-  uint64_t* zfull = bars;               // [8]
-  uint64_t* wfull = bars + 8;           // [8]
-  uint64_t* wempty = bars + 16;         // [8]
-  uint64_t* tfull = bars + 24;          // [2]
-  uint64_t* tempty = bars + 26;         // [2]
-  uint64_t* zfree = bars + 28;          // [1]
-  uint64_t* slabw = bars + 29;          // [1] the epilogue warps have written the local slab
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 30);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 2);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const int m0 = ((int)blockIdx.x / CL) * SW_ROWS; // first batch row of the cluster
-  const int n0 = (int)rank * SW_COLS;              // first output column of this CTA
-  const int r_first = P.first - P.run_first;       // run-relative index of the first layer
-
-  if (threadIdx.x == 0)
-  {
-    for (int j = 0; j < 8; ++j)
-    {
-      mbar_init(&zfull[j], 1);
-      mbar_init(&wfull[j], 1);
-      mbar_init(&wempty[j], 1);
-    }
-    for (int a = 0; a < 2; ++a)
-    {
-      mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], SW_EPI_WARPS);
-    }
-    mbar_init(zfree, CL);
-    mbar_init(slabw, SW_EPI_WARPS);
-    *abort_flag = 0;
-    *reinterpret_cast<volatile long long*>(abort_flag + 2) = P.wait_cycles;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1)
-  {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_holder)),
-                 "r"(128u)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  cluster_sync_all(); // every CTA's barriers exist before anything signals them
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_holder;
-
-  if (warp == 0)
-  {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0)
-    {
-      // the first layer's input: all CL slabs of both planes of this cluster's rows
-      for (int j = 0; j < CL; ++j)
-      {
-        mbar_expect_tx(&zfull[j], 2 * SW_SLAB);
-        tma_load_3d(zbuf + j * SW_SLAB, &mapZ, &zfull[j], 64 * j, m0, 2 * r_first);
-        tma_load_3d(zbuf + (CL + j) * SW_SLAB, &mapZ, &zfull[j], 64 * j, m0, 2 * r_first + 1);
-      }
-      int s = 0;
-      uint32_t phase = 1; // parity to wait for on wempty[s]; flips when the ring wraps
-      bool alive = true;
-      for (int t = 0; t < P.count && alive; ++t)
-      {
-        const int lcoord = r_first + t;
-        for (int j = 0; j < CL; ++j, s = (s + 1 == C::WST ? 0 : s + 1))
-        {
-          if (s == 0 && !(t == 0 && j == 0))
-            phase ^= 1;
-          if (!mbar_wait(&wempty[s], phase, abort_flag))
-          {
-            alive = false;
-            break;
-          }
-          uint8_t* dst = wring + s * SW_WSTAGE;
-          mbar_expect_tx(&wfull[s], SW_WSTAGE);
-          tma_load_3d(dst, &mapW, &wfull[s], 64 * j, n0, 2 * lcoord);
-          tma_load_3d(dst + SW_COLS * 128, &mapW, &wfull[s], 64 * j, n0, 2 * lcoord + 1);
-        }
-      }
-    }
-  }
-  else if (warp == 1)
-  {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0)
-    {
-      int s = 0;
-      uint32_t wphase = 0;
-      bool alive = true;
-      const uint64_t dz_hi = make_desc(smem_u32(zbuf), 16, 1024, 2);
-      const uint64_t dz_mid = make_desc(smem_u32(zbuf) + CL * SW_SLAB, 16, 1024, 2);
-      const uint64_t dw_hi = make_desc(smem_u32(wring), 16, 1024, 2);
-      const uint64_t dw_mid = make_desc(smem_u32(wring) + SW_COLS * 128, 16, 1024, 2);
-      for (int t = 0; t < P.count && alive; ++t)
-      {
-        const int acc = t & 1;
-        if (!mbar_wait(&tempty[acc], ((t >> 1) & 1) ^ 1, abort_flag))
-          break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * SW_COLS;
-        for (int j = 0; j < CL; ++j)
-        {
-          if (!mbar_wait_cluster(&zfull[j], (uint32_t)(t & 1), abort_flag))
-          {
-            alive = false;
-            break;
-          }
-          // this phase of zfull[j] is over: open the next one for the slab the peer will push
-          // (the own slab's phase is closed by the epilogue once it has written it)
-          if (t + 1 < P.count && j != (int)rank)
-            mbar_expect_tx(&zfull[j], 2 * SW_SLAB);
-          if (t < 256 && blockIdx.x == 0 && P.trace && (j == 0 || j == CL - 1))
-            trace_stamp_raw(P.trace, t, j == 0 ? 0 : 1);
-          if (!mbar_wait(&wfull[s], wphase, abort_flag))
-          {
-            alive = false;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t za = dz_hi + (uint64_t)(j * (SW_SLAB >> 4));
-          const uint64_t zm = dz_mid + (uint64_t)(j * (SW_SLAB >> 4));
-          const uint64_t wa = dw_hi + (uint64_t)(s * (SW_WSTAGE >> 4));
-          const uint64_t wm = dw_mid + (uint64_t)(s * (SW_WSTAGE >> 4));
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-          {
-            const uint64_t o = (uint64_t)(ks * 2); // 32 bytes per K = 16 step
-            tc_mma_bf16(d_tmem, za + o, wm + o, C::IDESC, (j | ks) != 0);
-            tc_mma_bf16(d_tmem, zm + o, wa + o, C::IDESC, 1);
-            tc_mma_bf16(d_tmem, za + o, wa + o, C::IDESC, 1);
-          }
-          tc_commit(&wempty[s]);
-          if (++s == C::WST)
-            s = 0, wphase ^= 1;
-        }
-        if (alive)
-          tc_commit(&tfull[acc]);
-      }
-    }
-  }
-  else
-  {
-    // ------------------------------------------------------------ epilogue
-    // Warp e of 16: tensor-memory quarter e & 3 (accumulator rows 16q .. 16q+15 sit in lanes
-    // 0..15 of quarter q when M = 64), columns 16 (e >> 2) .. +15 of the CTA's 64.
-    const int e = warp - 2;
-    const int quarter = warp & 3, grp = e >> 2;
-    const bool active = lane < 16;
-    const bool leader = e == 0 && lane == 0;
-    const bool tracing = leader && blockIdx.x == 0 && P.trace != nullptr;
-    const int row = quarter * 16 + (lane & 15);      // row inside the cluster's block
-    const int col = n0 + grp * 16;                   // first of this lane's 16 columns
-    const size_t o = (size_t)(m0 + row) * P.width + col;
-    // where this lane's 16 values go in slab `rank` of a belief copy: 128-byte rows, 16-byte
-    // chunks swizzled by the row (what the K-major 128-byte-swizzle descriptor expects)
-    uint8_t* slab_hi = zbuf + rank * SW_SLAB + row * 128;
-    const int ch0 = (2 * grp) ^ (row & 7), ch1 = (2 * grp + 1) ^ (row & 7);
-    for (int t = 0; t < P.count; ++t)
-    {
-      const int li = P.first + t;
-      const dpc_layer* Lp = &P.layers[li];
-      const float a = Lp->a;
-      const int act = Lp->act, lflags = Lp->flags;
-      float* preact = Lp->preact;
-      float* mu_out = Lp->mu;
-      const float* zin = Lp->z;
-      float* up_z = Lp[1].z;
-      float bb[16];
-      ld8(Lp->b + col, &bb[0]);
-      ld8(Lp->b + col + 8, &bb[8]);
-      const int acc = t & 1;
-      if (!mbar_wait(&tfull[acc], (t >> 1) & 1, abort_flag))
-        break;
-      tc_fence_after();
-      // this CTA's MMAs of layer t are complete: tell every CTA of the cluster (zfree)
-      if (leader)
-      {
-        if (tracing && t < 256)
-          trace_stamp_raw(P.trace, t, 2);
-#pragma unroll
-        for (int p = 0; p < CL; ++p)
-          mbar_arrive_cluster(mapa_u32(smem_u32(zfree), (uint32_t)p));
-      }
-      float v[16];
-      tc_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * SW_COLS + grp * 16, v);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(&tempty[acc]);
-      const bool no_mu = (P.flags & DPC_FWD_NO_MU) && !((P.flags & (1 << 10)) && t == 0);
-      float mu[16];
-#pragma unroll
-      for (int k = 0; k < 16; ++k)
-      {
-        v[k] = a * v[k] + bb[k];
-        mu[k] = act_fwd(act, v[k]);
-      }
-      if ((lflags & DPC_LAYER_RESIDUAL) && active)
-      {
-        float zz[16];
-        ld8(zin + o, &zz[0]);
-        ld8(zin + o + 8, &zz[8]);
-#pragma unroll
-        for (int k = 0; k < 16; ++k)
-          mu[k] += zz[k];
-      }
-      uint4 h0, m0v, h1, m1v;
-      split8(make_float4(mu[0], mu[1], mu[2], mu[3]), make_float4(mu[4], mu[5], mu[6], mu[7]), h0, m0v);
-      split8(make_float4(mu[8], mu[9], mu[10], mu[11]), make_float4(mu[12], mu[13], mu[14], mu[15]), h1,
-             m1v);
-      bool ok = true;
-      if (t + 1 < P.count)
-      {
-        // The next layer's input goes out first (it is what the whole cluster waits for).
-        // Nobody may still read the current input: peers the slabs this CTA pushed a layer ago,
-        // this CTA's outgoing copies the local slab they were read from.
-        if (lane == 0)
-          ok = mbar_wait_cluster(zfree, (uint32_t)(t & 1), abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (ok)
-        {
-          if (active)
-          {
-            *reinterpret_cast<uint4*>(slab_hi + (ch0 << 4)) = h0;
-            *reinterpret_cast<uint4*>(slab_hi + (ch1 << 4)) = h1;
-            *reinterpret_cast<uint4*>(slab_hi + CL * SW_SLAB + (ch0 << 4)) = m0v;
-            *reinterpret_cast<uint4*>(slab_hi + CL * SW_SLAB + (ch1 << 4)) = m1v;
-          }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0)
-            mbar_arrive(slabw); // this warp's part of the slab is written
-          if (leader)
-          {
-            // all 16 epilogue warps have written: push the slab to the peers
-            if (mbar_wait(slabw, (uint32_t)(t & 1), abort_flag))
-            {
-              const uint32_t src_hi = smem_u32(zbuf + rank * SW_SLAB);
-#pragma unroll
-              for (int p = 0; p < CL; ++p)
-              {
-                if (p == (int)rank)
-                  continue;
-                const uint32_t dst = mapa_u32(src_hi, (uint32_t)p);
-                const uint32_t bar = mapa_u32(smem_u32(&zfull[rank]), (uint32_t)p);
-                bulk_copy_to_peer(dst, zbuf + rank * SW_SLAB, SW_SLAB, bar);
-                bulk_copy_to_peer(dst + CL * SW_SLAB, zbuf + (CL + rank) * SW_SLAB, SW_SLAB, bar);
-              }
-              mbar_arrive(&zfull[rank]); // the own copy of the slab is in place
-              if (tracing && t < 256)
-                trace_stamp_raw(P.trace, t, 4);
-            }
-          }
-        }
-      }
-      // the copies for the later phases of the step (global memory, fp32 and planes)
-      if (active)
-      {
-        if (!(no_mu && (P.flags & DPC_FWD_NO_PREACT)))
-        {
-          st8(preact + o, &v[0]);
-          st8(preact + o + 8, &v[8]);
-        }
-        if (!no_mu)
-        {
-          st8(mu_out + o, &mu[0]);
-          st8(mu_out + o + 8, &mu[8]);
-        }
-        st8(up_z + o, &mu[0]);
-        st8(up_z + o + 8, &mu[8]);
-        __nv_bfloat16* hi = P.zp + 2 * (long long)(li + 1 - P.run_first) * P.act_elems + o;
-        *reinterpret_cast<uint4*>(hi) = h0;
-        *reinterpret_cast<uint4*>(hi + 8) = h1;
-        *reinterpret_cast<uint4*>(hi + P.act_elems) = m0v;
-        *reinterpret_cast<uint4*>(hi + P.act_elems + 8) = m1v;
-      }
-      if (tracing && t < 256)
-        trace_stamp_raw(P.trace, t, 3);
-      if (!ok)
-        break;
-    }
-  }
-
-  // ------------------------------------------------------------------ teardown
-  if (*abort_flag)
-  {
-    // copies of peers may still be on their way into this CTA's memory: give them time
-    const long long t0 = clock64();
-    while (clock64() - t0 < 4000000LL)
-    {
-    }
-  }
-  tc_fence_before();
-  cluster_sync_all(); // no CTA leaves while a peer may still touch its shared memory
-  if (threadIdx.x == 0 && *abort_flag)
-    atomicExch(P.error_flag, 1);
-  if (warp == 1)
-  {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u)
-                 : "memory");
-  }
-}
-
 // ------------------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -2439,51 +1804,6 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
   return rc;
 }
 
-template <int CL>
-static int launch_cluster_sweep(dpc_plan* p, TcState* st, int first, int count, int flags)
-{
-  using C = SweepCfg<CL>;
-  static bool configured = false;
-  auto kern = pc_sweep_kernel<CL>;
-  if (!configured)
-  {
-    if (C::SMEM_BYTES > st->max_smem)
-      return 1;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::SMEM_BYTES);
-    if (e != cudaSuccess)
-      return cuda_fail(e, "cudaFuncSetAttribute(sweep kernel)");
-    configured = true;
-  }
-  SweepParams P;
-  P.layers = p->d;
-  P.first = first, P.count = count, P.n_layers = p->n, P.run_first = p->run.first;
-  P.flags = flags;
-  P.zp = st->zp;
-  P.act_elems = (long long)p->batch * p->run.width;
-  P.width = p->run.width;
-  P.error_flag = st->error_flag;
-  P.wait_cycles = st->wait_cycles;
-  P.trace = st->trace;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)((p->batch / SW_ROWS) * CL));
-  cfg.blockDim = dim3(SW_THREADS);
-  cfg.dynamicSmemBytes = C::SMEM_BYTES;
-  cfg.stream = p->ctx->stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = CL;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, st->zp_km64, st->wp_km64, P);
-  p->ctx->launches += 1;
-  if (e != cudaSuccess)
-    return cuda_fail(e, "cluster sweep kernel launch");
-  return DPC_OK;
-}
-
 // The sequential forward sweep over layers [first, first+count) of the run as ONE persistent
 // launch: 128 x 64 output tiles, one CTA per tile, every CTA walking all layers and
 // synchronising per row block through counters in global memory (no grid-wide barrier: a
@@ -2495,23 +1815,6 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   if (!st || !st->ok || !range_in_run(p, first, count) || count < 2)
     return 1;
   const int H = p->run.width, B = p->batch;
-  // Pre-split operands and a width of 256 or 512: clusters of width/64 CTAs that keep their 64
-  // batch rows resident in shared memory for the whole sweep (no global flags, any batch size).
-  if (p->ctx->precision != DPC_PRECISION_TF32 && planes_on(p, st) && (H == 256 || H == 512) &&
-      B % SW_ROWS == 0 && !getenv("DPC_DISABLE_CLUSTER_SWEEP"))
-  {
-    const int r0 = first - p->run.first;
-    int rc;
-    if ((rc = planes_need(p, st, PL_Z, r0, r0 + 1)) != DPC_OK ||
-        (rc = planes_need(p, st, PL_W, r0, r0 + count)) != DPC_OK)
-      return rc;
-    rc = H == 512 ? launch_cluster_sweep<8>(p, st, first, count, flags)
-                  : launch_cluster_sweep<4>(p, st, first, count, flags);
-    if (rc == DPC_OK)
-      planes_mark(st, PL_Z, r0 + 1, r0 + count + 1, 0);
-    if (rc <= 0)
-      return rc;
-  }
   // Narrow 128 x 32 tiles: B/128 * H/32 CTAs (128 for the 1024 x 512 layers of the deep-stack
   // benchmark) keep the epilogue and the publish step on the dependent path short.  (Tiles of
   // 64 rows were measured too: a tcgen05.mma costs about the same whatever M and N are, so
@@ -2531,7 +1834,7 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   P.chain_counters = st->chain_counters;
   P.chain_target = (H / BNC) * 8 + st->chain_target_bias; // column tiles x epilogue warps
   P.trace = st->trace;
-  cudaError_t e = cudaMemsetAsync(st->chain_counters, 0, sizeof(int) * (size_t)count * (B / TBM),
+  cudaError_t e = cudaMemsetAsync(st->chain_counters, 0, sizeof(int) * (size_t)count * (B / 64),
                                   p->ctx->stream);
   if (e != cudaSuccess)
     return cuda_fail(e, "cudaMemsetAsync(chain counters)");

@@ -257,15 +257,19 @@ class ShardedDKPPCN:
 
     # ---- communication helpers -------------------------------------------------------------
     def _exchange(self, send=None, recv=None):
-        """send/recv: (tensor, peer rank) or None; both are posted before either is waited on."""
+        """send/recv: (tensor, peer rank) or None.  A send and a receive of the same phase go
+        out as ONE batched point-to-point group (a single NCCL group call: neither waits for
+        the other, and the backend does not serialise them)."""
         ops = []
+        if send is not None:
+            ops.append(self.dist.P2POp(self.dist.isend, send[0], send[1], group=self.group))
+        if recv is not None:
+            ops.append(self.dist.P2POp(self.dist.irecv, recv[0], recv[1], group=self.group))
+        if not ops:
+            return
         with self.eng.comm_stream():
-            if send is not None:
-                ops.append(self.dist.isend(send[0], send[1], group=self.group))
-            if recv is not None:
-                ops.append(self.dist.irecv(recv[0], recv[1], group=self.group))
-            for op in ops:
-                op.wait()
+            for work in self.dist.batch_isend_irecv(ops):
+                work.wait()
 
     def _broadcast_terminal_error(self):
         with self.eng.comm_stream():

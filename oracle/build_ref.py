@@ -74,6 +74,9 @@ def build(verbose: bool = True) -> str | None:
     os.makedirs(OUT_DIR, exist_ok=True)
     cmd = [
         "g++", "-std=c++20", "-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared",
+        # the host as a CUDA-enabled build of the reference compiles it: DEVICE_GPU networks bind
+        # device arenas and reach their backend through the plugin loader (no CUDA header needed)
+        "-DDEEPITY_USE_CUDA",
         "-I", os.path.join(HERE, "shim"),
         "-I", os.path.join(root, "include"),
         "-I", os.path.join(root, "src", "backend"),

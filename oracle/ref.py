@@ -32,6 +32,8 @@ def lib():
         f32p = ctypes.POINTER(ctypes.c_float)
         L.ref_create.restype = ctypes.c_void_p
         L.ref_create.argtypes = [ctypes.c_int, ctypes.c_int]
+        L.ref_create_on_gpu.restype = ctypes.c_void_p
+        L.ref_create_on_gpu.argtypes = [ctypes.c_int, ctypes.c_int]
         L.ref_destroy.argtypes = [ctypes.c_void_p]
         L.ref_add_layer.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_float, ctypes.c_float, ctypes.c_float,
@@ -78,10 +80,16 @@ class RefNet:
     """
 
     def __init__(self, kind: str, sizes, batch: int, *, lr=1e-3, ir=0.1, fl=1e-3, lmbda=0.0,
-                 act="tanh", last_act=None, options=None):
+                 act="tanh", last_act=None, options=None, device="cpu"):
         self.kind, self.sizes, self.batch = kind, list(sizes), batch
         L = lib()
-        self.h = L.ref_create(KIND[kind], batch)
+        if device == "cpu":
+            self.h = L.ref_create(KIND[kind], batch)
+        else:
+            # DEVICE_GPU: the reference's loader looks for libDeepityCUDA.so beside this library
+            self.h = L.ref_create_on_gpu(KIND[kind], batch)
+            if not self.h:
+                raise RuntimeError("the reference could not load a GPU backend plugin")
         ts = self.sizes[-1]
         n_w = len(self.sizes) - 1
         for i in range(n_w):

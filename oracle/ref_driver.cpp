@@ -10,6 +10,7 @@
 // Tensor names: "z" "e" "mu" (states), "W" "b" "Psi" (parameters), and the
 // optimizer-state names of Layer::GetOptimizerStateDict ("weight.m" ...).
 #include <cstdint>
+#include <cstdio>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -39,6 +40,7 @@ struct Net
 {
   int kind;
   int batch;
+  int device = 0; // 0: the reference's CPU backend, 1: whatever plugin its loader finds (GPU)
   std::unique_ptr<SimplePCNetwork> simple;
   std::unique_ptr<DirectKPPCNetwork> dkp;
   std::unique_ptr<FullPCNetwork> full;
@@ -121,13 +123,21 @@ View FindTensor(Net* n, int layer, const char* name)
     return ParamView(n->full->GetLayers()[layer].get(), nm);
   }
 }
+IComputeBackend* BackendOf(Net* n)
+{
+  if (n->kind == KIND_SIMPLE)
+    return n->simple->GetLayers().front()->GetBackend();
+  if (n->kind == KIND_DKP)
+    return n->dkp->GetLayers().front()->GetBackend();
+  return n->full->GetLayers().front()->GetBackend();
+}
 } // namespace
 
 extern "C"
 {
 void* ref_create(int kind, int batch)
 {
-  auto* n = new Net{kind, batch, nullptr, nullptr, nullptr};
+  auto* n = new Net{kind, batch, 0, nullptr, nullptr, nullptr};
   if (kind == KIND_SIMPLE)
     n->simple = std::make_unique<SimplePCNetwork>(batch);
   else if (kind == KIND_DKP)
@@ -135,6 +145,29 @@ void* ref_create(int kind, int batch)
   else
     n->full = std::make_unique<FullPCNetwork>(batch);
   return n;
+}
+
+// The same networks on DEVICE_GPU: the reference's loader (src/backend/CUDAPluginLoader.cpp:52-107)
+// then dlopens libDeepityCUDA.so from the directory of this library.  NULL when that fails
+// (no plugin there, no device).
+void* ref_create_on_gpu(int kind, int batch)
+{
+  try
+  {
+    auto* n = new Net{kind, batch, 1, nullptr, nullptr, nullptr};
+    if (kind == KIND_SIMPLE)
+      n->simple = std::make_unique<SimplePCNetwork>(batch, DeviceType::DEVICE_GPU);
+    else if (kind == KIND_DKP)
+      n->dkp = std::make_unique<DirectKPPCNetwork>(batch, DeviceType::DEVICE_GPU);
+    else
+      n->full = std::make_unique<FullPCNetwork>(batch, DeviceType::DEVICE_GPU);
+    return n;
+  }
+  catch (const std::exception& e)
+  {
+    fprintf(stderr, "ref_create_on_gpu: %s\n", e.what());
+    return nullptr;
+  }
 }
 
 void ref_destroy(void* h)
@@ -258,19 +291,38 @@ int64_t ref_tensor_size(void* h, int layer, const char* name)
 
 int ref_get_tensor(void* h, int layer, const char* name, float* out, int64_t count)
 {
-  View v = FindTensor(static_cast<Net*>(h), layer, name);
+  auto* n = static_cast<Net*>(h);
+  View v = FindTensor(n, layer, name);
   if (!v.p || (int64_t)(v.rows * v.cols) != count)
     return -1;
+  std::vector<float> staged;
+  const float* src = v.p;
+  if (n->device)
+  {
+    // the tensor lives in device memory: stage it through the network's backend
+    staged.resize(v.rows * v.stride);
+    BackendOf(n)->CopyToHost(staged.data(), v.p, staged.size());
+    src = staged.data();
+  }
   for (size_t r = 0; r < v.rows; ++r)
-    std::memcpy(out + r * v.cols, v.p + r * v.stride, v.cols * sizeof(float));
+    std::memcpy(out + r * v.cols, src + r * v.stride, v.cols * sizeof(float));
   return 0;
 }
 
 int ref_set_tensor(void* h, int layer, const char* name, const float* in, int64_t count)
 {
-  View v = FindTensor(static_cast<Net*>(h), layer, name);
+  auto* n = static_cast<Net*>(h);
+  View v = FindTensor(n, layer, name);
   if (!v.p || (int64_t)(v.rows * v.cols) != count)
     return -1;
+  if (n->device)
+  {
+    std::vector<float> staged(v.rows * v.stride, 0.0f);
+    for (size_t r = 0; r < v.rows; ++r)
+      std::memcpy(staged.data() + r * v.stride, in + r * v.cols, v.cols * sizeof(float));
+    BackendOf(n)->CopyFromHost(v.p, staged.data(), staged.size());
+    return 0;
+  }
   for (size_t r = 0; r < v.rows; ++r)
     std::memcpy(v.p + r * v.stride, in + r * v.cols, v.cols * sizeof(float));
   return 0;
