@@ -949,8 +949,8 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
       return rc;
     if (any_psi)
     {
-      dim3 gp(std::max(1, cdiv(max_size, 128)), c);
-      psi_update_kernel<<<gp, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, 0);
+      dim3 gp(std::max(1, cdiv(max_size, 64)), c);
+      psi_update_kernel<<<gp, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, 0);
       if ((rc = check_launch(p->ctx, "psi_update kernel")) != DPC_OK)
         return rc;
     }
@@ -1029,8 +1029,8 @@ int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
       return rc;
     if (any_psi)
     {
-      dim3 gp(std::max(1, cdiv(max_size, 128)), c);
-      psi_update_kernel<<<gp, 128, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, 1);
+      dim3 gp(std::max(1, cdiv(max_size, 64)), c);
+      psi_update_kernel<<<gp, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, 1);
       if ((rc = check_launch(p->ctx, "psi gradient kernel")) != DPC_OK)
         return rc;
     }

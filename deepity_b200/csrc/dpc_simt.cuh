@@ -874,10 +874,14 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
   }
 }
 
-// Feedback-weight update Psi[l] (+)= (fl*a/B) z[l]^T e_T, one thread per row of Psi with the
-// terminal columns in registers (chunks of 16).
-__global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
-                                  int batch, const float* __restrict__ eT, int grad_only)
+// Feedback-weight update Psi[l] (+)= (fl*a/B) z[l]^T e_T.  A block of 256 threads owns 64 rows of
+// Psi (= 64 columns of z): thread (g, i) adds up the batch rows b = g, g+4, ... for column i with
+// the terminal columns in registers (chunks of 16), the four row groups are then summed in a
+// fixed order through shared memory.  The terminal errors of PSI_ROWS batch rows at a time go
+// through shared memory (zero padded to 16 columns).
+__global__ void __launch_bounds__(256)
+    psi_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
+                      const float* __restrict__ eT, int grad_only)
 {
   const int li = first + blockIdx.y;
   if (li + 1 >= n_layers)
@@ -888,11 +892,13 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
   const int TS = L.terminal_size, s = L.size;
   const bool full_kind = (L.flags & DPC_LAYER_FULLPC_PSI) != 0;
   const float rate = full_kind ? L.fl * L.a : L.fl;
-  constexpr int PSI_ROWS = 64;
+  constexpr int PSI_ROWS = 64, GROUPS = 4, COLS = 64;
   __shared__ __align__(16) float es[PSI_ROWS][16];
-  for (int i0 = blockIdx.x * blockDim.x; i0 < s; i0 += gridDim.x * blockDim.x)
+  __shared__ float part[GROUPS][COLS][17];
+  const int g = threadIdx.x >> 6, ci = threadIdx.x & 63;
+  for (int i0 = blockIdx.x * COLS; i0 < s; i0 += gridDim.x * COLS)
   {
-    const int i = i0 + threadIdx.x;
+    const int i = i0 + ci;
     for (int kc = 0; kc < TS; kc += 16)
     {
       float acc[16];
@@ -900,8 +906,6 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
       for (int k = 0; k < 16; ++k)
         acc[k] = 0.0f;
       const int kn = min(16, TS - kc);
-      // The terminal errors of PSI_ROWS batch rows at a time go through shared memory (zero
-      // padded to 16 columns), so each thread issues one global load per row.
       for (int b0 = 0; b0 < batch; b0 += PSI_ROWS)
       {
         __syncthreads();
@@ -914,8 +918,8 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
         if (i < s)
         {
           const int rows = min(PSI_ROWS, batch - b0);
-#pragma unroll 8
-          for (int r = 0; r < rows; ++r)
+#pragma unroll 4
+          for (int r = g; r < rows; r += GROUPS)
           {
             const float zv = L.z[(size_t)(b0 + r) * s + i];
 #pragma unroll
@@ -930,49 +934,48 @@ __global__ void psi_update_kernel(const dpc_layer* __restrict__ layers, int firs
           }
         }
       }
-      if (i >= s)
-        continue;
-      float* prow = L.Psi + (size_t)i * L.psi_stride + kc;
-      if (grad_only)
-      {
-        float* grow = L.g_Psi + (size_t)i * L.psi_stride + kc;
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
-          if (k < kn)
-            grow[k] = acc[k];
-      }
-      else if (L.opt_psi == DPC_OPT_SGD)
+      for (int k = 0; k < 16; ++k)
+        part[g][ci][k] = acc[k];
+      __syncthreads();
+      // thread t < 64 * 4: column t / 4, terminal columns 4 (t % 4) .. +3
+      const int rc = threadIdx.x >> 2, k0 = (threadIdx.x & 3) * 4, row = i0 + rc;
+      if (row < s)
       {
-        const float decay = (!full_kind && L.psi_decay > 0.0f) ? 1.0f - L.psi_decay : 1.0f;
-        const float alpha = rate / (float)batch;
+        float* prow = L.Psi + (size_t)row * L.psi_stride + kc;
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
-          if (k < kn)
+        for (int q = 0; q < 4; ++q)
+        {
+          const int k = k0 + q;
+          if (k >= kn)
+            continue;
+          const float sum = ((part[0][rc][k] + part[1][rc][k]) + part[2][rc][k]) + part[3][rc][k];
+          if (grad_only)
+            L.g_Psi[(size_t)row * L.psi_stride + kc + k] = sum;
+          else if (L.opt_psi == DPC_OPT_SGD)
           {
+            const float decay = (!full_kind && L.psi_decay > 0.0f) ? 1.0f - L.psi_decay : 1.0f;
             float p = prow[k];
             if (decay != 1.0f)
               p *= decay;
-            prow[k] = fmaf(alpha, acc[k], p);
+            prow[k] = fmaf(rate / (float)batch, sum, p);
           }
-      }
-      else
-      {
-        const float step = adam_step_size(rate, *L.t_Psi);
-        float lr_wd = -1.0f;
-        if (L.opt_psi == DPC_OPT_ADAMW)
-          lr_wd = rate * ((!full_kind && L.psi_decay >= 0.0f) ? L.psi_decay : L.lmbda);
-        float* mrow = L.m_Psi + (size_t)i * L.psi_stride + kc;
-        float* vrow = L.v_Psi + (size_t)i * L.psi_stride + kc;
-#pragma unroll
-        for (int k = 0; k < 16; ++k)
-          if (k < kn)
+          else
           {
+            const float step = adam_step_size(rate, *L.t_Psi);
+            float lr_wd = -1.0f;
+            if (L.opt_psi == DPC_OPT_ADAMW)
+              lr_wd = rate * ((!full_kind && L.psi_decay >= 0.0f) ? L.psi_decay : L.lmbda);
+            float* mrow = L.m_Psi + (size_t)row * L.psi_stride + kc;
+            float* vrow = L.v_Psi + (size_t)row * L.psi_stride + kc;
             float m = mrow[k], v = vrow[k];
-            prow[k] = adam_update(prow[k], -acc[k], m, v, step, lr_wd);
+            prow[k] = adam_update(prow[k], -sum, m, v, step, lr_wd);
             mrow[k] = m;
             vrow[k] = v;
           }
+        }
       }
+      __syncthreads();
     }
   }
 }

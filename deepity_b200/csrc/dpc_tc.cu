@@ -83,6 +83,8 @@ struct TcState
   // the planes lag behind the fp32 tensor (1 = must be re-split before a kernel reads them).
   __nv_bfloat16 *zp = nullptr, *fep = nullptr, *wp = nullptr;
   CUtensorMap zp_km, zp_km64, zp_mn, fep_km, fep_mn, wp_km128, wp_km64, wp_mn;
+  CUtensorMap e_st, fep_st; // bulk-store maps: errors (fp32) and feedback-error planes (bf16)
+  bool store_maps = false;
   std::vector<uint8_t> dirty[3];
   bool planes = false;
   // The run's feedback errors exist only as planes: every reader of them is a kernel that takes
@@ -128,6 +130,7 @@ struct TcParams
   long long act_elems, w_elems; // elements per plane: batch x width, width x width
   long long wait_cycles;        // limit of every bounded wait of this launch
   int fe_only;                  // the fp32 feedback error of the run's layers is not written
+  int tstore;                   // the store maps of the launch are valid (staged epilogue outputs)
 };
 
 // Chain mode: wait (bounded) until `target` epilogue warps have published one row block of the
@@ -302,6 +305,13 @@ struct InStage
   int nbufs;     // power of two
   volatile int* abort_flag;
   const uint8_t* rx; // K-split sweep: the peer's partial sums for this CTA's 32 columns
+  // Output staging (pair-mode forward on pre-split operands): this warp's two 4 KB buffers
+  // ([e: 32 rows x 64 B][fe hi: 32 x 32 B][fe mid: 32 x 32 B]), the running count of chunks it
+  // has staged, the store maps and the coordinates of its 32 rows.  out == NULL: direct stores.
+  uint8_t* out;
+  uint32_t* out_seq;
+  const CUtensorMap *map_e, *map_fe;
+  int out_row0, layer_e, layer_fe;
 };
 
 template <int ACT, int BN, int GROUPS, bool PREFETCH, bool STAGED = false, bool KSUM = false>
@@ -334,6 +344,12 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
   const bool staged = STAGED && P.stage_in != 0 && up_src_all != nullptr;
   if (staged)
     up_src = nullptr; // the operand comes from shared memory, box by box
+  // Errors and feedback-error planes leave through shared memory and bulk tensor stores (whole
+  // 64- and 32-byte row segments per store instead of one 32-byte sector per lane and
+  // instruction): only in the passes that write nothing else.
+  const bool tstore = STAGED && in->out != nullptr && !store && !do_copy && (do_err || do_fe) &&
+                      (!do_fe || (P.fe_only && L.fe_hi != nullptr));
+  const int lane = threadIdx.x & 31;
   if (up_src)
   {
 #pragma unroll
@@ -364,6 +380,15 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
       __syncwarp();
       if ((threadIdx.x & 31) == 0)
         mbar_arrive(&in->empty[b]);
+    }
+    uint8_t* obuf = nullptr;
+    if (STAGED && tstore)
+    {
+      // the buffer staged two chunks ago must have been read by its stores
+      obuf = in->out + ((*in->out_seq) & 1u) * 4096u;
+      if (lane == 0)
+        bulk_wait_read<1>();
+      __syncwarp();
     }
     tc_ld16(taddr + c * CW, v);
     if (KSUM)
@@ -435,7 +460,16 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
           e[q] = (do_copy || !active) ? 0.0f : up[k + q] - mu[q];
           esum += e[q] * e[q];
         }
-        if (active)
+        if (STAGED && tstore)
+        {
+          // 64-byte rows, 16-byte chunks xor-ed with (row >> 1) & 3: the 64-byte swizzle
+          const int q = k >> 2;
+          *reinterpret_cast<float4*>(obuf + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
+              make_float4(e[0], e[1], e[2], e[3]);
+          *reinterpret_cast<float4*>(obuf + lane * 64 + (((q + 1) ^ ((lane >> 1) & 3)) << 4)) =
+              make_float4(e[4], e[5], e[6], e[7]);
+        }
+        else if (active)
           st8(up_e + o + k, e);
       }
       else if (do_fe)
@@ -449,7 +483,16 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
 #pragma unroll
         for (int q = 0; q < 8; ++q)
           e[q] *= d[q];
-        if (active)
+        if (STAGED && tstore)
+        {
+          // 32-byte rows, 16-byte chunks xor-ed with (row >> 2) & 1: the 32-byte swizzle
+          uint4 h, mm;
+          split8(make_float4(e[0], e[1], e[2], e[3]), make_float4(e[4], e[5], e[6], e[7]), h, mm);
+          const int off = lane * 32 + ((((k >> 3) & 1) ^ ((lane >> 2) & 1)) << 4);
+          *reinterpret_cast<uint4*>(obuf + 2048 + off) = h;
+          *reinterpret_cast<uint4*>(obuf + 3072 + off) = mm;
+        }
+        else if (active)
         {
           if (!P.fe_only)
             st8(L.fe + o + k, e);
@@ -459,6 +502,24 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
       }
       if (tl >= 0 && c == grp && k == 0 && threadIdx.x == 64)
         trace_stamp(P, tl, 6);
+    }
+    if (STAGED && tstore)
+    {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0)
+      {
+        const int col = n0 + c * CW;
+        if (do_err)
+          tma_store_3d(in->map_e, obuf, col, in->out_row0, in->layer_e);
+        if (do_fe)
+        {
+          tma_store_3d(in->map_fe, obuf + 2048, col, in->out_row0, 2 * in->layer_fe);
+          tma_store_3d(in->map_fe, obuf + 3072, col, in->out_row0, 2 * in->layer_fe + 1);
+        }
+        bulk_commit();
+      }
+      *in->out_seq += 1;
     }
     if (up_src && c + GROUPS < BN / CW)
     {
@@ -522,7 +583,9 @@ struct Cfg
   // The K-split sweep on pre-split operands has four k-blocks per layer: with four stages all of a
   // layer's operands are in flight at once (three stages left the fourth k-block waiting for a
   // stage to drain: one more load latency on the dependent path of every layer).
+  static constexpr bool TSTORE = PRE && PAIR && OP == TC_FWD; // staged epilogue outputs
   static constexpr int STAGES = B16 ? NR
+                                : TSTORE ? 2
                                 : (PRE && KS == 2) ? 4
                                 : (STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW));
   static constexpr int RING_BYTES = B16 ? (NR + NB) * RAWB : STAGES * STAGE_BYTES;
@@ -538,8 +601,10 @@ struct Cfg
   static constexpr bool STAGE_IN = PAIR && OP == TC_FWD;
   static constexpr int IN_BYTES = BM * 32 * 4;
   static constexpr int IN_BUFS = STAGE_IN ? (THREE_X ? 2 : 4) : 0;
+  // two 4 KB output buffers per epilogue warp
+  static constexpr int OUT_BYTES = TSTORE ? EPI_WARPS * 2 * 4096 : 0;
   static constexpr int SMEM_BYTES =
-      RING_BYTES + IN_BUFS * IN_BYTES + RX_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+      RING_BYTES + IN_BUFS * IN_BYTES + OUT_BYTES + RX_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static_assert(SMEM_BYTES <= 232448, "more than the 227 KB of shared memory a CTA can have");
   static constexpr uint32_t FMT = BF ? 1u : 2u; // operand format: 1 = BF16, 2 = TF32
   static constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1u : 0u) << 15) |
@@ -553,7 +618,8 @@ struct Cfg
 template <int OP, int BN, int THREE_X, int BM = 128, bool PAIR = false, int KS = 1>
 __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1)
     pc_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 const __grid_constant__ CUtensorMap mapU, const TcParams P)
+                 const __grid_constant__ CUtensorMap mapU, const __grid_constant__ CUtensorMap mapSE,
+                 const __grid_constant__ CUtensorMap mapSF, const TcParams P)
 {
   using C = Cfg<OP, BN, THREE_X, BM, PAIR, KS>;
   extern __shared__ uint8_t smem_raw[];
@@ -561,7 +627,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
                                              ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
   uint8_t* in_base = smem + C::RING_BYTES; // staged operand of the layer above
-  uint8_t* rx_base = in_base + C::IN_BUFS * C::IN_BYTES; // K-split sweep: peer's partial tile
+  uint8_t* out_base = in_base + C::IN_BUFS * C::IN_BYTES; // staged epilogue outputs
+  uint8_t* rx_base = out_base + C::OUT_BYTES; // K-split sweep: peer's partial tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(rx_base + C::RX_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + C::STAGES;
@@ -686,7 +753,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           // (MN-major); pre-split operands are the "hi" and "mid" planes (layer coordinates 2l and
           // 2l+1), each one box of 64 k-columns (K-major) or slabs of 64 columns (MN-major).
           auto load_operand = [&](uint8_t* dst, const CUtensorMap* map, bool mn, int rows, int r0,
-                                  int bytes, uint64_t* bar_local, uint32_t bar_pair, bool pair) {
+                                  int bytes, uint64_t* bar_local, uint32_t bar_pair, bool pair,
+                                  int kk) {
             auto one = [&](uint8_t* d, int c0, int c1, int c2) {
               if (pair)
                 tma_load_3d_pair(d, map, bar_pair, c0, c1, c2);
@@ -699,17 +767,17 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
               {
                 uint8_t* d = dst + pl * (bytes / 2);
                 if (!mn)
-                  one(d, k0, r0, 2 * lcoord + pl);
+                  one(d, kk, r0, 2 * lcoord + pl);
                 else
                   for (int i = 0; i < rows / 64; ++i)
-                    one(d + i * (C::KB * 128), r0 + 64 * i, k0, 2 * lcoord + pl);
+                    one(d + i * (C::KB * 128), r0 + 64 * i, kk, 2 * lcoord + pl);
               }
             }
             else if (!mn)
-              one(dst, k0, r0, lcoord);
+              one(dst, kk, r0, lcoord);
             else
               for (int i = 0; i < rows / 32; ++i)
-                one(dst + i * (TBK * 128), r0 + 32 * i, k0, lcoord);
+                one(dst + i * (TBK * 128), r0 + 32 * i, kk, lcoord);
           };
           if (PAIR && !C::SPLITW)
           {
@@ -718,12 +786,12 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
             if (leader)
               mbar_expect_tx(&full[s], 2 * (C::A_BYTES + C::B_BYTES));
             const uint32_t bar = lead_full + (uint32_t)(s * 8);
-            load_operand(b_dst, &mapB, C::B_MN, C::BN_LOCAL, n0, C::B_BYTES, nullptr, bar, true);
-            load_operand(a_dst, &mapA, C::A_MN, BM, m0, C::A_BYTES, nullptr, bar, true);
+            load_operand(b_dst, &mapB, C::B_MN, C::BN_LOCAL, n0, C::B_BYTES, nullptr, bar, true, k0);
+            load_operand(a_dst, &mapA, C::A_MN, BM, m0, C::A_BYTES, nullptr, bar, true, k0);
             continue;
           }
           mbar_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
-          load_operand(b_dst, &mapB, C::B_MN, C::BN_LOCAL, n0, C::B_BYTES, &full[s], 0, false);
+          load_operand(b_dst, &mapB, C::B_MN, C::BN_LOCAL, n0, C::B_BYTES, &full[s], 0, false, k0);
           if (P.chain && kb == 0 && t > 0)
           {
             // The rows of this layer's input are the previous layer's output: wait until every
@@ -734,7 +802,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
               alive = false; // the A copy below still runs so the stage's byte count completes
             trace_stamp(P, t, 0);
           }
-          load_operand(a_dst, &mapA, C::A_MN, BM, m0, C::A_BYTES, &full[s], 0, false);
+          load_operand(a_dst, &mapA, C::A_MN, BM, m0, C::A_BYTES, &full[s], 0, false, k0);
           if (!alive)
             break;
         }
@@ -885,6 +953,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
     constexpr int GROUPS = C::EPI_WARPS / 4;
     float esum = 0.0f;
     int tile_iter = 0;
+    uint32_t out_seq = 0; // chunks this warp has staged for bulk stores
     for (int t = t_begin; t < t_end; t += t_step, ++tile_iter)
     {
       const int lrel = P.chain ? t : t / tiles_per_layer;
@@ -934,6 +1003,11 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         in.row = quarter * 32 + lane, in.nbufs = C::IN_BUFS > 0 ? C::IN_BUFS : 1;
         in.abort_flag = abort_flag;
         in.rx = rx_base;
+        in.out = (C::TSTORE && P.tstore) ? out_base + (warp - 2) * 8192 : nullptr;
+        in.out_seq = &out_seq;
+        in.map_e = &mapSE, in.map_fe = &mapSF;
+        in.out_row0 = m - lane; // the row of this warp's lane 0
+        in.layer_e = li + 1 - P.run_first, in.layer_fe = li - P.run_first;
         if (KS == 2)
         {
           // Hand the peer this CTA's partial sums of the 32 columns the peer finishes (16 per
@@ -1113,6 +1187,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           mbar_arrive(&tempty[acc]);
       }
     }
+    if (C::TSTORE && lane == 0)
+      bulk_wait_all(); // this warp's bulk stores are complete before its shared memory goes away
     if (OP == TC_FWD && (P.flags & DPC_FWD_ENERGY))
     {
 #pragma unroll
@@ -1316,6 +1392,27 @@ bool make_map_bf16(CUtensorMap* map, const __nv_bfloat16* base, int cols, int ro
   return r == CUDA_SUCCESS;
 }
 
+// Store maps of the staged epilogue: [planes][rows][cols] with a (16 x 32 x 1) box, i.e. one warp's
+// 32 rows of a 16-column chunk; rows of 64 bytes (fp32, 64-byte swizzle) or 32 bytes (bf16,
+// 32-byte swizzle) in shared memory.
+bool make_store_map(CUtensorMap* map, const void* base, bool bf16, int cols, int rows, int planes,
+                    int64_t plane_elems)
+{
+  EncodeTiledFn fn = encode_fn();
+  if (!fn)
+    return false;
+  const cuuint64_t eb = bf16 ? 2 : 4;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)planes};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * eb, (cuuint64_t)plane_elems * eb};
+  cuuint32_t box[3] = {16, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  bf16 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // Re-splits the operand planes of `kind` for layers [first, first + gridDim.y) from the fp32
 // tensors (after something other than a kernel of this file wrote them).
 __global__ void split_planes_kernel(const dpc_layer* __restrict__ layers, int first, int run_first,
@@ -1341,6 +1438,8 @@ int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b,
            const CUtensorMap* up = nullptr)
 {
   const CUtensorMap& u = up ? *up : a; // unused unless P.stage_in
+  const CUtensorMap& se = P.tstore ? st->e_st : a; // unused unless P.tstore
+  const CUtensorMap& sf = P.tstore ? st->fep_st : a;
   using C = Cfg<OP, BN, THREE_X, BM, PAIR, KS>;
   static bool configured = false;
   auto kern = pc_tc_kernel<OP, BN, THREE_X, BM, PAIR, KS>;
@@ -1372,14 +1471,14 @@ int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b,
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, b, u, P);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, b, u, se, sf, P);
     p->ctx->launches += 1;
     if (e != cudaSuccess)
       return cuda_fail(e, "tensor-core pair kernel launch");
     return DPC_OK;
   }
   const int grid = P.chain ? P.tiles_m * P.tiles_n : std::min(total, p->ctx->sm_count);
-  kern<<<grid, C::THREADS, C::SMEM_BYTES, p->ctx->stream>>>(a, b, u, P);
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, p->ctx->stream>>>(a, b, u, se, sf, P);
   p->ctx->launches += 1;
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess)
@@ -1457,7 +1556,12 @@ int tc_plan_init(dpc_plan* plan)
     return DPC_OK;
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, plan->ctx->device) != cudaSuccess || prop.major != 10)
-    return DPC_OK; // tcgen05 exists on sm_100 only; other devices keep the CUDA-core path
+  {
+    // tcgen05 exists on sm_100 only; other devices keep the CUDA-core path
+    fprintf(stderr, "deepity_b200: device %d is not sm_100: every layer runs on the CUDA-core "
+                    "kernels\n", plan->ctx->device);
+    return DPC_OK;
+  }
   st->max_smem = (int)prop.sharedMemPerBlockOptin;
   const int B = plan->batch, n = plan->n;
   if (B % TBM != 0)
@@ -1522,7 +1626,12 @@ int tc_plan_init(dpc_plan* plan)
   ok &= make_map(&st->fe_mn, L0.fe, H, B, best_count, plan->run.out_stride, 32, true);
   ok &= make_map(&st->w_mn, L0.W, H, H, best_count, plan->run.w_stride, 32, true);
   if (!ok)
-    return DPC_OK; // the driver refused a tensor map: stay on the CUDA-core path
+  {
+    // the driver refused a tensor map: stay on the CUDA-core path, audibly
+    fprintf(stderr, "deepity_b200: a tensor map for layers %d..%d was refused: they run on the "
+                    "CUDA-core kernels\n", best_first, best_first + best_count - 1);
+    return DPC_OK;
+  }
   {
     // Maps over beliefs and errors that also cover the layer above the run's last layer (it
     // has the run's width, and sits one stride further when the arenas are contiguous).
@@ -1553,7 +1662,16 @@ int tc_plan_init(dpc_plan* plan)
   plan->run.first = best_first;
   plan->run.count = best_count;
   plan->run.width = H;
-  if (!planes_init(plan, st, best_first, best_count, H))
+  if (planes_init(plan, st, best_first, best_count, H) && st->planes && st->up_maps &&
+      !getenv("DPC_DISABLE_STAGED_OUTPUT"))
+  {
+    // errors of the run's layers and the layer above it sit at the belief stride (checked for
+    // up_maps above): one store map covers them
+    st->store_maps =
+        make_store_map(&st->e_st, L0.e, false, H, B, best_count + 1, plan->run.z_stride) &&
+        make_store_map(&st->fep_st, st->fep, true, H, B, 2 * best_count, (int64_t)B * H);
+  }
+  if (!st->planes && !getenv("DPC_DISABLE_PLANES") && split_scheme(plan) == 2 && pair_ok(B, H))
   {
     // no memory (or no tensor map) for the planes: the kernels split the operands themselves
     planes_free(st);
@@ -1721,6 +1839,7 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
   P.w_elems = (long long)p->run.width * p->run.width;
   P.wait_cycles = st->wait_cycles;
   P.fe_only = fe_only_now(p, st) ? 1 : 0;
+  P.tstore = 0;
   P.layers = p->d;
   P.first = first;
   P.count = count;
@@ -1776,6 +1895,7 @@ int tc_forward(dpc_plan* p, int first, int count, int flags)
       if ((rc = planes_need(p, st, PL_Z, r0, r0 + count)) != DPC_OK ||
           (rc = planes_need(p, st, PL_W, r0, r0 + count)) != DPC_OK)
         return rc;
+      P.tstore = (st->store_maps && P.stage_in != 0) ? 1 : 0;
       rc = launch<TC_FWD, 256, 3, 128, true>(p, st, st->zp_km, st->wp_km128, P, up);
     }
     else

@@ -92,6 +92,30 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
                "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
                : "memory");
 }
+// Bulk tensor STORE shared -> global (completion through the bulk async-group of the issuing
+// thread: commit, then wait before the shared-memory source is reused / before the kernel ends).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1,
+                                             int c2)
+{
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit()
+{
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// at most N committed groups may still be reading their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read()
+{
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all()
+{
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
 // ---- CTA-pair (cta_group::2) helpers: two CTAs of a cluster share one 256-row tile ---------
 __device__ __forceinline__ uint32_t cluster_ctarank()
 {

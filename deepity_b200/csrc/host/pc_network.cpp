@@ -24,7 +24,7 @@ size_t Pad64(size_t n)
 void PCNetwork::Check(int rc) const
 {
   if (rc != DPC_OK)
-    throw std::runtime_error(std::string("deepity_b200: ") + dpc_last_error());
+    throw StatusError(rc, std::string("deepity_b200: ") + dpc_last_error());
 }
 
 void PCNetwork::RequireCompiled() const
@@ -1287,6 +1287,12 @@ int Guard(const std::function<void()>& fn)
   {
     fn();
     return DPC_OK;
+  }
+  catch (const Deep::StatusError& e)
+  {
+    // a dpc_* call failed underneath: its status travels up unchanged (DPC_ERR_TIMEOUT ...)
+    dpc::set_error(e.what());
+    return e.status;
   }
   catch (const std::invalid_argument& e)
   {

@@ -19,6 +19,13 @@
 
 namespace Deep
 {
+// A dpc_* call returned a negative status; carries it through the C++ layer to the C ABI.
+struct StatusError : std::runtime_error
+{
+  int status;
+  StatusError(int rc, const std::string& msg) : std::runtime_error(msg), status(rc) {}
+};
+
 enum class DeviceType
 {
   DEVICE_CPU,

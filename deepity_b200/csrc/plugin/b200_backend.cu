@@ -14,6 +14,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <random>
 #include <vector>
 
@@ -591,7 +592,9 @@ Ctx* create()
   if (cudaGetDeviceProperties(&prop, c->device) == cudaSuccess)
   {
     c->sm_count = prop.multiProcessorCount;
-    c->tensor_cores = prop.major == 10 && c->tc.init((int)prop.sharedMemPerBlockOptin);
+    // DEEPITY_B200_NO_TENSOR_CORES keeps every GEMM on the fp32 CUDA-core kernel (a test switch)
+    c->tensor_cores = prop.major == 10 && !getenv("DEEPITY_B200_NO_TENSOR_CORES") &&
+                      c->tc.init((int)prop.sharedMemPerBlockOptin);
   }
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&c->partials, sizeof(double) * (kPartials + 1)) != cudaSuccess ||

@@ -16,6 +16,21 @@
  * Every function returns DPC_OK (0) or a negative dpc_status; dpc_last_error() gives
  * the message of the last failure on the calling thread.  There is no CPU fallback:
  * without a CUDA device every call fails with DPC_ERR_NO_DEVICE.
+ *
+ * Which kernels run is decided per plan from the layer shapes (dpc_plan_describe tells); a plan
+ * whose shapes qualify for the tensor-core kernels but cannot get them (no sm_100 device, a
+ * refused tensor map, no memory for the operand copies) says so once on stderr.  Environment
+ * switches, read when a plan is created or a phase is launched -- diagnostic aids that the
+ * tests use to compare code paths, not tuning knobs:
+ *   DPC_DISABLE_TENSOR_CORES   every layer on the CUDA-core kernels
+ *   DPC_DISABLE_CTA_PAIRS      single-CTA 128-row tiles instead of cta_group::2 pairs
+ *   DPC_FP32_SCHEME=tf32x3     FP32 mode with three TF32 passes instead of three BF16 passes
+ *   DPC_DISABLE_PLANES         3xBF16 operands split inside the kernels, not pre-split copies
+ *   DPC_KEEP_FE_FP32           keep writing the fp32 feedback errors beside their bf16 copies
+ *   DPC_DISABLE_STAGED_INPUT / DPC_DISABLE_STAGED_OUTPUT
+ *                              forward epilogue reads / writes global memory lane by lane
+ *                              instead of through shared memory and bulk tensor copies
+ *   DPC_DISABLE_KSPLIT         forward sweep without the two-CTA split of K
  */
 #ifndef DEEPITY_B200_H
 #define DEEPITY_B200_H

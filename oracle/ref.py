@@ -61,6 +61,10 @@ def lib():
         L.ref_omp_threads.restype = ctypes.c_int
         L.ref_num_procs.restype = ctypes.c_int
         L.ref_blas_config.restype = ctypes.c_char_p
+        L.ref_backend_matmul.argtypes = [ctypes.c_int] * 6 + [ctypes.c_float, f32p, ctypes.c_int64,
+                                         ctypes.c_int, f32p, ctypes.c_int64, ctypes.c_int,
+                                         ctypes.c_float, f32p, ctypes.c_int64, ctypes.c_int,
+                                         ctypes.c_int]
         L.ref_blas_threads.restype = ctypes.c_int
         L.ref_set_threads.argtypes = [ctypes.c_int]
         _lib = L
@@ -164,6 +168,22 @@ def host_info() -> dict:
     L = lib()
     return {"omp_threads": L.ref_omp_threads(), "nproc": L.ref_num_procs(),
             "blas_threads": L.ref_blas_threads(), "blas": L.ref_blas_config().decode()}
+
+
+def backend_matmul(device: str, trans_a: bool, trans_b: bool, M: int, N: int, K: int, alpha: float,
+                   A: np.ndarray, lda: int, B: np.ndarray, ldb: int, beta: float, C: np.ndarray,
+                   ldc: int, allow_tf32=None) -> np.ndarray:
+    """C = alpha*op(A)*op(B) + beta*C through IComputeBackend::MatMul of the reference's CPU backend
+    (device 'cpu') or of whatever GPU plugin its loader finds ('gpu'); returns the new C."""
+    a = np.ascontiguousarray(A, dtype=np.float32).ravel()
+    b = np.ascontiguousarray(B, dtype=np.float32).ravel()
+    c = np.ascontiguousarray(C, dtype=np.float32).ravel().copy()
+    rc = lib().ref_backend_matmul(int(device != "cpu"), int(trans_a), int(trans_b), M, N, K, alpha,
+                                  _ptr(a), a.size, lda, _ptr(b), b.size, ldb, beta, _ptr(c), c.size,
+                                  ldc, -1 if allow_tf32 is None else int(allow_tf32))
+    if rc != 0:
+        raise RuntimeError(f"backend MatMul failed ({rc})")
+    return c
 
 
 def set_threads(n: int) -> None:

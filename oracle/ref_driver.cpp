@@ -19,6 +19,7 @@
 
 #include <omp.h>
 
+#include <deepity/backend/Backend.h>
 #include <deepity/networks/DirectKPPCNetwork.h>
 #include <deepity/networks/FullPCNetwork.h>
 #include <deepity/networks/SimplePCNetwork.h>
@@ -451,6 +452,43 @@ float ref_phase(void* h, const char* op, const float* data, int64_t count)
   else
     return -1.0f;
   return 0.0f;
+}
+
+// One GEMM through the reference's backend interface on host arrays (device 1: the GPU plugin the
+// loader finds; 0: the CPU backend): C = alpha*op(A)*op(B) + beta*C with BLAS leading dimensions.
+// For primitive-level checks of a plugin's MatMul (tests/tMatMulLargeAsymmetricVerify.cpp's idea).
+// a_elems/b_elems/c_elems: sizes of the host arrays.  allow_tf32 < 0 leaves the backend's default.
+int ref_backend_matmul(int device, int transA, int transB, int M, int N, int K, float alpha,
+                       const float* A, int64_t a_elems, int lda, const float* B, int64_t b_elems,
+                       int ldb, float beta, float* C, int64_t c_elems, int ldc, int allow_tf32)
+{
+  try
+  {
+    std::unique_ptr<IComputeBackend> be =
+        CreateBackend(device ? DeviceType::DEVICE_GPU : DeviceType::DEVICE_CPU);
+    if (allow_tf32 >= 0)
+      be->SetAllowTF32(allow_tf32 != 0);
+    float* dA = be->Allocate((size_t)a_elems);
+    float* dB = be->Allocate((size_t)b_elems);
+    float* dC = be->Allocate((size_t)c_elems);
+    if (!dA || !dB || !dC)
+      return -2;
+    be->CopyFromHost(dA, A, (size_t)a_elems);
+    be->CopyFromHost(dB, B, (size_t)b_elems);
+    be->CopyFromHost(dC, C, (size_t)c_elems);
+    be->MatMul(transA != 0, transB != 0, M, N, K, alpha, dA, lda, dB, ldb, beta, dC, ldc);
+    be->Synchronize();
+    be->CopyToHost(C, dC, (size_t)c_elems);
+    be->Free(dA);
+    be->Free(dB);
+    be->Free(dC);
+    return 0;
+  }
+  catch (const std::exception& e)
+  {
+    fprintf(stderr, "ref_backend_matmul: %s\n", e.what());
+    return -1;
+  }
 }
 
 // Host threading the reference chose for this batch size
