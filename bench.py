@@ -573,8 +573,8 @@ def layer_sharded_main(args, w, sizes, config):
     dist.all_reduce(lc)
     flops = net.train_step_flops(T)
     ranges = net.ranges
-    net.close()
-    del net
+    # (the sharded network stays alive to the end of the process: torch tensors that were used on
+    # its stream outlive this function, and freeing them after the stream is gone aborts)
     side = None if args.no_side else batch_sharded_measure(args, dict(WORKLOADS["c4"]))
     if rank == 0:
         peaks = load_peaks()

@@ -4,7 +4,7 @@
 // own GPU backend uses by default (src/backend/cuda/CUDABackendGemm.cu:435-445,
 // CUDABackendCore.cu:54-67).  One CTA per 128 x BN output tile: warp 0 streams 32-wide k-blocks
 // of both operands through a shared-memory ring by TMA (2-D tensor maps built per call from the
-// caller's pointers and leading dimensions; no multicast), warp 1 issues the MMAs, warps 2-5
+// caller's pointers and leading dimensions; every CTA loads its own tiles), warp 1 issues the MMAs, warps 2-5
 // read the accumulator (one tensor-memory quarter each) and apply alpha / beta.
 //
 // Either operand may be "K-major" (k contiguous in memory: A not transposed, B transposed) or

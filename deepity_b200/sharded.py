@@ -169,8 +169,12 @@ class GpuEngine:
         self.check(self.lib.dpc_plan_invalidate(self.plan, layer, 1, 1))  # DPC_WROTE_Z
 
     def close(self):
-        """Free the block's device memory (the network, its plan and context)."""
+        """Free the block's device memory (the network, its plan and context, its stream).
+        Every torch tensor that was used on the block's stream must have been released before:
+        torch's allocator records an event on each stream a tensor was used on when the tensor is
+        freed, and aborts the process if that stream no longer exists."""
         if self.h:
+            self.torch.cuda.synchronize()
             self._views.clear()
             self.lib.dpcn_destroy(self.h)
             self.h = None
