@@ -104,18 +104,58 @@ from deepity_b200.flops import algorithmic_flops  # noqa: E402
 
 # ------------------------------------------------------------------------------ clocks
 class ClockSampler:
+    """SM clock and throttle reasons of one GPU, sampled every 50 ms while the timed region runs.
+    Reads through NVML in-process (nvidia_ml_py); one nvidia-smi process per sample is the
+    fallback (slow, and eight of them at once on an 8-GPU host get in the ranks' way)."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index=0):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self.index = index
+        self.source = None
         self.thread = threading.Thread(target=self._run, daemon=True)
 
-    def _run(self):
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if visible:
+                try:
+                    idx = int(visible.split(",")[self.index])
+                except ValueError:
+                    pass
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(idx)
+
+    def _run_nvml(self):
+        nv, h = self._nvml_handle()
+        self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                "sw_power_cap": 0x4}
+        self.source = "nvml"
+        while not self._stop.is_set():
+            self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+            mask = int(get_reasons(h))
+            for nm, bit in bits.items():
+                if mask & bit:
+                    self.reasons.add(nm)
+            self._stop.wait(0.05)
+
+    def _run_smi(self):
+        self.source = "nvidia-smi"
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
@@ -123,12 +163,18 @@ class ClockSampler:
                                      text=True, timeout=5).stdout.strip().split(",")
                 self.samples.append(float(out[0]))
                 self.max_mhz = float(out[1])
-                for nm, v in zip(names, out[2:]):
+                for nm, v in zip(self.NAMES, out[2:]):
                     if v.strip().lower().startswith("active"):
                         self.reasons.add(nm)
             except Exception:
                 pass
             self._stop.wait(0.2)
+
+    def _run(self):
+        try:
+            self._run_nvml()
+        except Exception:
+            self._run_smi()
 
     def __enter__(self):
         self.thread.start()
@@ -141,7 +187,7 @@ class ClockSampler:
     def summary(self):
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
+                "samples": len(self.samples), "source": self.source}
 
 
 # ------------------------------------------------------------------------------ CPU leg
@@ -455,9 +501,9 @@ def load_peaks():
 
 # DRAM bytes per 1024x512x512 layer of one launch of the dominant kernel, measured with ncu
 # (dram__bytes_read.sum + dram__bytes_write.sum) as the difference between a 127-layer and a
-# 63-layer capture divided by 64, so that the dirty lines a launch leaves in L2 cancel.
-# None until such a pair of captures exists for the current kernel.
-NCU_DRAM_BYTES_PER_LAYER = None
+# 63-layer capture divided by 64, so that the dirty lines a launch leaves in L2 cancel:
+# (669.2 + 478.8) MB - (333.0 + 214.7) MB = 600.3 MB over 64 layers (algorithmic: 9.44 MB).
+NCU_DRAM_BYTES_PER_LAYER = 9.38e6
 
 
 def forward_roofline(B, sizes, k_ms, precision, passes, peaks):

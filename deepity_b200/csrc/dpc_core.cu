@@ -824,12 +824,28 @@ static int launch_dfa_proj(dpc_plan* p, int first, int count, int from_output)
     int mxn = 1;
     for (int k = i; k < j; ++k)
       mxn = std::max(mxn, p->h[k].next_size);
-    if (v)
+    bool wide = v;
+    for (int k = i; k < j && wide; ++k)
+      wide = p->h[k].next_size <= 0 || p->h[k].next_size % 128 == 0;
+    const int ts4 = cdiv(std::max(p->h[i].terminal_size, 1), 4);
+    if (wide && ts4 <= 4 && cdiv(mxn, 128) * c >= 2 * p->ctx->sm_count)
+    {
+      // blocks of 128 columns x the whole batch
+      dim3 grid(cdiv(mxn, 128), c);
+      if (ts4 <= 1)
+        dfa_proj128_kernel<1><<<grid, 256, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, planes);
+      else if (ts4 == 2)
+        dfa_proj128_kernel<2><<<grid, 256, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, planes);
+      else if (ts4 == 3)
+        dfa_proj128_kernel<3><<<grid, 256, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, planes);
+      else
+        dfa_proj128_kernel<4><<<grid, 256, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, planes);
+    }
+    else if (v)
     {
       const int rpb =
           cdiv(mxn, 256) * cdiv(p->batch, DFA4_ROWS) * c >= 4 * p->ctx->sm_count ? DFA4_ROWS : 32;
       dim3 grid(cdiv(mxn, 256), cdiv(p->batch, rpb), c);
-      const int ts4 = cdiv(std::max(p->h[i].terminal_size, 1), 4);
       if (ts4 <= 1)
         dfa_proj4_kernel<1><<<grid, 64, 0, st>>>(p->d, i, p->n, p->batch, p->e_terminal, from_output, rpb, planes);
       else if (ts4 == 2)
@@ -871,6 +887,39 @@ int dpc_direct_feedback(dpc_plan* p, int first, int count, int decay_w)
   return dispatch_range(
       p, first, count, [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_DFA, decay_w); },
       [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA, flags); });
+}
+
+// Psi update (or its raw sums) of layers [f, f+c): the 128-columns-per-block kernel when every
+// layer of the launch that has feedback weights is a multiple of 128 wide with at most 16
+// terminal units, the general kernel otherwise.
+static int launch_psi_update(dpc_plan* p, int f, int c, int max_size, int grad_only)
+{
+  cudaStream_t st = p->ctx->stream;
+  bool fast = true;
+  int ts = 0;
+  for (int i = f; i < f + c && i < p->n; ++i)
+  {
+    const dpc_layer& L = p->h[i];
+    if (L.next_size <= 0 || L.Psi == nullptr || (L.flags & DPC_LAYER_INPUT_ACT))
+      continue;
+    if (L.size % 128 != 0 || L.terminal_size > 16)
+      fast = false;
+    ts = std::max(ts, L.terminal_size);
+  }
+  if (fast && ts > 0)
+  {
+    dim3 g(std::max(1, cdiv(max_size, 128)), c);
+    if (ts <= 12)
+      psi_update4_kernel<12><<<g, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, grad_only);
+    else
+      psi_update4_kernel<16><<<g, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, grad_only);
+  }
+  else
+  {
+    dim3 g(std::max(1, cdiv(max_size, 64)), c);
+    psi_update_kernel<<<g, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, grad_only);
+  }
+  return check_launch(p->ctx, grad_only ? "psi gradient kernel" : "psi_update kernel");
 }
 
 int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
@@ -949,9 +998,7 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
       return rc;
     if (any_psi)
     {
-      dim3 gp(std::max(1, cdiv(max_size, 64)), c);
-      psi_update_kernel<<<gp, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, 0);
-      if ((rc = check_launch(p->ctx, "psi_update kernel")) != DPC_OK)
+      if ((rc = launch_psi_update(p, f, c, max_size, 0)) != DPC_OK)
         return rc;
     }
     if (center_rows)
@@ -1029,9 +1076,7 @@ int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
       return rc;
     if (any_psi)
     {
-      dim3 gp(std::max(1, cdiv(max_size, 64)), c);
-      psi_update_kernel<<<gp, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, 1);
-      if ((rc = check_launch(p->ctx, "psi gradient kernel")) != DPC_OK)
+      if ((rc = launch_psi_update(p, f, c, max_size, 1)) != DPC_OK)
         return rc;
     }
   }
