@@ -725,6 +725,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-side", action="store_true",
                     help="skip the batch-sharded C4 measurement that rides along with C3")
+    ap.add_argument("--sweep-trace", action="store_true",
+                    help="print the per-layer time stamps of the forward-sweep kernel "
+                         "(c3 cut to 300 hidden layers unless --depth is given) and exit")
     ap.add_argument("--sample-depth", type=int, default=None,
                     help="hidden layers of the CPU arm's bounded sample (default: calibrated)")
     args = ap.parse_args()
@@ -747,6 +750,11 @@ def main():
                               "optimizer is on; 1e-2 in tf32 mode; 1e-3 in mixed mode",
               "l2": "working set (z,e,preact,mu,fe,W of every layer) is far larger than the 126 MB L2"
               if args.workload in ("c3", "c4") else "L2 flushed between timed steps"}
+
+    if args.sweep_trace:
+        if rank == 0:
+            sweep_trace(args, w)
+        return
 
     if args.impl == "reference":
         if rank != 0:
@@ -888,6 +896,45 @@ def sample_energy_check(w, leg, precision):
     ref = leg["last_energy"]
     return {"hidden_layers": hidden, "steps": leg["steps_run"] + leg["warmup_run"],
             "cpu_energy": ref, "gpu_energy": e, "relative_difference": abs(e - ref) / max(1.0, abs(ref))}
+
+
+def sweep_trace(args, w):
+    """Profiling aid: where a layer of the persistent forward-sweep kernel spends its time.
+    CTA 0 of the kernel stamps %globaltimer at six points of every layer (the first 256 layers);
+    prints the median differences over layers 50..250 as one JSON line."""
+    import ctypes
+    import torch
+    from deepity_b200 import _lib
+    if not args.depth:
+        w = dict(w, hidden=300)
+    sizes = sizes_of(w)
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    net = build_net(w, sizes, args.precision)
+    net.set_use_graph(False)
+    stamps = torch.zeros(256 * 8, dtype=torch.int64, device="cuda")
+    _lib.check(lib.dpc_plan_set_chain_trace(lib.dpcn_plan(net._h), ctypes.c_void_p(stamps.data_ptr())))
+    x, y, params = synth(w, sizes)
+    for l, p in enumerate(params):
+        for nm, v in p.items():
+            net.set_tensor(l, nm, v)
+    for _ in range(3):
+        net.train_step(x, y, w["T"])
+    t = stamps.cpu().numpy().reshape(256, 8).astype(np.int64)
+    _lib.check(lib.dpc_plan_set_chain_trace(lib.dpcn_plan(net._h), None))
+    lo, hi = 50, min(250, len(sizes) - 4)
+    d = t[lo:hi]
+    med = lambda v: float(np.median(v))
+    out = {"workload": w["desc"], "precision": args.precision, "hidden_layers": w["hidden"],
+           "layers_sampled": [lo, hi], "unit": "ns (globaltimer, 32 ns steps)",
+           "dependency_seen_to_first_operands_landed": med(d[:, 1] - d[:, 0]),
+           "first_operands_to_accumulator_complete": med(d[:, 2] - d[:, 1]),
+           "accumulator_complete_to_stores_issued": med(d[:, 3] - d[:, 2]),
+           "of_which_until_partial_sums_exchanged": med(d[:, 5] - d[:, 2]),
+           "stores_issued_to_published": med(d[:, 4] - d[:, 3]),
+           "published_to_next_dependency_seen": med(t[lo + 1:hi + 1, 0] - d[:, 4]),
+           "layer_period": med(t[lo + 1:hi + 1, 0] - d[:, 0])}
+    print(json.dumps(out))
 
 
 def single_gpu_side(w, args):
