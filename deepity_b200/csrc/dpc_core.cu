@@ -549,29 +549,43 @@ static int forward_simt(dpc_plan* p, int first, int count, int flags)
   return DPC_OK;
 }
 
-// Splits [first, first+count) into the part the tensor-core path takes and the rest.
+// Splits [first, first+count) into what the tensor-core path takes (the part inside the run as
+// one piece, single layers outside it that fit the CTA-pair kernels one by one) and maximal
+// pieces for the CUDA-core kernels.  A piece the tensor-core entry point declines (returns 1)
+// goes to the CUDA-core kernels too.
 template <typename TcFn, typename SimtFn>
 static int dispatch_range(dpc_plan* p, int first, int count, TcFn tc, SimtFn simt)
 {
-  if (count == 0)
-    return DPC_OK;
-  const int r0 = std::max(first, p->run.first);
-  const int r1 = std::min(first + count, p->run.first + p->run.count);
-  if (p->run.count > 0 && r1 > r0)
+  const int end = first + count;
+  const int run0 = p->run.first, run1 = p->run.first + p->run.count;
+  int i = first;
+  while (i < end)
   {
-    int rc = tc(r0, r1 - r0);
+    int j, rc;
+    if (p->run.count > 0 && i >= run0 && i < run1)
+    {
+      j = std::min(end, run1);
+      rc = tc(i, j - i);
+    }
+    else if (tc_extra_layer(p, i))
+    {
+      j = i + 1;
+      rc = tc(i, 1);
+    }
+    else
+    {
+      j = i + 1;
+      while (j < end && !(p->run.count > 0 && j >= run0 && j < run1) && !tc_extra_layer(p, j))
+        ++j;
+      rc = 1;
+    }
     if (rc < 0)
       return rc;
-    if (rc == DPC_OK)
-    {
-      if (r0 > first && (rc = simt(first, r0 - first)) != DPC_OK)
-        return rc;
-      if (first + count > r1 && (rc = simt(r1, first + count - r1)) != DPC_OK)
-        return rc;
-      return DPC_OK;
-    }
+    if (rc != DPC_OK && (rc = simt(i, j - i)) != DPC_OK)
+      return rc;
+    i = j;
   }
-  return simt(first, count);
+  return DPC_OK;
 }
 
 int dpc_forward(dpc_plan* p, int first, int count, int flags)

@@ -95,4 +95,10 @@ int tc_sync_planes(dpc_plan* plan);
 // on the forward sweep's publication target (test hook: a target nothing reaches).
 void tc_set_wait_limit(dpc_plan* plan, long long cycles, int chain_target_bias);
 std::string tc_describe(dpc_plan* plan);
+// Single layers outside the run whose shapes fit the CTA-pair tensor-core kernels (batch, input
+// and output width multiples of 256).  Same return convention as the run's entry points.
+bool tc_extra_layer(dpc_plan* plan, int layer);
+int tc_extra_forward(dpc_plan* plan, int layer, int flags);
+int tc_extra_update_state(dpc_plan* plan, int layer);
+int tc_extra_weight_gemm(dpc_plan* plan, int layer, int mode, int decay_w);
 } // namespace dpc

@@ -91,6 +91,14 @@ struct TcState
   // the planes (feedback and weight-shaped products of this file, the bias column sums).
   bool fe_only = false;
   bool warned_fallback = false;
+  // Single layers outside the run that still fit the CTA-pair kernels (batch, input and output
+  // width all multiples of 256, e.g. a 3072 -> 1024 first layer): one set of tensor maps each.
+  struct Extra
+  {
+    int layer;
+    CUtensorMap z_km, w_km128, fe_km, w_mn, fe_mn, z_mn;
+  };
+  std::vector<Extra> extras;
 };
 enum
 {
@@ -1619,6 +1627,8 @@ static void planes_free(TcState* st)
   st->planes = false;
 }
 
+static bool run_init(dpc_plan* plan, TcState* st, int best_first, int best_count);
+
 int tc_plan_init(dpc_plan* plan)
 {
   plan->run = TensorRun();
@@ -1675,8 +1685,48 @@ int tc_plan_init(dpc_plan* plan)
     }
     i = j;
   }
-  if (best_count < 1)
+  if (cudaMalloc(&st->error_flag, sizeof(int)) != cudaSuccess ||
+      cudaMemset(st->error_flag, 0, sizeof(int)) != cudaSuccess ||
+      cudaMallocHost(&st->error_host, sizeof(int)) != cudaSuccess)
     return DPC_OK;
+  *st->error_host = 0;
+  if (best_count >= 1 && !run_init(plan, st, best_first, best_count))
+    best_count = 0;
+  // Layers outside the run whose three products fit the 256 x 256 CTA-pair tiles.
+  if (pair_ok(B, 256) && !getenv("DPC_DISABLE_RECTANGULAR"))
+    for (int l = 0; l + 1 < n; ++l)
+    {
+      if (best_count > 0 && l >= best_first && l < best_first + best_count)
+        continue;
+      const dpc_layer& L = plan->h[l];
+      if (L.next_size <= 0 || L.size % 256 != 0 || L.next_size % 256 != 0 ||
+          (L.flags & DPC_LAYER_INPUT_ACT) || !L.fe || !L.preact || !L.W || !L.z ||
+          ((uintptr_t)L.z % 128) != 0 || ((uintptr_t)L.W % 128) != 0 || ((uintptr_t)L.fe % 128) != 0)
+        continue;
+      TcState::Extra x;
+      x.layer = l;
+      const int s_in = L.size, s_out = L.next_size;
+      bool ok = true;
+      ok &= make_map(&x.z_km, L.z, s_in, B, 1, (int64_t)B * s_in, TBM, false);
+      ok &= make_map(&x.z_mn, L.z, s_in, B, 1, (int64_t)B * s_in, 32, true);
+      ok &= make_map(&x.fe_km, L.fe, s_out, B, 1, (int64_t)B * s_out, TBM, false);
+      ok &= make_map(&x.fe_mn, L.fe, s_out, B, 1, (int64_t)B * s_out, 32, true);
+      ok &= make_map(&x.w_km128, L.W, s_in, s_out, 1, (int64_t)s_in * s_out, 128, false);
+      ok &= make_map(&x.w_mn, L.W, s_in, s_out, 1, (int64_t)s_in * s_out, 32, true);
+      if (ok)
+        st->extras.push_back(x);
+      else
+        fprintf(stderr, "deepity_b200: a tensor map for layer %d was refused: it runs on the "
+                        "CUDA-core kernels\n", l);
+    }
+  st->ok = best_count > 0 || !st->extras.empty();
+  return DPC_OK;
+}
+
+// Tensor maps, sweep counters and operand planes of the run [best_first, best_first + best_count).
+static bool run_init(dpc_plan* plan, TcState* st, int best_first, int best_count)
+{
+  const int B = plan->batch, n = plan->n;
   if (best_count == 1)
   {
     const dpc_layer& L0 = plan->h[best_first];
@@ -1702,7 +1752,7 @@ int tc_plan_init(dpc_plan* plan)
     // the driver refused a tensor map: stay on the CUDA-core path, audibly
     fprintf(stderr, "deepity_b200: a tensor map for layers %d..%d was refused: they run on the "
                     "CUDA-core kernels\n", best_first, best_first + best_count - 1);
-    return DPC_OK;
+    return false;
   }
   {
     // Maps over beliefs and errors that also cover the layer above the run's last layer (it
@@ -1724,13 +1774,8 @@ int tc_plan_init(dpc_plan* plan)
       st->up_maps = make_map(&st->zup_km, L0.z, H, B, best_count + 1, plan->run.z_stride, TBM, false) &&
                     make_map(&st->eup_km, L0.e, H, B, best_count + 1, plan->run.z_stride, TBM, false);
   }
-  if (cudaMalloc(&st->chain_counters, sizeof(int) * (size_t)best_count * (B / 64)) != cudaSuccess ||
-      cudaMalloc(&st->error_flag, sizeof(int)) != cudaSuccess ||
-      cudaMemset(st->error_flag, 0, sizeof(int)) != cudaSuccess ||
-      cudaMallocHost(&st->error_host, sizeof(int)) != cudaSuccess)
-    return DPC_OK;
-  *st->error_host = 0;
-  st->ok = true;
+  if (cudaMalloc(&st->chain_counters, sizeof(int) * (size_t)best_count * (B / 64)) != cudaSuccess)
+    return false;
   plan->run.first = best_first;
   plan->run.count = best_count;
   plan->run.width = H;
@@ -1750,7 +1795,7 @@ int tc_plan_init(dpc_plan* plan)
     fprintf(stderr, "deepity_b200: operand planes unavailable for this plan, using the in-kernel "
                     "operand split\n");
   }
-  return DPC_OK;
+  return true;
 }
 
 void tc_plan_free(dpc_plan* plan)
@@ -1936,6 +1981,8 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
 int tc_forward(dpc_plan* p, int first, int count, int flags)
 {
   auto* st = static_cast<TcState*>(p->tc);
+  if (st && st->ok && count == 1 && !range_in_run(p, first, 1))
+    return tc_extra_forward(p, first, flags);
   if (!st || !st->ok || !range_in_run(p, first, count))
     return 1;
   const int H = p->run.width, B = p->batch;
@@ -2077,6 +2124,8 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
 int tc_update_state(dpc_plan* p, int first, int count)
 {
   auto* st = static_cast<TcState*>(p->tc);
+  if (st && st->ok && count == 1 && !range_in_run(p, first, 1))
+    return tc_extra_update_state(p, first);
   if (!st || !st->ok || !range_in_run(p, first, count))
     return 1;
   const int H = p->run.width, B = p->batch;
@@ -2116,6 +2165,8 @@ int tc_update_state(dpc_plan* p, int first, int count)
 int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
 {
   auto* st = static_cast<TcState*>(p->tc);
+  if (st && st->ok && count == 1 && !range_in_run(p, first, 1))
+    return tc_extra_weight_gemm(p, first, mode, decay_w);
   if (!st || !st->ok || !range_in_run(p, first, count))
     return 1;
   for (int i = first; i < first + count; ++i)
@@ -2225,6 +2276,92 @@ int tc_sync_planes(dpc_plan* p)
   return DPC_OK;
 }
 
+// ---- single layers outside the run (TcState::Extra) --------------------------------------------
+// The same CTA-pair kernels on tensor maps of one layer: operands are the fp32 tensors (one TF32
+// pass, three TF32 passes, or the three-BF16-pass split inside the kernel; no operand planes), the
+// layer coordinate of every load is 0, the epilogue reads the layer above with per-lane loads.
+static const TcState::Extra* find_extra(const TcState* st, int layer)
+{
+  for (const auto& x : st->extras)
+    if (x.layer == layer)
+      return &x;
+  return nullptr;
+}
+
+bool tc_extra_layer(dpc_plan* p, int layer)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  return st && st->ok && find_extra(st, layer) != nullptr;
+}
+
+static TcParams extra_params(dpc_plan* p, TcState* st, int layer, int M, int N, int K, int flags,
+                             int mode)
+{
+  TcParams P = base_params(p, st, layer, 1, M, N, K, 256, flags, mode, 256);
+  P.run_first = layer; // the maps hold this layer only
+  P.zp = P.fep = P.wp = nullptr;
+  P.fe_only = 0;
+  return P;
+}
+
+int tc_extra_forward(dpc_plan* p, int layer, int flags)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  const TcState::Extra* x = (st && st->ok) ? find_extra(st, layer) : nullptr;
+  if (!x)
+    return 1;
+  const dpc_layer& L = p->h[layer];
+  const bool refresh =
+      (flags & DPC_FWD_FE) && !(flags & DPC_FWD_ERR_NEXT) && (flags & DPC_FWD_TRANSIENT);
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || (refresh && fast_grad(p));
+  const int scheme = split_scheme(p);
+  TcParams P = extra_params(p, st, layer, p->batch, L.next_size, L.size, flags, 0);
+  const int rc =
+      tf32 ? launch<TC_FWD, 256, 0, 128, true>(p, st, x->z_km, x->w_km128, P)
+      : scheme == 2 ? launch<TC_FWD, 256, 2, 128, true>(p, st, x->z_km, x->w_km128, P)
+                    : launch<TC_FWD, 256, 1, 128, true>(p, st, x->z_km, x->w_km128, P);
+  // the belief it may have written can be the first layer of the run: its planes are stale
+  if (rc == DPC_OK && (flags & DPC_FWD_COPY_NEXT))
+    tc_touch(p, PL_Z, layer + 1, 1);
+  return rc;
+}
+
+int tc_extra_update_state(dpc_plan* p, int layer)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  const TcState::Extra* x = (st && st->ok) ? find_extra(st, layer) : nullptr;
+  if (!x)
+    return 1;
+  const dpc_layer& L = p->h[layer];
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  const int scheme = split_scheme(p);
+  TcParams P = extra_params(p, st, layer, p->batch, L.size, L.next_size, 0, 0);
+  return tf32 ? launch<TC_FB, 256, 0, 128, true>(p, st, x->fe_km, x->w_mn, P)
+       : scheme == 2 ? launch<TC_FB, 256, 2, 128, true>(p, st, x->fe_km, x->w_mn, P)
+                     : launch<TC_FB, 256, 1, 128, true>(p, st, x->fe_km, x->w_mn, P);
+}
+
+int tc_extra_weight_gemm(dpc_plan* p, int layer, int mode, int decay_w)
+{
+  auto* st = static_cast<TcState*>(p->tc);
+  const TcState::Extra* x = (st && st->ok) ? find_extra(st, layer) : nullptr;
+  if (!x)
+    return 1;
+  const dpc_layer& L = p->h[layer];
+  if (mode == WG_LEARN_MODE && L.opt != DPC_OPT_SGD)
+    return 1; // Adam-type updates go through the staging buffer (mode | WG_GRAD_MODE)
+  if ((mode & WG_GRAD_MODE) && (!L.g_W || ((uintptr_t)L.g_W % 32) != 0))
+    return 1;
+  if ((mode & 1) == WG_DFA_MODE && (layer + 1 >= p->n || !p->h[layer + 1].Psi))
+    return 1;
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || fast_grad(p);
+  const int scheme = split_scheme(p);
+  TcParams P = extra_params(p, st, layer, L.next_size, L.size, p->batch, decay_w ? 1 : 0, mode);
+  return tf32 ? launch<TC_WG, 256, 0, 128, true>(p, st, x->fe_mn, x->z_mn, P)
+       : scheme == 2 ? launch<TC_WG, 256, 2, 128, true>(p, st, x->fe_mn, x->z_mn, P)
+                     : launch<TC_WG, 256, 1, 128, true>(p, st, x->fe_mn, x->z_mn, P);
+}
+
 void tc_set_wait_limit(dpc_plan* p, long long cycles, int chain_target_bias)
 {
   auto* st = static_cast<TcState*>(p->tc);
@@ -2239,18 +2376,35 @@ std::string tc_describe(dpc_plan* p)
 {
   auto* st = static_cast<TcState*>(p->tc);
   const int weight_layers = p->n - 1;
-  if (!st || !st->ok || p->run.count <= 0)
+  if (!st || !st->ok)
     return "all " + std::to_string(weight_layers) + " weight layers on CUDA cores";
-  const bool pair = pair_ok(p->batch, p->run.width);
-  std::string mode = p->ctx->precision == DPC_PRECISION_TF32 ? "1xTF32"
-                     : split_scheme(p) == 2 ? (planes_on(p, st) ? "3xBF16 from pre-split planes"
-                                                               : "3xBF16 split in the kernel")
-                                            : "3xTF32";
-  if (p->ctx->precision == DPC_PRECISION_MIXED)
-    mode += " (gradient path 1xTF32)";
-  return "layers " + std::to_string(p->run.first) + ".." +
-         std::to_string(p->run.first + p->run.count - 1) + " on tcgen05 (" +
-         (pair ? "CTA pairs 256x256" : "single-CTA tiles") + ", " + mode + "); " +
-         std::to_string(weight_layers - p->run.count) + " weight layers on CUDA cores";
+  const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32;
+  std::string out;
+  int on_tc = 0;
+  if (p->run.count > 0)
+  {
+    const bool pair = pair_ok(p->batch, p->run.width);
+    std::string mode = tf32 ? "1xTF32"
+                       : split_scheme(p) == 2 ? (planes_on(p, st) ? "3xBF16 from pre-split planes"
+                                                                 : "3xBF16 split in the kernel")
+                                              : "3xTF32";
+    if (p->ctx->precision == DPC_PRECISION_MIXED)
+      mode += " (gradient path 1xTF32)";
+    out = "layers " + std::to_string(p->run.first) + ".." +
+          std::to_string(p->run.first + p->run.count - 1) + " on tcgen05 (" +
+          (pair ? "CTA pairs 256x256" : "single-CTA tiles") + ", " + mode + "); ";
+    on_tc += p->run.count;
+  }
+  if (!st->extras.empty())
+  {
+    out += "layer";
+    for (const auto& x : st->extras)
+      out += " " + std::to_string(x.layer) + " (" + std::to_string(p->h[x.layer].size) + "->" +
+             std::to_string(p->h[x.layer].next_size) + ")";
+    out += std::string(" on tcgen05 (CTA pairs 256x256, ") +
+           (tf32 ? "1xTF32" : split_scheme(p) == 2 ? "3xBF16 split in the kernel" : "3xTF32") + "); ";
+    on_tc += (int)st->extras.size();
+  }
+  return out + std::to_string(weight_layers - on_tc) + " weight layers on CUDA cores";
 }
 } // namespace dpc

@@ -31,6 +31,8 @@
  *                              forward epilogue reads / writes global memory lane by lane
  *                              instead of through shared memory and bulk tensor copies
  *   DPC_DISABLE_KSPLIT         forward sweep without the two-CTA split of K
+ *   DPC_DISABLE_RECTANGULAR    single layers outside the run of identical square layers stay on
+ *                              the CUDA-core kernels even where their shapes fit the pair tiles
  */
 #ifndef DEEPITY_B200_H
 #define DEEPITY_B200_H

@@ -146,6 +146,54 @@ def test_tensor_core_path_tf32_bound(name, built_library):
                     init=initial_parameters(case), delta_tol=DELTA_TOL_TF32)
 
 
+# Layers outside the run of identical square layers whose batch, input and output width are all
+# multiples of 256 run on the same CTA-pair tensor-core kernels, one launch per layer.
+RECTANGULAR = {
+    # 512->256 below and 256->512 above a run of two 256x256 layers, 512->10 on the CUDA cores
+    "dkp_rectangular_around_run": dict(
+        kind="dkp", sizes=[512, 256, 256, 256, 512, 10], batch=256, T=2, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="tanh")),
+    # no two identical layers at all: rectangular layers only
+    "dkp_rectangular_only": dict(
+        kind="dkp", sizes=[256, 512, 256, 768, 10], batch=256, T=3, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="gelu")),
+    # the shape class of the wide benchmark network: wide input layer, softmax head, Adam.
+    # (Adam's first steps move every element by about lr whatever its gradient, so an element
+    # whose gradient is zero to rounding may move the other way: the rates keep twice that inside
+    # the bound.)
+    "full_wide_input_ce_adam": dict(
+        kind="full", sizes=[768, 256, 256, 256, 10], batch=512, T=4, steps=3,
+        hyper=dict(lr=1e-4, ir=0.1, fl=1e-4, lmbda=0.0, act="gelu"),
+        options=dict(optimizer="ADAM", psi_optimizer="ADAM", cross_entropy=1)),
+}
+
+
+def _describe(case, precision):
+    import ctypes
+    from common import build_gpu_net
+    from deepity_b200 import _lib
+    net, _, _ = build_gpu_net(case, precision)
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(512)
+    lib.dpc_plan_describe(lib.dpcn_plan(net._h), buf, 512)
+    return buf.value.decode()
+
+
+@pytest.mark.parametrize("name", sorted(RECTANGULAR))
+@pytest.mark.parametrize("precision", ["fp32", "tf32"])
+def test_rectangular_layers_on_tensor_cores(name, precision, built_library):
+    case = RECTANGULAR[name]
+    text = _describe(case, precision)
+    first = case["sizes"][0], case["sizes"][1]
+    assert f"layer 0 ({first[0]}->{first[1]})" in text or "layers 0.." in text, text
+    adam = "optimizer" in case.get("options", {})
+    tol = TF32_TOL if precision == "tf32" else (ADAM_TOL if adam else TOL)
+    delta = DELTA_TOL_TF32 if precision == "tf32" else DELTA_TOL
+    compare_outputs(run_oracle(case), run_gpu(case, precision=precision), tol, f"{name} {precision}",
+                    init=None if adam else initial_parameters(case),
+                    delta_tol=None if adam else delta)
+
+
 def test_adam_on_tensor_core_layers(built_library):
     """Adam / AdamW weight updates of the tensor-core layers: product into the staging buffer,
     optimizer as an elementwise kernel; FullPC's decayed direct-feedback update on tensor cores."""
