@@ -534,9 +534,28 @@ static int forward_simt(dpc_plan* p, int first, int count, int flags)
       max_tiles(p, f, c, OP_FWD, tx, ty);
       if (tx == 0)
         continue;
-      dim3 grid(tx, ty, c);
-      pc_gemm_kernel<OP_FWD><<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, flags, 0,
-                                                       p->energy);
+      // heads (at most 16 output units) with vector-loadable rows: one warp per batch row
+      bool narrow = true;
+      for (int i = f; i < f + c && narrow; ++i)
+      {
+        const dpc_layer& L = p->h[i];
+        if (L.next_size <= 0)
+          continue;
+        narrow = L.next_size <= 16 && L.size % 4 == 0 && L.size >= 128 &&
+                 !(L.flags & DPC_LAYER_INPUT_ACT) && ((uintptr_t)L.z % 16) == 0 &&
+                 ((uintptr_t)L.W % 16) == 0;
+      }
+      if (narrow)
+      {
+        dim3 grid(cdiv(p->batch, NTHREADS / 32), 1, c);
+        narrow_forward_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, flags, p->energy);
+      }
+      else
+      {
+        dim3 grid(tx, ty, c);
+        pc_gemm_kernel<OP_FWD><<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, flags, 0,
+                                                         p->energy);
+      }
     }
     int rc = check_launch(p->ctx, "forward kernel");
     if (rc != DPC_OK)

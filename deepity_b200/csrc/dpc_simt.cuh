@@ -129,6 +129,106 @@ __device__ __forceinline__ void block_energy_add(float local, double* energy)
 }
 
 // ---------------------------------------------------------------------------------------
+// Forward pass of narrow layers (at most 16 output units: the heads, e.g. 1024 -> 10).  The tiled
+// kernel below gives such a layer one column of 64 x 64 tiles, i.e. batch/64 CTAs that each walk
+// all of K: latency-bound (96 us for 4096 x 10 x 1024 against 3 us of traffic).  Here a warp owns
+// one batch row: its lanes stride over K with 16-byte loads of the row and of the (L1-resident)
+// weight rows, the partial dot products are reduced by shuffles, and lane j finishes output unit
+// j with the same epilogue as the tiled kernel.  Needs size % 4 == 0 and 16-byte aligned z, W.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NTHREADS)
+    narrow_forward_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
+                          int flags, double* energy)
+{
+  const int li = first + blockIdx.z;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0)
+    return;
+  const int N = L.next_size, K = L.size;
+  const dpc_layer* Lup = (li + 1 < n_layers) ? &layers[li + 1] : nullptr;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (NTHREADS / 32) + warp;
+  const bool row_ok = m < batch;
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    acc[j] = 0.0f;
+  if (row_ok)
+  {
+    const float* zrow = L.z + (size_t)m * K;
+    for (int k = lane * 4; k < K; k += 128)
+    {
+      const float4 zv = *reinterpret_cast<const float4*>(zrow + k);
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+      {
+        if (j < N)
+        {
+          const float4 wv = __ldg(reinterpret_cast<const float4*>(L.W + (size_t)j * K + k));
+          acc[j] = fmaf(zv.x, wv.x, acc[j]);
+          acc[j] = fmaf(zv.y, wv.y, acc[j]);
+          acc[j] = fmaf(zv.z, wv.z, acc[j]);
+          acc[j] = fmaf(zv.w, wv.w, acc[j]);
+        }
+      }
+    }
+  }
+  // all lanes end up with every sum; lane j keeps sum j
+  float mine = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+  {
+    float v = acc[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == j)
+      mine = v;
+  }
+  float esum = 0.0f;
+  const bool next_ce = Lup && (Lup->flags & DPC_LAYER_SOFTMAX_CE);
+  const bool do_err = (flags & DPC_FWD_ERR_NEXT) && Lup && !next_ce;
+  const bool do_fe = (flags & DPC_FWD_FE) && Lup && !(next_ce && (flags & DPC_FWD_ERR_NEXT));
+  const bool do_copy = (flags & DPC_FWD_COPY_NEXT) && Lup;
+  if (row_ok && lane < N)
+  {
+    const int n = lane;
+    const size_t o = (size_t)m * N + n;
+    const float pre = L.a * mine + L.b[n];
+    float mu, d = 1.0f;
+    if (do_fe)
+      act_both(L.act, pre, mu, d);
+    else
+      mu = act_fwd(L.act, pre);
+    if (L.flags & DPC_LAYER_RESIDUAL)
+      mu += L.z[o];
+    if (!(flags & DPC_FWD_TRANSIENT))
+    {
+      const bool no_mu = do_copy && (flags & DPC_FWD_NO_MU);
+      if (L.preact && !(no_mu && (flags & DPC_FWD_NO_PREACT)))
+        L.preact[o] = pre;
+      if (!no_mu)
+        L.mu[o] = mu;
+    }
+    if (do_copy)
+      Lup->z[o] = mu;
+    float e = 0.0f;
+    if (do_err)
+    {
+      e = (do_copy ? mu : Lup->z[o]) - mu;
+      Lup->e[o] = e;
+      esum += e * e;
+    }
+    else if (do_fe)
+      e = Lup->e[o];
+    if (do_fe)
+      L.fe[o] = e * d;
+  }
+  if (flags & DPC_FWD_ENERGY)
+    block_energy_add(do_err ? esum : 0.0f, energy);
+}
+
+// ---------------------------------------------------------------------------------------
 // The grouped GEMM kernel.  OP selects operand layouts and the fused epilogue.
 // ---------------------------------------------------------------------------------------
 template <int OP>
