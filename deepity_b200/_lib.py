@@ -36,6 +36,7 @@ SIGNATURES = {
     "dpc_alloc_host": (_i, [_vp, ctypes.c_size_t, ctypes.POINTER(_vp)]),
     "dpc_free_host": (_i, [_vp, _vp]),
     "dpc_sync": (_i, [_vp]),
+    "dpc_gather_rows": (_i, [_vp, _vp, _vp, _i64, _i, _i64, _vp]),
     "dpc_graph_begin": (_i, [_vp, _i]),
     "dpc_graph_end": (_i, [_vp, _i]),
     "dpc_graph_launch": (_i, [_vp, _i]),

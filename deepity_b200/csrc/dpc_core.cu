@@ -257,6 +257,43 @@ int dpc_sync(dpc_ctx* ctx)
   return DPC_OK;
 }
 
+namespace dpc
+{
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int64_t* __restrict__ index,
+                                   int64_t first, int rows, int64_t cols, float* __restrict__ dst,
+                                   int vec)
+{
+  const int64_t per_row = vec ? cols / 4 : cols;
+  const int64_t total = (int64_t)rows * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x)
+  {
+    const int64_t r = i / per_row, c = i - r * per_row;
+    const int64_t s = index[first + r];
+    if (vec)
+      reinterpret_cast<float4*>(dst + r * cols)[c] =
+          __ldg(reinterpret_cast<const float4*>(src + s * cols) + c);
+    else
+      dst[r * cols + c] = src[s * cols + c];
+  }
+}
+} // namespace dpc
+
+int dpc_gather_rows(dpc_ctx* ctx, const float* src_dev, const int64_t* index_dev, int64_t first,
+                    int rows, int64_t cols, float* dst_dev)
+{
+  if (!ctx || !src_dev || !index_dev || !dst_dev || rows < 0 || cols <= 0 || first < 0)
+    return fail(DPC_ERR_INVALID, "dpc_gather_rows: bad argument");
+  if (rows == 0)
+    return DPC_OK;
+  const int vec = cols % 4 == 0 && ((uintptr_t)src_dev % 16) == 0 && ((uintptr_t)dst_dev % 16) == 0;
+  const int64_t total = (int64_t)rows * (vec ? cols / 4 : cols);
+  const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)ctx->sm_count * 16);
+  dpc::gather_rows_kernel<<<blocks, 256, 0, ctx->stream>>>(src_dev, index_dev, first, rows, cols,
+                                                          dst_dev, vec);
+  return check_launch(ctx, "gather_rows kernel");
+}
+
 int dpc_graph_begin(dpc_ctx* ctx, int slot)
 {
   if (!ctx || slot < 0 || slot >= dpc_ctx::kSlots)

@@ -248,11 +248,19 @@ class _Network:
         return out.reshape(self.batch_size, self.terminal_size)
 
     def fit(self, X, Y, epochs: int, inference_steps: int = 1, initial_lr: Optional[float] = None,
-            decay_rate: float = 1.0, shuffle: bool = True, verbose: bool = False):
-        """Epoch loop of ``deepity/utils.py:19-143`` without the progress bars."""
+            decay_rate: float = 1.0, shuffle: bool = True, verbose: bool = False,
+            device_resident: bool = True):
+        """Epoch loop of ``deepity/utils.py:19-143`` without the progress bars.
+
+        ``device_resident`` (default): the data set is uploaded once, every epoch's permutation
+        (``np.random.permutation``, as in the reference, so a seeded run visits the same batches)
+        goes up as an index vector, and each mini-batch is gathered on the device straight into the
+        step's inputs -- no host slicing, no per-batch upload, no host synchronisation except one
+        energy read per epoch (every step when ``verbose``).  ``device_resident=False`` slices on
+        the host and calls ``train_step`` per batch."""
         self._require_configured()
-        X = np.asarray(X, dtype=np.float32)
-        Y = np.asarray(Y, dtype=np.float32)
+        X = np.ascontiguousarray(X, dtype=np.float32)
+        Y = np.ascontiguousarray(Y, dtype=np.float32)
         n, bsz = len(X), self.batch_size
         if n == 0:
             raise ValueError("Training data cannot be empty.")
@@ -260,15 +268,47 @@ class _Network:
             raise ValueError(f"Number of samples ({n}) must be divisible by batch_size ({bsz}).")
         if initial_lr is None:
             initial_lr = self._learning_rate
-        for epoch in range(epochs):
-            self.set_learning_rate(initial_lr * (decay_rate ** epoch))
-            idx = np.random.permutation(n) if shuffle else np.arange(n)
-            total = 0.0
-            for b in range(n // bsz):
-                sel = idx[b * bsz:(b + 1) * bsz]
-                total += self.train_step(X[sel], Y[sel], inference_steps)
-            if verbose:
-                print(f"epoch {epoch + 1} avg energy = {total / (n // bsz):.4f}")
+        batches = n // bsz
+        if not device_resident:
+            for epoch in range(epochs):
+                self.set_learning_rate(initial_lr * (decay_rate ** epoch))
+                idx = np.random.permutation(n) if shuffle else np.arange(n)
+                total = 0.0
+                for b in range(batches):
+                    sel = idx[b * bsz:(b + 1) * bsz]
+                    total += self.train_step(X[sel], Y[sel], inference_steps)
+                if verbose:
+                    print(f"epoch {epoch + 1} avg energy = {total / batches:.4f}")
+            return self
+
+        import torch
+        lib = self._lib
+        ctx = lib.dpcn_context(self._h)
+        device = torch.device("cuda", self._device_index)
+        stream = torch.cuda.ExternalStream(lib.dpc_stream(ctx), device=device)
+        X2, Y2 = X.reshape(n, -1), Y.reshape(n, -1)
+        with torch.cuda.stream(stream):
+            Xd = torch.from_numpy(X2).to(device)
+            Yd = torch.from_numpy(Y2).to(device)
+            xb = torch.empty((bsz, X2.shape[1]), dtype=torch.float32, device=device)
+            yb = torch.empty((bsz, Y2.shape[1]), dtype=torch.float32, device=device)
+            for epoch in range(epochs):
+                self.set_learning_rate(initial_lr * (decay_rate ** epoch))
+                idx = np.random.permutation(n) if shuffle else np.arange(n)
+                order = torch.from_numpy(np.ascontiguousarray(idx, dtype=np.int64)).to(device)
+                total = 0.0
+                for b in range(batches):
+                    for src, dst in ((Xd, xb), (Yd, yb)):
+                        _lib.check(lib.dpc_gather_rows(
+                            ctx, ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(order.data_ptr()),
+                            b * bsz, bsz, src.shape[1], ctypes.c_void_p(dst.data_ptr())))
+                    read = verbose or b == batches - 1
+                    energy = self.train_step_device(xb, yb, inference_steps, read_energy=read)
+                    if verbose:
+                        total += energy
+                if verbose:
+                    print(f"epoch {epoch + 1} avg energy = {total / batches:.4f}")
+            stream.synchronize()
         return self
 
     def set_gradient_sync(self, reduce_fn, global_batch: int) -> None:

@@ -133,6 +133,12 @@ DPC_API int dpc_copy_d2h_sync(dpc_ctx* ctx, void* host_dst, const void* src, siz
 DPC_API int dpc_alloc_host(dpc_ctx* ctx, size_t bytes, void** out); /* pinned */
 DPC_API int dpc_free_host(dpc_ctx* ctx, void* ptr);
 DPC_API int dpc_sync(dpc_ctx* ctx); /* IComputeBackend::Synchronize */
+/* dst[r, :] = src[index[first + r], :] for r in [0, rows), rows of `cols` floats, all pointers
+ * device memory, ordered on the context's stream.  The mini-batch gather of an epoch loop over a
+ * data set that stays on the device (deepity/utils.py:19-143 slices a shuffled host array per
+ * batch instead). */
+DPC_API int dpc_gather_rows(dpc_ctx* ctx, const float* src_dev, const int64_t* index_dev,
+                            int64_t first, int rows, int64_t cols, float* dst_dev);
 
 /* CUDA graphs (IComputeBackend::BeginGraphCapture/EndGraphCapture/ReplayGraph,
  * src/backend/cuda/CUDABackendCore.cu:120-187).  slot in [0, 8). */
