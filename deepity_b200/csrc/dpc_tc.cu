@@ -84,6 +84,8 @@ struct TcState
   __nv_bfloat16 *zp = nullptr, *fep = nullptr, *wp = nullptr;
   CUtensorMap zp_km, zp_km64, zp_mn, fep_km, fep_mn, wp_km128, wp_km64, wp_mn;
   CUtensorMap e_st, fep_st; // bulk-store maps: errors (fp32) and feedback-error planes (bf16)
+  CUtensorMap z_st, zp_st;  // beliefs (fp32) and their planes, for the feedback kernel
+  CUtensorMap w_st, wp_st;  // weights (fp32) and their planes, for the weight kernel
   bool store_maps = false;
   std::vector<uint8_t> dirty[3];
   bool planes = false;
@@ -617,14 +619,21 @@ struct Cfg
   // layer's operands are in flight at once (three stages left the fourth k-block waiting for a
   // stage to drain: one more load latency on the dependent path of every layer).
   static constexpr bool TSTORE = PRE && PAIR && OP == TC_FWD; // staged epilogue outputs
+  // Pair-mode feedback kernel on pre-split operands: the error and the belief of the tile come in
+  // through shared memory (16-column boxes filled by a TMA warp), the updated belief is written
+  // back into its box and leaves, with its operand planes, through bulk tensor stores.
+  static constexpr bool FBIO = PRE && PAIR && OP == TC_FB;
+  // ... and the weight kernel likewise: the weight tile comes in through 16-column boxes, is
+  // updated in place and leaves with its planes through bulk tensor stores.
+  static constexpr bool WGIO = PRE && PAIR && OP == TC_WG;
   static constexpr int STAGES = B16 ? NR
-                                : TSTORE ? 2
+                                : (TSTORE || FBIO || WGIO) ? 2
                                 : (PRE && KS == 2) ? 4
                                 : (STAGES_RAW < 2 ? 2 : (STAGES_RAW > 8 ? 8 : STAGES_RAW));
   static constexpr int RING_BYTES = B16 ? (NR + NB) * RAWB : STAGES * STAGE_BYTES;
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS =
-      (2 + EPI_WARPS + (SPLITW ? 4 : 0) + ((PAIR && OP == TC_FWD) ? 1 : 0)) * 32;
+      (2 + EPI_WARPS + (SPLITW ? 4 : 0) + ((PAIR && (OP == TC_FWD || FBIO || WGIO)) ? 1 : 0)) * 32;
   // K-split sweep on pre-split operands: a narrow tile's main loop is bound by the shared-memory
   // reads of its MMAs (every tcgen05.mma reads its A and B tiles again: 6 KB for 128x64x16).  The
   // "hi" and "mid" tiles of B lie back to back in a stage, so ONE instruction with N = 2 BN
@@ -641,10 +650,14 @@ struct Cfg
   // Pair-mode forward: the operand of the layer above (128 rows x 32 columns per box, 16 KB)
   // arrives through IN_BUFS shared-memory buffers filled by a dedicated TMA warp.
   static constexpr bool STAGE_IN = PAIR && OP == TC_FWD;
-  static constexpr int IN_BYTES = BM * 32 * 4;
-  static constexpr int IN_BUFS = STAGE_IN ? (THREE_X ? 2 : 4) : 0;
-  // two 4 KB output buffers per epilogue warp
-  static constexpr int OUT_BYTES = TSTORE ? EPI_WARPS * 2 * 4096 : 0;
+  // FBIO: [error: 128 rows x 64 B][belief: 128 rows x 64 B] per buffer, 64-byte swizzle
+  // WGIO: [weights: 128 rows x 64 B] per buffer
+  static constexpr int IN_BYTES = FBIO ? 2 * BM * 16 * 4 : WGIO ? BM * 16 * 4 : BM * 32 * 4;
+  static constexpr int IN_BUFS = STAGE_IN ? (THREE_X ? 2 : 4) : ((FBIO || WGIO) ? 4 : 0);
+  // forward: two 4 KB output buffers per epilogue warp; feedback: one 2 KB buffer per warp for the
+  // planes (the belief itself is updated in place in its input box)
+  static constexpr int OUT_BYTES =
+      TSTORE ? EPI_WARPS * 2 * 4096 : ((FBIO || WGIO) ? EPI_WARPS * 2048 : 0);
   static constexpr int SMEM_BYTES =
       RING_BYTES + IN_BUFS * IN_BYTES + OUT_BYTES + RX_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static_assert(SMEM_BYTES <= 232448, "more than the 227 KB of shared memory a CTA can have");
@@ -716,7 +729,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
     for (int b = 0; b < C::IN_BUFS; ++b)
     {
       mbar_init(&in_full[b], 1);
-      mbar_init(&in_empty[b], C::EPI_WARPS);
+      mbar_init(&in_empty[b], (C::FBIO || C::WGIO) ? C::EPI_WARPS / 2 : C::EPI_WARPS);
     }
     mbar_init(rx_full, 1);
     mbar_init(pub, C::EPI_WARPS);
@@ -1061,9 +1074,11 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         in.map_e = &mapSE, in.map_fe = &mapSF;
         in.out_row0 = m - lane; // the row of this warp's lane 0
         in.layer_e = li + 1 - P.run_first, in.layer_fe = li - P.run_first;
-        // (one 16-column chunk per warp: the narrow tiles of the sweep)
-        deferred = P.chain && (BNE / GROUPS == 16) && (P.flags & DPC_FWD_COPY_NEXT) && active &&
-                   meta.up_z != nullptr;
+        // (one 16-column chunk per warp: the narrow tiles of the sweep; only where the next
+        // layer's tensor cores read the operand planes -- in the other schemes the fp32 belief
+        // IS the operand and must be stored before the publication)
+        deferred = C::PRE && P.chain && (BNE / GROUPS == 16) && (P.flags & DPC_FWD_COPY_NEXT) &&
+                   active && meta.up_z != nullptr && meta.upz_hi != nullptr;
         in.defer = deferred ? defer_z : nullptr, in.defer_o = &defer_o;
         if (KS == 2)
         {
@@ -1118,6 +1133,75 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         const dpc_layer L = P.layers[li];
         const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
         __nv_bfloat16* z_hi = P.zp ? P.zp + 2 * (long long)(li - P.run_first) * P.act_elems : nullptr;
+        if (C::FBIO && P.tstore)
+        {
+          // 16-column chunks; the two warp groups take alternate chunks, so every box is read
+          // by the four warps of one group (one 32-row quarter each).
+          const int row = quarter * 32 + lane;
+          const int lz = li - P.run_first;
+          uint8_t* obuf = out_base + (warp - 2) * 2048;
+          bool ok = true;
+          for (int c = grp; c < BN / 16 && ok; c += GROUPS)
+          {
+            const uint32_t q = (uint32_t)tile_iter * (uint32_t)(BN / 16) + (uint32_t)c;
+            constexpr uint32_t NBUF = C::IN_BUFS > 0 ? C::IN_BUFS : 1;
+            const uint32_t b = q & (NBUF - 1);
+            if (!mbar_wait(&in_full[b], (q / NBUF) & 1u, abort_flag))
+            {
+              ok = false;
+              break;
+            }
+            uint8_t* ebuf = in_base + b * C::IN_BYTES;
+            uint8_t* zbuf = ebuf + BM * 64;
+            float ee[16], zz[16], v[16];
+            const int sw = (row >> 1) & 3;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+            {
+              const float4 x = *reinterpret_cast<const float4*>(ebuf + row * 64 + ((i ^ sw) << 4));
+              const float4 y = *reinterpret_cast<const float4*>(zbuf + row * 64 + ((i ^ sw) << 4));
+              ee[4 * i] = x.x, ee[4 * i + 1] = x.y, ee[4 * i + 2] = x.z, ee[4 * i + 3] = x.w;
+              zz[4 * i] = y.x, zz[4 * i + 1] = y.y, zz[4 * i + 2] = y.z, zz[4 * i + 3] = y.w;
+            }
+            tc_ld16(taddr + c * 16, v);
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+              zz[k] += L.ir * (L.a * v[k] - ee[k]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<float4*>(zbuf + row * 64 + ((i ^ sw) << 4)) =
+                  make_float4(zz[4 * i], zz[4 * i + 1], zz[4 * i + 2], zz[4 * i + 3]);
+#pragma unroll
+            for (int k = 0; k < 16; k += 8)
+            {
+              // 32-byte rows, 16-byte chunks xor-ed with (row >> 2) & 1: the 32-byte swizzle
+              uint4 h, mm;
+              split8(make_float4(zz[k], zz[k + 1], zz[k + 2], zz[k + 3]),
+                     make_float4(zz[k + 4], zz[k + 5], zz[k + 6], zz[k + 7]), h, mm);
+              const int off = lane * 32 + ((((k >> 3) & 1) ^ ((lane >> 2) & 1)) << 4);
+              *reinterpret_cast<uint4*>(obuf + off) = h;
+              *reinterpret_cast<uint4*>(obuf + 1024 + off) = mm;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+            {
+              const int col = n0 + c * 16, row0 = m - lane;
+              tma_store_3d(&mapSE, zbuf + quarter * 2048, col, row0, lz);
+              tma_store_3d(&mapSF, obuf, col, row0, 2 * lz);
+              tma_store_3d(&mapSF, obuf + 1024, col, row0, 2 * lz + 1);
+              bulk_commit();
+              // the stores have read their shared memory: the box may be refilled, the plane
+              // buffer rewritten
+              bulk_wait_read<0>();
+              mbar_arrive(&in_empty[b]);
+            }
+            __syncwarp();
+          }
+          if (!ok)
+            break;
+        }
+        else
         for (int c = grp; c < BN / 32; c += GROUPS)
         {
           const size_t o = (size_t)m * P.N + n0 + c * 32;
@@ -1200,6 +1284,70 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
               st8(L.g_W + o + k, &v[k]);
           }
         }
+        else if (C::WGIO && P.tstore)
+        {
+          const int row = quarter * 32 + lane;
+          const int lw = li - P.run_first;
+          uint8_t* obuf = out_base + (warp - 2) * 2048;
+          bool ok = true;
+          for (int c = grp; c < BN / 16 && ok; c += GROUPS)
+          {
+            constexpr uint32_t NBUF = C::IN_BUFS > 0 ? C::IN_BUFS : 1;
+            const uint32_t q = (uint32_t)tile_iter * (uint32_t)(BN / 16) + (uint32_t)c;
+            const uint32_t b = q & (NBUF - 1);
+            if (!mbar_wait(&in_full[b], (q / NBUF) & 1u, abort_flag))
+            {
+              ok = false;
+              break;
+            }
+            uint8_t* wbuf = in_base + b * C::IN_BYTES;
+            float w[16], v[16];
+            const int sw = (row >> 1) & 3;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+            {
+              const float4 x = *reinterpret_cast<const float4*>(wbuf + row * 64 + ((i ^ sw) << 4));
+              w[4 * i] = x.x, w[4 * i + 1] = x.y, w[4 * i + 2] = x.z, w[4 * i + 3] = x.w;
+            }
+            tc_ld16(taddr + c * 16, v);
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+            {
+              if (decay != 1.0f)
+                w[k] *= decay;
+              w[k] = fmaf(alpha, v[k], w[k]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<float4*>(wbuf + row * 64 + ((i ^ sw) << 4)) =
+                  make_float4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+#pragma unroll
+            for (int k = 0; k < 16; k += 8)
+            {
+              uint4 h, mm;
+              split8(make_float4(w[k], w[k + 1], w[k + 2], w[k + 3]),
+                     make_float4(w[k + 4], w[k + 5], w[k + 6], w[k + 7]), h, mm);
+              const int off = lane * 32 + ((((k >> 3) & 1) ^ ((lane >> 2) & 1)) << 4);
+              *reinterpret_cast<uint4*>(obuf + off) = h;
+              *reinterpret_cast<uint4*>(obuf + 1024 + off) = mm;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+            {
+              const int col = n0 + c * 16, row0 = m - lane;
+              tma_store_3d(&mapSE, wbuf + quarter * 2048, col, row0, lw);
+              tma_store_3d(&mapSF, obuf, col, row0, 2 * lw);
+              tma_store_3d(&mapSF, obuf + 1024, col, row0, 2 * lw + 1);
+              bulk_commit();
+              bulk_wait_read<0>();
+              mbar_arrive(&in_empty[b]);
+            }
+            __syncwarp();
+          }
+          if (!ok)
+            break;
+        }
         else
         {
         __nv_bfloat16* w_hi = P.wp ? P.wp + 2 * (long long)(li - P.run_first) * P.w_elems : nullptr;
@@ -1267,7 +1415,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           mbar_arrive(&tempty[acc]);
       }
     }
-    if (C::TSTORE && lane == 0)
+    if ((C::TSTORE || C::FBIO || C::WGIO) && lane == 0)
       bulk_wait_all(); // this warp's bulk stores are complete before its shared memory goes away
     if (OP == TC_FWD && (P.flags & DPC_FWD_ENERGY))
     {
@@ -1306,6 +1454,48 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           mbar_expect_tx(&in_full[b], C::IN_BYTES);
           tma_load_3d(in_base + b * C::IN_BYTES, &mapU, &in_full[b], n0 + 32 * j, m0, lcoord);
+        }
+      }
+    }
+  }
+  else if ((C::FBIO || C::WGIO) && warp == 2 + C::EPI_WARPS)
+  {
+    // ---------------------------------------------------------------- staged error / belief loader
+    // This CTA's 128 rows of the layer's error and belief, one 16-column chunk at a time, each as
+    // four 32-row slices (the box shape of the store maps, which also serve as load maps).
+    if (lane == 0 && P.tstore)
+    {
+      uint32_t q = 0;
+      bool alive = true;
+      for (int t = t_begin; t < t_end && alive; t += t_step)
+      {
+        const int lrel = t / tiles_per_layer, rem = t % tiles_per_layer;
+        const int m0 = (rem / P.tiles_n) * C::TILE_M + (int)rank * BM;
+        const int n0 = (rem % P.tiles_n) * BN;
+        const int lcoord = P.first + lrel - P.run_first;
+        for (int c = 0; c < BN / 16; ++c, ++q)
+        {
+          constexpr uint32_t NBUF = C::IN_BUFS > 0 ? C::IN_BUFS : 1;
+          const uint32_t b = q & (NBUF - 1);
+          if (!mbar_wait(&in_empty[b], ((q / NBUF) & 1u) ^ 1u, abort_flag))
+          {
+            alive = false;
+            break;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_expect_tx(&in_full[b], C::IN_BYTES);
+          uint8_t* ebuf = in_base + b * C::IN_BYTES;
+          uint8_t* zbuf = ebuf + BM * 64;
+          for (int s4 = 0; s4 < BM / 32; ++s4)
+          {
+            if (C::WGIO) // the weight tile alone
+              tma_load_3d(ebuf + s4 * 2048, &mapSE, &in_full[b], n0 + 16 * c, m0 + 32 * s4, lcoord);
+            else
+            {
+              tma_load_3d(ebuf + s4 * 2048, &mapU, &in_full[b], n0 + 16 * c, m0 + 32 * s4, lcoord);
+              tma_load_3d(zbuf + s4 * 2048, &mapSE, &in_full[b], n0 + 16 * c, m0 + 32 * s4, lcoord);
+            }
+          }
         }
       }
     }
@@ -1517,9 +1707,12 @@ template <int OP, int BN, int THREE_X, int BM = 128, bool PAIR = false, int KS =
 int launch(dpc_plan* p, TcState* st, const CUtensorMap& a, const CUtensorMap& b, TcParams P,
            const CUtensorMap* up = nullptr)
 {
-  const CUtensorMap& u = up ? *up : a; // unused unless P.stage_in
-  const CUtensorMap& se = P.tstore ? st->e_st : a; // unused unless P.tstore
-  const CUtensorMap& sf = P.tstore ? st->fep_st : a;
+  // forward: up = staged operand of the layer above, stores of errors and fe planes; feedback:
+  // loads of the layer's error, loads and stores of its belief, stores of the belief's planes
+  const CUtensorMap& u = (OP == TC_FB && P.tstore) ? st->e_st : (up ? *up : a);
+  const CUtensorMap& se = P.tstore ? (OP == TC_FB ? st->z_st : OP == TC_WG ? st->w_st : st->e_st) : a;
+  const CUtensorMap& sf =
+      P.tstore ? (OP == TC_FB ? st->zp_st : OP == TC_WG ? st->wp_st : st->fep_st) : a;
   using C = Cfg<OP, BN, THREE_X, BM, PAIR, KS>;
   static bool configured = false;
   auto kern = pc_tc_kernel<OP, BN, THREE_X, BM, PAIR, KS>;
@@ -1786,7 +1979,11 @@ static bool run_init(dpc_plan* plan, TcState* st, int best_first, int best_count
     // up_maps above): one store map covers them
     st->store_maps =
         make_store_map(&st->e_st, L0.e, false, H, B, best_count + 1, plan->run.z_stride) &&
-        make_store_map(&st->fep_st, st->fep, true, H, B, 2 * best_count, (int64_t)B * H);
+        make_store_map(&st->fep_st, st->fep, true, H, B, 2 * best_count, (int64_t)B * H) &&
+        make_store_map(&st->z_st, L0.z, false, H, B, best_count + 1, plan->run.z_stride) &&
+        make_store_map(&st->zp_st, st->zp, true, H, B, 2 * (best_count + 1), (int64_t)B * H) &&
+        make_store_map(&st->w_st, L0.W, false, H, H, best_count, plan->run.w_stride) &&
+        make_store_map(&st->wp_st, st->wp, true, H, H, 2 * best_count, (int64_t)H * H);
   }
   if (!st->planes && !getenv("DPC_DISABLE_PLANES") && split_scheme(plan) == 2 && pair_ok(B, H))
   {
@@ -2141,6 +2338,13 @@ int tc_update_state(dpc_plan* p, int first, int count)
       if ((rc = planes_need(p, st, PL_FE, r0, r0 + count)) != DPC_OK ||
           (rc = planes_need(p, st, PL_W, r0, r0 + count)) != DPC_OK)
         return rc;
+      // plain updates (no momentum, no residual term) take their error and belief through
+      // shared memory and write belief and planes with bulk stores
+      bool plain = st->store_maps && !getenv("DPC_DISABLE_STAGED_OUTPUT") &&
+                   !getenv("DPC_DISABLE_STAGED_INPUT");
+      for (int i = first; i < first + count && plain; ++i)
+        plain = !p->h[i].v && !(p->h[i].flags & DPC_LAYER_RESIDUAL);
+      P.tstore = plain ? 1 : 0;
       rc = launch<TC_FB, 256, 3, 128, true>(p, st, st->fep_km, st->wp_mn, P);
     }
     else
@@ -2202,6 +2406,12 @@ int tc_weight_gemm(dpc_plan* p, int first, int count, int mode, int decay_w)
       if ((rc = planes_need(p, st, PL_FE, r0, r0 + count)) != DPC_OK ||
           (rc = planes_need(p, st, PL_Z, r0, r0 + count)) != DPC_OK)
         return rc;
+      // in-place SGD updates take the weight tile through shared memory and write it and its
+      // planes back with bulk stores
+      P.tstore = (st->store_maps && !(mode & WG_GRAD_MODE) && !getenv("DPC_DISABLE_STAGED_OUTPUT") &&
+                  !getenv("DPC_DISABLE_STAGED_INPUT"))
+                     ? 1
+                     : 0;
       rc = launch<TC_WG, 256, 3, 128, true>(p, st, st->fep_mn, st->zp_mn, P);
     }
     else

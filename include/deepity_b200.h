@@ -28,8 +28,8 @@
  *   DPC_DISABLE_PLANES         3xBF16 operands split inside the kernels, not pre-split copies
  *   DPC_KEEP_FE_FP32           keep writing the fp32 feedback errors beside their bf16 copies
  *   DPC_DISABLE_STAGED_INPUT / DPC_DISABLE_STAGED_OUTPUT
- *                              forward epilogue reads / writes global memory lane by lane
- *                              instead of through shared memory and bulk tensor copies
+ *                              epilogues of the pair-tile kernels read / write global memory lane
+ *                              by lane instead of through shared memory and bulk tensor copies
  *   DPC_DISABLE_KSPLIT         forward sweep without the two-CTA split of K
  *   DPC_DISABLE_RECTANGULAR    single layers outside the run of identical square layers stay on
  *                              the CUDA-core kernels even where their shapes fit the pair tiles
