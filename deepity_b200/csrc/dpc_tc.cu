@@ -854,7 +854,11 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
             // The rows of this layer's input are the previous layer's output: wait until every
             // tile of that row block has been published (the weights above are already on
             // their way).
-            if (!chain_wait(&P.chain_counters[(t - 1) * P.tiles_m + m0 / C::TILE_M], P.chain_target,
+            // K-split: this CTA's half of K is the output of half of the previous layer's column
+            // tiles, which count themselves in on a counter of their own (fewer CTAs to wait for)
+            const int dep = KS == 2 ? ((t - 1) * P.tiles_m + m0 / C::TILE_M) * 2 + (int)krank
+                                    : (t - 1) * P.tiles_m + m0 / C::TILE_M;
+            if (!chain_wait(&P.chain_counters[dep], P.chain_target,
                             abort_flag))
               alive = false; // the A copy below still runs so the stage's byte count completes
             trace_stamp(P, t, 0);
@@ -1394,7 +1398,11 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           if (mbar_wait(pub, (uint32_t)(tile_iter & 1), abort_flag))
           {
             asm volatile("fence.acq_rel.gpu;" ::: "memory");
-            atomicAdd(&P.chain_counters[lrel * P.tiles_m + rem / P.tiles_n], 1);
+            // (K-split: the counter of the half of K that this tile's columns belong to)
+            const int pub_idx =
+                KS == 2 ? (lrel * P.tiles_m + rem / P.tiles_n) * 2 + ((rem % P.tiles_n) * 2 >= P.tiles_n ? 1 : 0)
+                        : lrel * P.tiles_m + rem / P.tiles_n;
+            atomicAdd(&P.chain_counters[pub_idx], 1);
           }
         }
         if (OP == TC_FWD && deferred)
@@ -2289,8 +2297,8 @@ int tc_project_forward(dpc_plan* p, int first, int count, int flags)
   {
     TcParams Q = base_params(p, st, first, count, B, H, H, 64, flags, 0);
     Q.chain = 1, Q.chain_counters = st->chain_counters, Q.trace = st->trace;
-    // column tiles x CTAs per tile
-    Q.chain_target = (H / 64) * 2 + st->chain_target_bias;
+    // CTAs that produce one half of K: half of the column tiles x CTAs per tile
+    Q.chain_target = (H / 64) + st->chain_target_bias;
     if (!tf32 && planes_on(p, st))
     {
       // the first layer's input and every layer's weights must be split; the sweep itself
