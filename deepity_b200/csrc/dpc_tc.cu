@@ -451,13 +451,11 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
         ld8(L.b + n0 + c * CW + k, bb);
 #pragma unroll
       for (int q = 0; q < 8; ++q)
-      {
         pre[q] = L.a * v[k + q] + bb[q];
-        if (do_fe)
-          act_both(act, pre[q], mu[q], d[q]);
-        else
-          mu[q] = act_fwd(act, pre[q]), d[q] = 1.0f;
-      }
+      if (do_fe)
+        act_both8<true>(act, pre, mu, d);
+      else
+        act_both8<false>(act, pre, mu, d);
       if (residual && active)
       {
         float zz[8];
@@ -549,8 +547,7 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
           tma_store_3d(in->map_e, obuf, col, in->out_row0, in->layer_e);
         if (do_fe)
         {
-          tma_store_3d(in->map_fe, obuf + 2048, col, in->out_row0, 2 * in->layer_fe);
-          tma_store_3d(in->map_fe, obuf + 3072, col, in->out_row0, 2 * in->layer_fe + 1);
+          tma_store_3d(in->map_fe, obuf + 2048, col, in->out_row0, 2 * in->layer_fe); // hi + mid
         }
         bulk_commit();
       }
@@ -1192,8 +1189,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
             {
               const int col = n0 + c * 16, row0 = m - lane;
               tma_store_3d(&mapSE, zbuf + quarter * 2048, col, row0, lz);
-              tma_store_3d(&mapSF, obuf, col, row0, 2 * lz);
-              tma_store_3d(&mapSF, obuf + 1024, col, row0, 2 * lz + 1);
+              tma_store_3d(&mapSF, obuf, col, row0, 2 * lz); // hi + mid
               bulk_commit();
               // the stores have read their shared memory: the box may be refilled, the plane
               // buffer rewritten
@@ -1341,8 +1337,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
             {
               const int col = n0 + c * 16, row0 = m - lane;
               tma_store_3d(&mapSE, wbuf + quarter * 2048, col, row0, lw);
-              tma_store_3d(&mapSF, obuf, col, row0, 2 * lw);
-              tma_store_3d(&mapSF, obuf + 1024, col, row0, 2 * lw + 1);
+              tma_store_3d(&mapSF, obuf, col, row0, 2 * lw); // hi + mid
               bulk_commit();
               bulk_wait_read<0>();
               mbar_arrive(&in_empty[b]);
@@ -1682,7 +1677,9 @@ bool make_store_map(CUtensorMap* map, const void* base, bool bf16, int cols, int
   const cuuint64_t eb = bf16 ? 2 : 4;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)planes};
   cuuint64_t strides[2] = {(cuuint64_t)cols * eb, (cuuint64_t)plane_elems * eb};
-  cuuint32_t box[3] = {16, 32, 1};
+  // bf16 planes: the hi and the mid plane of a layer (neighbours in the outer dimension) go out
+  // in ONE store from two adjacent 1 KB tiles
+  cuuint32_t box[3] = {16, 32, bf16 ? 2u : 1u};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
