@@ -231,11 +231,11 @@ def _cpu_net(w, hidden):
     return run, kind, sizes
 
 
-def cpu_reference_leg(w, steps, warmup, budget_s=25.0, sample_hidden=None):
+def cpu_reference_leg(w, steps, warmup, seconds_wanted=25.0, sample_hidden=None):
     """The reference's CPU train step on a depth-reduced copy of the workload.
 
     The sample depth is picked from a calibration step on a 16-layer cut so that
-    warmup + steps sample steps take about `budget_s` seconds (capped at 256 layers), unless
+    warmup + steps sample steps take about `seconds_wanted` seconds (capped at 256 layers), unless
     `sample_hidden` fixes it.  Threads: the reference's own DynamicThread policy first
     (include/deepity/utils/Optimize.h:108-131); if half the affinity mask is faster on this
     host (OpenMP plus OpenBLAS pools oversubscribing it), that count is used instead and both
@@ -266,7 +266,7 @@ def cpu_reference_leg(w, steps, warmup, budget_s=25.0, sample_hidden=None):
                  "ms_per_step_half_affinity_threads": t_half * 1e3,
                  "ms_per_layer_at_16": per_layer * 1e3}
         if sample_hidden is None:
-            want = budget_s / ((steps + warmup) * per_layer)
+            want = seconds_wanted / ((steps + warmup) * per_layer)
             sample_hidden = 256 if want >= 256 else 128 if want >= 128 else 64 if want >= 64 else 32
     hidden = min(full_hidden, sample_hidden or (64 if deep else full_hidden))
     run, kind, sizes = _cpu_net(w, hidden)
@@ -764,7 +764,7 @@ def main():
         if rank != 0:
             return
         # K steps and W warm-up steps of a bounded sample (see the module docstring)
-        leg = cpu_reference_leg(w, max(1, args.steps), max(1, args.warmup), budget_s=90.0,
+        leg = cpu_reference_leg(w, max(1, args.steps), max(1, args.warmup), seconds_wanted=90.0,
                                 sample_hidden=args.sample_depth)
         line = {"impl": "reference", "metric": "train_step samples/sec", "value": leg["value"],
                 "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
@@ -872,7 +872,7 @@ def main():
         print(f"bench: {paths['cuda_core_weight_layers']} weight layers of this workload run on the "
               f"CUDA-core kernels ({paths['kernels']})", file=sys.stderr)
     if not args.no_cpu:
-        leg = cpu_reference_leg(w, 5, 1, budget_s=25.0, sample_hidden=args.sample_depth)
+        leg = cpu_reference_leg(w, 5, 1, seconds_wanted=25.0, sample_hidden=args.sample_depth)
         line["cpu_baseline"] = cpu_keys(leg)
         if args.workload == "c3" and leg["kind"] == "reference":
             # the same cut on the GPU, same seeds and step count: the energies must agree

@@ -8,7 +8,7 @@ driver's tensor-map encoder at run time, so they have no link-time dependency be
 
 The plugin implements the reference's backend interface, so its vtable object is compiled
 against the reference's own interface header: it needs the reference checkout (environment
-variable DEEPITY_REFERENCE, default /root/reference) and a sleef.h (the reference's headers
+variable DEEPITY_REFERENCE, else the default location below) and a sleef.h (the reference's headers
 include it; the one shipped inside torch's include tree is used).  Without the checkout the
 plugin is skipped and a previously built libDeepityCUDA.so is used as is.
 """
