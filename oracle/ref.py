@@ -198,7 +198,8 @@ class RefConvNet:
     ``layers``: list of dicts(inC, outC, H, W, kH, kW, sH, sW, pH, pW, act); the last one has
     outC = 0 (the terminal layer)."""
 
-    def __init__(self, layers, batch, lr, ir, lmbda, optimizer="SGD", center_weights=False):
+    def __init__(self, layers, batch, lr, ir, lmbda, optimizer="SGD", center_weights=False,
+                 device="cpu"):
         L = lib()
         f32p = ctypes.POINTER(ctypes.c_float)
         L.refc_create.restype = ctypes.c_void_p
@@ -221,7 +222,15 @@ class RefConvNet:
         L.refc_predict.argtypes = [ctypes.c_void_p, f32p, ctypes.c_int64, ctypes.c_int,
                                    ctypes.c_int, f32p, ctypes.c_int64]
         self.L, self.batch, self.layers = L, batch, layers
-        self.h = ctypes.c_void_p(L.refc_create(batch))
+        if device == "cpu":
+            self.h = ctypes.c_void_p(L.refc_create(batch))
+        else:
+            # the reference's own device path, on whatever libDeepityCUDA.so its loader finds
+            L.refc_create_on_gpu.restype = ctypes.c_void_p
+            L.refc_create_on_gpu.argtypes = [ctypes.c_int]
+            self.h = ctypes.c_void_p(L.refc_create_on_gpu(batch))
+            if not self.h:
+                raise RuntimeError("the reference could not create its GPU backend")
         for d in layers:
             L.refc_add_layer(self.h, d["inC"], d["outC"], d["H"], d["W"], d["kH"], d["kW"],
                              d["sH"], d["sW"], d["pH"], d["pW"], lr, ir, lmbda, ACT[d["act"]])

@@ -3,7 +3,9 @@
 // (include/deepity/networks/SimpleConvPCNetwork.h), compiled together with the reference
 // sources where they lie.  Tensor names: "z" "e" "mu" "W" "b".
 #include <cstdint>
+#include <cstdio>
 #include <cstring>
+#include <exception>
 #include <memory>
 #include <string>
 #include <vector>
@@ -18,7 +20,13 @@ struct ConvNet
 {
   int batch;
   std::unique_ptr<SimpleConvPCNetwork> net;
+  int device; // 1: the tensors live in device memory (the network runs on the backend plugin)
 };
+
+IComputeBackend* BackendOf(ConvNet* n)
+{
+  return n->net->GetLayers().front()->GetBackend();
+}
 
 bool Find(ConvNet* n, int layer, const char* name, float** p, size_t* count)
 {
@@ -48,8 +56,23 @@ extern "C"
 {
 void* refc_create(int batch)
 {
-  auto* n = new ConvNet{batch, std::make_unique<SimpleConvPCNetwork>(batch)};
+  auto* n = new ConvNet{batch, std::make_unique<SimpleConvPCNetwork>(batch), 0};
   return n;
+}
+
+// The same network on DEVICE_GPU: the reference's loader then dlopens libDeepityCUDA.so from the
+// directory of this library.  NULL when that fails (no plugin, no usable device).
+void* refc_create_on_gpu(int batch)
+{
+  try
+  {
+    return new ConvNet{batch, std::make_unique<SimpleConvPCNetwork>(batch, DeviceType::DEVICE_GPU), 1};
+  }
+  catch (const std::exception& e)
+  {
+    fprintf(stderr, "refc_create_on_gpu: %s\n", e.what());
+    return nullptr;
+  }
 }
 
 void refc_destroy(void* h)
@@ -98,9 +121,13 @@ int refc_get_tensor(void* h, int layer, const char* name, float* out, int64_t co
 {
   float* p;
   size_t c = 0;
-  if (!Find(static_cast<ConvNet*>(h), layer, name, &p, &c) || (int64_t)c != count)
+  auto* n = static_cast<ConvNet*>(h);
+  if (!Find(n, layer, name, &p, &c) || (int64_t)c != count)
     return -1;
-  std::memcpy(out, p, c * sizeof(float));
+  if (n->device)
+    BackendOf(n)->CopyToHost(out, p, c);
+  else
+    std::memcpy(out, p, c * sizeof(float));
   return 0;
 }
 
@@ -108,9 +135,13 @@ int refc_set_tensor(void* h, int layer, const char* name, const float* in, int64
 {
   float* p;
   size_t c = 0;
-  if (!Find(static_cast<ConvNet*>(h), layer, name, &p, &c) || (int64_t)c != count)
+  auto* n = static_cast<ConvNet*>(h);
+  if (!Find(n, layer, name, &p, &c) || (int64_t)c != count)
     return -1;
-  std::memcpy(p, in, c * sizeof(float));
+  if (n->device)
+    BackendOf(n)->CopyFromHost(p, in, c);
+  else
+    std::memcpy(p, in, c * sizeof(float));
   return 0;
 }
 

@@ -71,11 +71,13 @@ def run_conv_oracle(case):
     return _collect(net.get, case, energies, pred)
 
 
-def run_conv_reference(case):
+def run_conv_reference(case, device="cpu"):
+    """device="gpu": the reference's own device path on whatever backend plugin its loader finds."""
     from oracle.ref import RefConvNet
     hy = case["hyper"]
     net = RefConvNet(case["layers"], case["batch"], hy["lr"], hy["ir"], hy["lmbda"],
-                     case.get("optimizer", "SGD"), bool(case.get("center_weights", 0)))
+                     case.get("optimizer", "SGD"), bool(case.get("center_weights", 0)),
+                     device=device)
     energies, pred = _drive(net, case)
     # only the fixtures are reduced to statistics; the implementations under test return tensors
     return _collect(net.get, case, energies, pred, stats=bool(case.get("stats_only")))
