@@ -95,9 +95,12 @@ struct TcState
   bool warned_fallback = false;
   // Single layers outside the run that still fit the CTA-pair kernels (batch, input and output
   // width all multiples of 256, e.g. a 3072 -> 1024 first layer): one set of tensor maps each.
+  // SimplePC layers (DPC_LAYER_INPUT_ACT) multiply f(z) instead of z and the error of the layer
+  // above instead of a feedback error: for them z_* cover zF and fe_* cover e of the layer above.
   struct Extra
   {
     int layer;
+    bool simple;
     CUtensorMap z_km, w_km128, fe_km, w_mn, fe_mn, z_mn;
   };
   std::vector<Extra> extras;
@@ -293,6 +296,9 @@ __device__ __forceinline__ void load_fwd_meta(const TcParams& P, int li, FwdMeta
 {
   const dpc_layer* Lp = &P.layers[li];
   M.a = Lp->a, M.flags = Lp->flags, M.act = Lp->act, M.b = Lp->b, M.z = Lp->z;
+  // SimplePC: the activation was applied to the operand (zF = f(z)); the prediction is linear
+  if (Lp->flags & DPC_LAYER_INPUT_ACT)
+    M.act = DPC_ACT_LINEAR;
   M.preact = Lp->preact, M.mu = Lp->mu, M.fe = Lp->fe;
   if (li + 1 < P.n_layers)
   {
@@ -342,7 +348,8 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
   const bool Lup = L.up_z != nullptr;
   const bool next_ce = Lup && (L.up_flags & DPC_LAYER_SOFTMAX_CE);
   const bool do_err = (P.flags & DPC_FWD_ERR_NEXT) && Lup && !next_ce;
-  const bool do_fe = (P.flags & DPC_FWD_FE) && Lup && !(next_ce && (P.flags & DPC_FWD_ERR_NEXT));
+  const bool do_fe = (P.flags & DPC_FWD_FE) && Lup && !(L.flags & DPC_LAYER_INPUT_ACT) &&
+                     !(next_ce && (P.flags & DPC_FWD_ERR_NEXT));
   const bool do_copy = (P.flags & DPC_FWD_COPY_NEXT) && Lup;
   const bool store = !(P.flags & DPC_FWD_TRANSIENT);
   // bit 10 (internal): the launch starts at the first layer of the sweep, whose mu is kept
@@ -466,7 +473,7 @@ __device__ __forceinline__ void fwd_epilogue_tile(const TcParams& P, const FwdMe
       }
       if (store && active)
       {
-        if (!(no_mu && (P.flags & DPC_FWD_NO_PREACT)))
+        if (L.preact && !(no_mu && (P.flags & DPC_FWD_NO_PREACT))) // (SimplePC keeps no preact)
           st8(L.preact + o + k, pre);
         if (!no_mu)
           st8(L.mu + o + k, mu);
@@ -1220,7 +1227,14 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
 #pragma unroll
             for (int q = 0; q < 8; ++q)
               fb[q] = L.a * v[k + q] - ee[k + q];
-            if (L.v)
+            if (L.flags & DPC_LAYER_INPUT_ACT)
+            {
+              // SimplePC (src/layers/SimplePCLayer.cpp:205-257): z += ir (f'(z) (e_above W) - e)
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                zz[k + q] += L.ir * (v[k + q] * act_deriv(L.act, zz[k + q]) - ee[k + q]);
+            }
+            else if (L.v)
             {
               float vv[8];
               ld8(L.v + o + k, vv);
@@ -1266,7 +1280,7 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         }
         else
         {
-          alpha = L.a * L.lr / Bf;
+          alpha = (L.flags & DPC_LAYER_INPUT_ACT) ? L.lr / Bf : L.a * L.lr / Bf;
           if (L.lmbda > 0.0f)
             decay = 1.0f - L.lmbda;
         }
@@ -1897,18 +1911,24 @@ int tc_plan_init(dpc_plan* plan)
       if (best_count > 0 && l >= best_first && l < best_first + best_count)
         continue;
       const dpc_layer& L = plan->h[l];
-      if (L.next_size <= 0 || L.size % 256 != 0 || L.next_size % 256 != 0 ||
-          (L.flags & DPC_LAYER_INPUT_ACT) || !L.fe || !L.preact || !L.W || !L.z ||
-          ((uintptr_t)L.z % 128) != 0 || ((uintptr_t)L.W % 128) != 0 || ((uintptr_t)L.fe % 128) != 0)
+      const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+      // operands: the belief (SimplePC: f(z), kept in zF) and the feedback error (SimplePC: the
+      // error of the layer above)
+      const float* a_in = simple ? L.zF : L.z;
+      const float* a_out = simple ? plan->h[l + 1].e : L.fe;
+      if (L.next_size <= 0 || L.size % 256 != 0 || L.next_size % 256 != 0 || !a_in || !a_out ||
+          !L.W || !L.z || (!simple && !L.preact) || plan->h[l + 1].size != L.next_size ||
+          ((uintptr_t)a_in % 128) != 0 || ((uintptr_t)L.W % 128) != 0 || ((uintptr_t)a_out % 128) != 0)
         continue;
       TcState::Extra x;
       x.layer = l;
+      x.simple = simple;
       const int s_in = L.size, s_out = L.next_size;
       bool ok = true;
-      ok &= make_map(&x.z_km, L.z, s_in, B, 1, (int64_t)B * s_in, TBM, false);
-      ok &= make_map(&x.z_mn, L.z, s_in, B, 1, (int64_t)B * s_in, 32, true);
-      ok &= make_map(&x.fe_km, L.fe, s_out, B, 1, (int64_t)B * s_out, TBM, false);
-      ok &= make_map(&x.fe_mn, L.fe, s_out, B, 1, (int64_t)B * s_out, 32, true);
+      ok &= make_map(&x.z_km, a_in, s_in, B, 1, (int64_t)B * s_in, TBM, false);
+      ok &= make_map(&x.z_mn, a_in, s_in, B, 1, (int64_t)B * s_in, 32, true);
+      ok &= make_map(&x.fe_km, a_out, s_out, B, 1, (int64_t)B * s_out, TBM, false);
+      ok &= make_map(&x.fe_mn, a_out, s_out, B, 1, (int64_t)B * s_out, 32, true);
       ok &= make_map(&x.w_km128, L.W, s_in, s_out, 1, (int64_t)s_in * s_out, 128, false);
       ok &= make_map(&x.w_mn, L.W, s_in, s_out, 1, (int64_t)s_in * s_out, 32, true);
       if (ok)
@@ -2519,6 +2539,22 @@ static TcParams extra_params(dpc_plan* p, TcState* st, int layer, int M, int N, 
   return P;
 }
 
+// SimplePC: zF = f(z), the operand of the layer's forward product and of its weight update
+// (src/layers/SimplePCLayer.cpp:146-150 keeps f(z) as last fed to the GEMM).
+__global__ void input_activation_kernel(const dpc_layer* __restrict__ layers, int layer, long long n)
+{
+  const dpc_layer& L = layers[layer];
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long long)gridDim.x * blockDim.x * 4)
+  {
+    const float4 z = *reinterpret_cast<const float4*>(L.z + i);
+    const float in[8] = {z.x, z.y, z.z, z.w, 0.0f, 0.0f, 0.0f, 0.0f};
+    float f[8], d[8];
+    act_both8<false>(L.act, in, f, d);
+    *reinterpret_cast<float4*>(L.zF + i) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+}
+
 int tc_extra_forward(dpc_plan* p, int layer, int flags)
 {
   auto* st = static_cast<TcState*>(p->tc);
@@ -2530,6 +2566,15 @@ int tc_extra_forward(dpc_plan* p, int layer, int flags)
       (flags & DPC_FWD_FE) && !(flags & DPC_FWD_ERR_NEXT) && (flags & DPC_FWD_TRANSIENT);
   const bool tf32 = p->ctx->precision == DPC_PRECISION_TF32 || (refresh && fast_grad(p));
   const int scheme = split_scheme(p);
+  if (x->simple)
+  {
+    const long long n = (long long)p->batch * L.size; // a multiple of 256 x 256
+    const unsigned blocks = (unsigned)std::min<long long>((n / 4 + 255) / 256, 4096);
+    input_activation_kernel<<<blocks, 256, 0, p->ctx->stream>>>(p->d, layer, n);
+    p->ctx->launches += 1;
+    if (cudaPeekAtLastError() != cudaSuccess)
+      return cuda_fail(cudaGetLastError(), "input_activation kernel launch");
+  }
   TcParams P = extra_params(p, st, layer, p->batch, L.next_size, L.size, flags, 0);
   const int rc =
       tf32 ? launch<TC_FWD, 256, 0, 128, true>(p, st, x->z_km, x->w_km128, P)

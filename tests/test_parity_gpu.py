@@ -157,6 +157,13 @@ RECTANGULAR = {
     "dkp_rectangular_only": dict(
         kind="dkp", sizes=[256, 512, 256, 768, 10], batch=256, T=3, steps=2,
         hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="gelu")),
+    # SimplePC layers (activation on the input side of the product) on the same kernels
+    "simple_rectangular": dict(
+        kind="simple", sizes=[256, 512, 256, 10], batch=256, T=3, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, lmbda=0.0, act="tanh")),
+    "simple_rectangular_decay_sigmoid": dict(
+        kind="simple", sizes=[512, 256, 256, 10], batch=256, T=4, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, lmbda=0.01, act="sigmoid")),
     # the shape class of the wide benchmark network: wide input layer, softmax head, Adam.
     # (Adam's first steps move every element by about lr whatever its gradient, so an element
     # whose gradient is zero to rounding may move the other way: the rates keep twice that inside
