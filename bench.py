@@ -714,7 +714,7 @@ def batch_sharded_main(args, w, sizes, config):
 
 
 DTYPES = {"fp32": "f32 (tensor-core layers: 3xBF16 operand split for SGD networks, 3xTF32 otherwise)",
-          "tf32": "tf32", "mixed": "f32 state path, tf32 gradient path"}
+          "tf32": "tf32", "mixed": "as f32 where the plan keeps operand planes; else f32 state path, tf32 gradient path"}
 
 
 def main():

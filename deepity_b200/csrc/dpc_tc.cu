@@ -2079,9 +2079,14 @@ static bool all_sgd(const dpc_plan* p)
 
 // DPC_PRECISION_MIXED: gradient-path products in one TF32 pass when every weight optimizer is
 // SGD (an Adam-type update would turn the TF32 rounding of a near-zero gradient into a full step).
+// Not where the plan has operand planes: the three-BF16-pass kernels on pre-split operands are
+// faster than the one-pass TF32 kernels on fp32 tensors (they read half the operand bytes per
+// pass pair and need no fp32 feedback errors) AND exact to 2^-16, so the mode then runs exactly
+// what the FP32 mode runs.
 static bool fast_grad(const dpc_plan* p)
 {
-  return p->ctx->precision == DPC_PRECISION_MIXED && all_sgd(p);
+  const auto* st = static_cast<const TcState*>(p->tc);
+  return p->ctx->precision == DPC_PRECISION_MIXED && all_sgd(p) && !(st && st->planes);
 }
 
 // fp32 mode: how the operands are split for the tensor cores.  2 = three BF16 passes over
@@ -2159,11 +2164,11 @@ static bool planes_kept(const dpc_plan* p, const TcState* st)
   return planes_on(p, st);
 }
 
-// The fp32 feedback errors of the run are dropped only in the plain FP32 mode: the mixed mode's
-// one-pass gradient products read the fp32 tensor.
+// The fp32 feedback errors of the run are dropped wherever the planes are kept (FP32 mode and the
+// mixed mode, which then runs the same kernels).
 static bool fe_only_now(const dpc_plan* p, const TcState* st)
 {
-  return planes_kept(p, st) && st->fe_only && p->ctx->precision == DPC_PRECISION_FP32;
+  return planes_kept(p, st) && st->fe_only && p->ctx->precision != DPC_PRECISION_TF32;
 }
 
 static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int M, int N, int K,
@@ -2648,7 +2653,7 @@ std::string tc_describe(dpc_plan* p)
                        : split_scheme(p) == 2 ? (planes_on(p, st) ? "3xBF16 from pre-split planes"
                                                                  : "3xBF16 split in the kernel")
                                               : "3xTF32";
-    if (p->ctx->precision == DPC_PRECISION_MIXED)
+    if (fast_grad(p))
       mode += " (gradient path 1xTF32)";
     out = "layers " + std::to_string(p->run.first) + ".." +
           std::to_string(p->run.first + p->run.count - 1) + " on tcgen05 (" +

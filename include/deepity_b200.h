@@ -83,8 +83,8 @@ typedef enum dpc_opt
   DPC_OPT_ADAMW = 2
 } dpc_opt;
 
-/* GEMM arithmetic.  FP32: every product and sum in fp32 (CUDA cores, or 3xTF32 split on
- * the tensor cores where the shape allows) — the mode judged at 1e-4 against the CPU
+/* GEMM arithmetic.  FP32: every product and sum in fp32 (CUDA cores, or a three-pass operand
+ * split -- 3xBF16 for SGD networks, 3xTF32 otherwise -- on the tensor cores where the shape allows) — the mode judged at 1e-4 against the CPU
  * reference.  TF32: one tensor-core pass with fp32 accumulation, the analogue of the
  * reference's default cuBLAS TF32 math mode (src/backend/cuda/CUDABackendCore.cu:54-67,
  * IComputeBackend::SetAllowTF32); judged at the reference's own 1e-2 CPU-vs-GPU bound.
@@ -92,7 +92,9 @@ typedef enum dpc_opt
  * settling passes, energy -- as in FP32; the gradient path of the tensor-core layers -- the
  * prediction refresh before learning and the two weight-shaped products -- as in TF32, when
  * every weight optimizer is SGD.  The TF32 rounding (5e-4 relative) then lands on the UPDATE
- * of W, not on W; judged at 1e-3. */
+ * of W, not on W; judged at 1e-3.  Where a plan keeps pre-split bf16 operand copies (the default
+ * for SGD networks on 256-multiple shapes) the mode runs exactly what FP32 runs: those kernels are
+ * faster than the one-pass TF32 ones and more exact. */
 typedef enum dpc_precision
 {
   DPC_PRECISION_FP32 = 0,
