@@ -7,7 +7,7 @@
 One "step" is one full ``train_step`` (settle T times, learn, final energy) on one batch of
 synthetic data.  At N=1 the workload is the configuration the headline metric is quoted on:
 DKPPCN, width 512, 2048 hidden layers, batch 1024, T=2, tanh, SGD for W and Psi, inputs
-N(0,1), one-hot 10-class targets (it fits one GPU: about 23 GB).  Printed on rank 0: ONE
+N(0,1), one-hot 10-class targets (it fits one GPU: about 30 GB).  Printed on rank 0: ONE
 JSON line with
 
 * ``value``     samples/s with x,y already resident in HBM (``train_step_device``), timed with
@@ -15,12 +15,15 @@ JSON line with
 * ``e2e``       the same metric through the public host-buffer call ``net.train_step(x, y, T)``
                 (pinned staging + H2D of x,y and the D2H energy read inside the timed region);
 * ``roofline``  the dominant kernel (the grouped forward GEMM of one settling pass) timed on
-                its own: algorithmic FLOPs per launch / mean launch time against the measured
-                dense tensor peak of MEASURED_PEAKS.json;
+                its own with CUDA events: both floors are stated (three tensor passes against the
+                measured dense bf16 peak, algorithmic bytes against the measured copy bandwidth
+                of MEASURED_PEAKS.json) and ``bound`` is the larger one; ``traffic`` is the DRAM
+                traffic measured with ncu per layer times the layers of the launch; at N > 1 the
+                same launch over each rank's own layers, the slowest rank's figure reported;
 * ``cpu_baseline`` the reference's own CPU code (oracle/_ref; numpy restatement if that is
                 absent) on a bounded sample of the workload — the same network cut to a few
                 layers, scaled to the full depth by the layer ratio;
-* clocks sampled with nvidia-smi during the timed region.
+* clocks and throttle reasons sampled through NVML every 50 ms during the timed region.
 
 ``--impl reference`` times only the CPU leg and prints the same line shape with
 ``"impl": "reference"``: every one of its K steps is one train step of a BOUNDED SAMPLE of the
@@ -621,6 +624,28 @@ def layer_sharded_main(args, w, sizes, config):
     dist.all_reduce(lc)
     flops = net.train_step_flops(T)
     ranges = net.ranges
+    # dominant kernel on this rank's block of layers (the same settle-pass forward launch as at
+    # N = 1, over the local layers), timed alone with CUDA events on the library's stream; the
+    # slowest rank's figure is reported
+    eng = net.eng
+    local_sizes = list(eng.sizes)
+    k_first, k_count = 1, len(local_sizes) - 2
+    fwd_flags = 2 | 8 | 256  # DPC_FWD_ERR_NEXT | DPC_FWD_FE | DPC_FWD_TRANSIENT
+    k_ms = None
+    if k_count > 0:
+        for _ in range(3):
+            eng.lib.dpc_forward(eng.plan, k_first, k_count, fwd_flags)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(args.steps, 5)
+        a.record(eng.stream)
+        for _ in range(reps):
+            eng.lib.dpc_forward(eng.plan, k_first, k_count, fwd_flags)
+        b.record(eng.stream)
+        b.synchronize()
+        k_ms = a.elapsed_time(b) / reps
+    kt = torch.tensor([k_ms or 0.0, float(k_count)], device="cuda", dtype=torch.float64)
+    gathered = [torch.zeros_like(kt) for _ in range(world)]
+    dist.all_gather(gathered, kt)
     # (the sharded network stays alive to the end of the process: torch tensors that were used on
     # its stream outlive this function, and freeing them after the stream is gone aborts)
     side = None if args.no_side else batch_sharded_measure(args, dict(WORKLOADS["c4"]))
@@ -629,6 +654,16 @@ def layer_sharded_main(args, w, sizes, config):
         peak = (peaks.get("bf16_tflops_sustained") or 1590.0) * world
         config = dict(config, parallelism=f"layer-sharded x{world}",
                       layers_per_rank=[e - b for b, e in ranges])
+        # per-layer time of the slowest rank's launch -> the roofline object of that launch
+        per_rank = [(float(g[0]), int(g[1])) for g in gathered]
+        slow_ms, slow_layers = max(per_rank, key=lambda t: t[0] / max(t[1], 1))
+        roofline = None
+        if slow_layers > 0:
+            H = sizes[1]
+            roofline = forward_roofline(B, [H] * (slow_layers + 2), slow_ms, args.precision,
+                                        2 if args.precision == "tf32" else 3, peaks)
+            roofline["per_rank_launch_ms"] = [round(t[0], 4) for t in per_rank]
+            roofline["per_rank_layers"] = [t[1] for t in per_rank]
         line = {"metric": "train_step samples/sec", "value": B / (ms * 1e-3), "unit": "samples/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -639,7 +674,7 @@ def layer_sharded_main(args, w, sizes, config):
                 "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8},
                 "gpu_launches": int(lc.item()), "clocks": clk.summary(),
-                "roofline": None, "cpu_baseline": None, "batch_sharded_c4": side}
+                "roofline": roofline, "cpu_baseline": None, "batch_sharded_c4": side}
         print(json.dumps(line))
     dist.barrier()
     dist.destroy_process_group()
