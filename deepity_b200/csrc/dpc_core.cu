@@ -116,6 +116,20 @@ int dpc_create(int device, dpc_ctx** out)
   DPC_CUDA(cudaGetDeviceProperties(&prop, device));
   ctx->sm_count = prop.multiProcessorCount;
   DPC_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+  // streams that consecutive single tensor-core layers of one phase fork to (see dispatch_range)
+  if (!getenv("DPC_DISABLE_LAYER_STREAMS"))
+  {
+    bool ok = cudaEventCreateWithFlags(&ctx->fork_ev, cudaEventDisableTiming) == cudaSuccess;
+    for (int s = 0; s < dpc_ctx::kSide && ok; ++s)
+      ok = cudaStreamCreateWithFlags(&ctx->side[s], cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&ctx->join_ev[s], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok)
+    {
+      const cudaError_t e = cudaGetLastError();
+      dpc_destroy(ctx);
+      return cuda_fail(e, "creating the per-layer streams");
+    }
+  }
   *out = ctx;
   return DPC_OK;
 }
@@ -137,6 +151,18 @@ int dpc_destroy(dpc_ctx* ctx)
     cudaStreamSynchronize(ctx->stream);
     cudaStreamDestroy(ctx->stream);
   }
+  for (int s = 0; s < dpc_ctx::kSide; ++s)
+  {
+    if (ctx->side[s])
+    {
+      cudaStreamSynchronize(ctx->side[s]);
+      cudaStreamDestroy(ctx->side[s]);
+    }
+    if (ctx->join_ev[s])
+      cudaEventDestroy(ctx->join_ev[s]);
+  }
+  if (ctx->fork_ev)
+    cudaEventDestroy(ctx->fork_ev);
   delete ctx;
   return DPC_OK;
 }
@@ -609,15 +635,57 @@ static int forward_simt(dpc_plan* p, int first, int count, int flags)
 // one piece, single layers outside it that fit the CTA-pair kernels one by one) and maximal
 // pieces for the CUDA-core kernels.  A piece the tensor-core entry point declines (returns 1)
 // goes to the CUDA-core kernels too.
+// `independent`: the layers of the range neither read what another layer of the range writes nor
+// write the same tensors (true of a settle pass, a state update and a weight update; not of a
+// sweep).  Consecutive single layers on the tensor cores then go to up to four streams that fork
+// from and join the context's stream (inside a graph capture: parallel branches), because one such
+// layer alone fills only a part of the GPU.
 template <typename TcFn, typename SimtFn>
-static int dispatch_range(dpc_plan* p, int first, int count, TcFn tc, SimtFn simt)
+static int dispatch_range(dpc_plan* p, int first, int count, TcFn tc, SimtFn simt,
+                          bool independent = false)
 {
   const int end = first + count;
   const int run0 = p->run.first, run1 = p->run.first + p->run.count;
+  dpc_ctx* ctx = p->ctx;
   int i = first;
   while (i < end)
   {
     int j, rc;
+    if (independent && ctx->fork_ev && tc_extra_layer(p, i) && i + 1 < end &&
+        tc_extra_layer(p, i + 1))
+    {
+      j = i + 2;
+      while (j < end && tc_extra_layer(p, j))
+        ++j;
+      cudaStream_t main_stream = ctx->stream;
+      const int used = std::min(j - i - 1, dpc_ctx::kSide);
+      bool forked = cudaEventRecord(ctx->fork_ev, main_stream) == cudaSuccess;
+      for (int s = 0; s < used && forked; ++s)
+        forked = cudaStreamWaitEvent(ctx->side[s], ctx->fork_ev, 0) == cudaSuccess;
+      if (!forked)
+        return cuda_fail(cudaGetLastError(), "fork of the per-layer streams");
+      rc = DPC_OK;
+      for (int q = i; q < j && rc == DPC_OK; ++q)
+      {
+        const int lane = (q - i) % (used + 1);
+        ctx->stream = lane == 0 ? main_stream : ctx->side[lane - 1];
+        rc = tc(q, 1);
+        if (rc > 0)
+          rc = simt(q, 1);
+      }
+      ctx->stream = main_stream;
+      // join whatever happened: a capture must not end with a stream still forked
+      bool joined = true;
+      for (int s = 0; s < used; ++s)
+        joined &= cudaEventRecord(ctx->join_ev[s], ctx->side[s]) == cudaSuccess &&
+                  cudaStreamWaitEvent(main_stream, ctx->join_ev[s], 0) == cudaSuccess;
+      if (rc != DPC_OK)
+        return rc;
+      if (!joined)
+        return cuda_fail(cudaGetLastError(), "join of the per-layer streams");
+      i = j;
+      continue;
+    }
     if (p->run.count > 0 && i >= run0 && i < run1)
     {
       j = std::min(end, run1);
@@ -653,7 +721,8 @@ int dpc_forward(dpc_plan* p, int first, int count, int flags)
     return forward_simt(p, first, count, flags);
   return dispatch_range(
       p, first, count, [&](int f, int c) { return tc_forward(p, f, c, flags); },
-      [&](int f, int c) { return forward_simt(p, f, c, flags); });
+      [&](int f, int c) { return forward_simt(p, f, c, flags); },
+      /*independent=*/!(flags & DPC_FWD_COPY_NEXT));
 }
 
 int dpc_project_forward(dpc_plan* p, int first, int count, int skip_last_copy)
@@ -787,7 +856,7 @@ int dpc_update_state(dpc_plan* p, int first, int count)
     return rc;
   return dispatch_range(
       p, first, count, [&](int f, int c) { return tc_update_state(p, f, c); },
-      [&](int f, int c) { return update_state_simt(p, f, c); });
+      [&](int f, int c) { return update_state_simt(p, f, c); }, /*independent=*/true);
 }
 
 int dpc_epc_reconstruct(dpc_plan* p, int layer)
@@ -956,7 +1025,7 @@ int dpc_direct_feedback(dpc_plan* p, int first, int count, int decay_w)
   const int flags = decay_w ? 1 : 0;
   return dispatch_range(
       p, first, count, [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_DFA, decay_w); },
-      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA, flags); });
+      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA, flags); }, /*independent=*/true);
 }
 
 // Psi update (or its raw sums) of layers [f, f+c): the 128-columns-per-block kernel when every
@@ -1051,7 +1120,7 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
         }
         return DPC_OK;
       },
-      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_LEARN, 0); });
+      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_LEARN, 0); }, /*independent=*/true);
   if (rc != DPC_OK)
     return rc;
   for (int f = first; f < first + count; f += kMaxZ)
@@ -1117,12 +1186,14 @@ int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
     return dispatch_range(
         p, first, count,
         [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_DFA | WG_GRAD_ONLY); },
-        [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA | WG_GRAD_ONLY, 0); });
+        [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_DFA | WG_GRAD_ONLY, 0); },
+        /*independent=*/true);
   }
   rc = dispatch_range(
       p, first, count,
       [&](int f, int c) { return tc_weight_gemm(p, f, c, WG_LEARN | WG_GRAD_ONLY); },
-      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_LEARN | WG_GRAD_ONLY, 0); });
+      [&](int f, int c) { return weight_gemm_simt(p, f, c, WG_LEARN | WG_GRAD_ONLY, 0); },
+      /*independent=*/true);
   if (rc != DPC_OK)
     return rc;
   bool any_psi = false;

@@ -46,6 +46,11 @@ struct dpc_ctx
   int capturing_slot = -1;
   int64_t launches_at_begin = 0;
   int64_t graph_kernels[kSlots] = {};
+  // Streams that fork from `stream` and join it again within one phase call (never visible to the
+  // caller): consecutive single tensor-core layers of a phase run side by side on them.
+  static constexpr int kSide = 3;
+  cudaStream_t side[kSide] = {};
+  cudaEvent_t fork_ev = nullptr, join_ev[kSide] = {};
 };
 
 struct dpc_plan

@@ -93,8 +93,9 @@ struct TcState
   // the planes (feedback and weight-shaped products of this file, the bias column sums).
   bool fe_only = false;
   bool warned_fallback = false;
-  // Single layers outside the run that still fit the CTA-pair kernels (batch, input and output
-  // width all multiples of 256, e.g. a 3072 -> 1024 first layer): one set of tensor maps each.
+  // Single layers outside the run that still fit the CTA-pair kernels (batch and output width
+  // multiples of 256, input width a multiple of 8, e.g. a 3072 -> 1024 or a 784 -> 256 first
+  // layer): one set of tensor maps each.
   // SimplePC layers (DPC_LAYER_INPUT_ACT) multiply f(z) instead of z and the error of the layer
   // above instead of a feedback error: for them z_* cover zF and fe_* cover e of the layer above.
   struct Extra
@@ -714,7 +715,9 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
   const int t_begin = P.chain ? 0 : (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x);
   const int t_end = P.chain ? P.count : total_tiles;
   const int t_step = P.chain ? 1 : (PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x);
-  const int kblocks = P.K / C::KB / KS;
+  // (a K that is not a multiple of the stage depth: the copies of the last block read zeros
+  // beyond the tensor's extent)
+  const int kblocks = (P.K + C::KB - 1) / C::KB / KS;
 
   if (threadIdx.x == 0)
   {
@@ -1211,11 +1214,17 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         else
         for (int c = grp; c < BN / 32; c += GROUPS)
         {
+          // columns of this chunk inside the tensor (a multiple of 8; the same for every lane)
+          const int nv = P.N - (n0 + c * 32);
+          if (nv <= 0)
+            break;
           const size_t o = (size_t)m * P.N + n0 + c * 32;
           float ee[32], zz[32], v[32];
 #pragma unroll
           for (int k = 0; k < 32; k += 8)
           {
+            if (k >= nv)
+              continue;
             ld8(L.e + o + k, &ee[k]);
             ld8(L.z + o + k, &zz[k]);
           }
@@ -1223,6 +1232,8 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
 #pragma unroll
           for (int k = 0; k < 32; k += 8)
           {
+            if (k >= nv)
+              continue;
             float fb[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q)
@@ -1290,12 +1301,16 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
           // or a sum over batch shards first) applies them
           for (int c = grp; c < BN / 32; c += GROUPS)
           {
+            const int nv = P.N - (n0 + c * 32);
+            if (nv <= 0)
+              break;
             const size_t o = (size_t)m * P.N + n0 + c * 32;
             float v[32];
             tc_ld32(taddr + c * 32, v);
 #pragma unroll
             for (int k = 0; k < 32; k += 8)
-              st8(L.g_W + o + k, &v[k]);
+              if (k < nv)
+                st8(L.g_W + o + k, &v[k]);
           }
         }
         else if (C::WGIO && P.tstore)
@@ -1366,15 +1381,21 @@ __global__ void __launch_bounds__(Cfg<OP, BN, THREE_X, BM, PAIR, KS>::THREADS, 1
         __nv_bfloat16* w_hi = P.wp ? P.wp + 2 * (long long)(li - P.run_first) * P.w_elems : nullptr;
         for (int c = grp; c < BN / 32; c += GROUPS)
         {
+          const int nv = P.N - (n0 + c * 32);
+          if (nv <= 0)
+            break;
           const size_t o = (size_t)m * P.N + n0 + c * 32;
           float w[32], v[32];
 #pragma unroll
           for (int k = 0; k < 32; k += 8)
-            ld8(L.W + o + k, &w[k]);
+            if (k < nv)
+              ld8(L.W + o + k, &w[k]);
           tc_ld32(taddr + c * 32, v);
 #pragma unroll
           for (int k = 0; k < 32; k += 8)
           {
+            if (k >= nv)
+              continue;
 #pragma unroll
             for (int q = 0; q < 8; ++q)
             {
@@ -1905,6 +1926,16 @@ int tc_plan_init(dpc_plan* plan)
   if (best_count >= 1 && !run_init(plan, st, best_first, best_count))
     best_count = 0;
   // Layers outside the run whose three products fit the 256 x 256 CTA-pair tiles.
+  // One launch per layer and product only pays when the product is large: a 256 x 256 tile takes
+  // about 25 us from launch to its last store however few tiles there are, while the CUDA-core
+  // kernels take all layers of a phase in one launch.  Measured on SimplePC networks of four equal
+  // layers (whose launches of one phase run side by side on four streams), this path against the
+  // CUDA-core kernels by batch x inputs x outputs: 2^28 equal, 2^29 1.5x, 2^30 1.9x, 2^32 2.8x
+  // faster; a lone first layer: 2^28.6 equal, 2^31.6 5 % of the step.  Hence 2^29;
+  // DPC_RECTANGULAR_MIN_WORK overrides it.
+  long long min_work = 1LL << 29;
+  if (const char* e = getenv("DPC_RECTANGULAR_MIN_WORK"))
+    min_work = atoll(e);
   if (pair_ok(B, 256) && !getenv("DPC_DISABLE_RECTANGULAR"))
     for (int l = 0; l + 1 < n; ++l)
     {
@@ -1916,7 +1947,12 @@ int tc_plan_init(dpc_plan* plan)
       // error of the layer above)
       const float* a_in = simple ? L.zF : L.z;
       const float* a_out = simple ? plan->h[l + 1].e : L.fe;
-      if (L.next_size <= 0 || L.size % 256 != 0 || L.next_size % 256 != 0 || !a_in || !a_out ||
+      if ((long long)B * L.size * L.next_size < min_work)
+        continue;
+      // (the input width may be any multiple of 8 from 64 up, e.g. 784: the operand copies of the
+      // last K block and of the last column tile read zeros beyond the extent and the epilogues
+      // stop at the last column)
+      if (L.next_size <= 0 || L.size % 8 != 0 || L.size < 64 || L.next_size % 256 != 0 || !a_in || !a_out ||
           !L.W || !L.z || (!simple && !L.preact) || plan->h[l + 1].size != L.next_size ||
           ((uintptr_t)a_in % 128) != 0 || ((uintptr_t)L.W % 128) != 0 || ((uintptr_t)a_out % 128) != 0)
         continue;
@@ -2192,7 +2228,7 @@ static TcParams base_params(dpc_plan* p, TcState* st, int first, int count, int 
   P.run_first = p->run.first;
   P.M = M, P.N = N, P.K = K;
   P.tiles_m = M / BM;
-  P.tiles_n = N / BN;
+  P.tiles_n = (N + BN - 1) / BN; // a last column tile may reach beyond N: its epilogue stops at N
   P.flags = flags;
   P.mode = mode;
   P.energy = p->energy;
@@ -2573,7 +2609,7 @@ int tc_extra_forward(dpc_plan* p, int layer, int flags)
   const int scheme = split_scheme(p);
   if (x->simple)
   {
-    const long long n = (long long)p->batch * L.size; // a multiple of 256 x 256
+    const long long n = (long long)p->batch * L.size; // a multiple of 4
     const unsigned blocks = (unsigned)std::min<long long>((n / 4 + 255) / 256, 4096);
     input_activation_kernel<<<blocks, 256, 0, p->ctx->stream>>>(p->d, layer, n);
     p->ctx->launches += 1;

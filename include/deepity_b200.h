@@ -33,6 +33,12 @@
  *   DPC_DISABLE_KSPLIT         forward sweep without the two-CTA split of K
  *   DPC_DISABLE_RECTANGULAR    single layers outside the run of identical square layers stay on
  *                              the CUDA-core kernels even where their shapes fit the pair tiles
+ *   DPC_RECTANGULAR_MIN_WORK   such a layer goes to the pair tiles only when batch x inputs x
+ *                              outputs is at least this (default 2^29: below it the CUDA-core
+ *                              kernels, which take all layers of a phase in one launch, are as fast)
+ *   DPC_DISABLE_LAYER_STREAMS  consecutive such layers of one phase are launched one after the other
+ *                              on the context's stream instead of side by side on internal streams
+ *                              that fork from it and join it again
  */
 #ifndef DEEPITY_B200_H
 #define DEEPITY_B200_H

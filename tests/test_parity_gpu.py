@@ -146,8 +146,9 @@ def test_tensor_core_path_tf32_bound(name, built_library):
                     init=initial_parameters(case), delta_tol=DELTA_TOL_TF32)
 
 
-# Layers outside the run of identical square layers whose batch, input and output width are all
-# multiples of 256 run on the same CTA-pair tensor-core kernels, one launch per layer.
+# Layers outside the run of identical square layers whose batch and output width are multiples of
+# 256 (input width: any multiple of 8 from 64 up) run on the same CTA-pair tensor-core kernels, one
+# launch per layer.
 RECTANGULAR = {
     # 512->256 below and 256->512 above a run of two 256x256 layers, 512->10 on the CUDA cores
     "dkp_rectangular_around_run": dict(
@@ -172,7 +173,29 @@ RECTANGULAR = {
         kind="full", sizes=[768, 256, 256, 256, 10], batch=512, T=4, steps=3,
         hyper=dict(lr=1e-4, ir=0.1, fl=1e-4, lmbda=0.0, act="gelu"),
         options=dict(optimizer="ADAM", psi_optimizer="ADAM", cross_entropy=1)),
+    # 784 inputs (not a multiple of the 32-wide K block nor of the 256-wide column tile): the last
+    # K block of the forward product and the last column tile of the weight update are ragged
+    "dkp_784_input": dict(
+        kind="dkp", sizes=[784, 256, 256, 256, 10], batch=256, T=2, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.01, act="tanh")),
+    "full_784_input_ce_adam": dict(
+        kind="full", sizes=[784, 512, 256, 10], batch=256, T=4, steps=3,
+        hyper=dict(lr=1e-4, ir=0.1, fl=1e-4, lmbda=0.0, act="gelu"),
+        options=dict(optimizer="ADAM", psi_optimizer="ADAM", cross_entropy=1)),
+    "simple_784_input": dict(
+        kind="simple", sizes=[784, 256, 256, 10], batch=256, T=3, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, lmbda=0.0, act="tanh")),
+    # a ragged width on a HIDDEN layer: its state update stops inside a column tile as well
+    "dkp_ragged_hidden_width": dict(
+        kind="dkp", sizes=[256, 264, 256, 10], batch=256, T=3, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, fl=0.01, lmbda=0.0, act="tanh")),
+    "simple_ragged_hidden_width": dict(
+        kind="simple", sizes=[256, 328, 256, 10], batch=256, T=3, steps=2,
+        hyper=dict(lr=0.01, ir=0.1, lmbda=0.0, act="sigmoid")),
 }
+# which layer of a case the plan must report on the tensor cores (default: layer 0)
+ON_TENSOR_CORES = {"dkp_ragged_hidden_width": "layer 1 (264->256)",
+                   "simple_ragged_hidden_width": "layer 1 (328->256)"}
 
 
 def _describe(case, precision):
@@ -188,17 +211,45 @@ def _describe(case, precision):
 
 @pytest.mark.parametrize("name", sorted(RECTANGULAR))
 @pytest.mark.parametrize("precision", ["fp32", "tf32"])
-def test_rectangular_layers_on_tensor_cores(name, precision, built_library):
+def test_rectangular_layers_on_tensor_cores(name, precision, built_library, monkeypatch):
+    # (by default only layers of at least 2^29 multiply-adds per product leave the CUDA cores;
+    # these small shapes are sent to the tensor cores to exercise every ragged edge)
+    monkeypatch.setenv("DPC_RECTANGULAR_MIN_WORK", "0")
     case = RECTANGULAR[name]
     text = _describe(case, precision)
     first = case["sizes"][0], case["sizes"][1]
-    assert f"layer 0 ({first[0]}->{first[1]})" in text or "layers 0.." in text, text
+    want = ON_TENSOR_CORES.get(name, f"layer 0 ({first[0]}->{first[1]})")
+    assert want in text or "layers 0.." in text, text
     adam = "optimizer" in case.get("options", {})
     tol = TF32_TOL if precision == "tf32" else (ADAM_TOL if adam else TOL)
     delta = DELTA_TOL_TF32 if precision == "tf32" else DELTA_TOL
     compare_outputs(run_oracle(case), run_gpu(case, precision=precision), tol, f"{name} {precision}",
                     init=None if adam else initial_parameters(case),
                     delta_tol=None if adam else delta)
+
+
+def test_rectangular_layers_need_enough_work(built_library):
+    """A single layer outside the run takes one launch per product: it goes to the tensor cores only
+    when batch x inputs x outputs reaches 2^29 (below that the CUDA-core kernels, which take all
+    layers of a phase in one launch, are as fast or faster)."""
+    small = _describe(RECTANGULAR["simple_784_input"], "fp32")
+    assert "on tcgen05" not in small, small
+    big = dict(kind="full", sizes=[784, 1024, 1024, 10], batch=4096, T=2, steps=1,
+               hyper=dict(lr=1e-4, ir=0.1, fl=1e-4, lmbda=0.0, act="gelu"),
+               options=dict(optimizer="ADAM", psi_optimizer="ADAM", cross_entropy=1))
+    text = _describe(big, "fp32")
+    assert "layer 0 (784->1024) on tcgen05" in text, text
+
+
+def test_simple_network_on_tensor_cores_by_default(built_library):
+    """Four SimplePC layers of 2^29 multiply-adds each: on the tensor cores without any switch, the
+    four launches of every phase side by side on the context's internal streams."""
+    case = dict(kind="simple", sizes=[512] * 5 + [10], batch=2048, T=3, steps=2,
+                hyper=dict(lr=0.01, ir=0.1, lmbda=0.0, act="tanh"))
+    text = _describe(case, "fp32")
+    assert "layer 0 (512->512) 1 (512->512) 2 (512->512) 3 (512->512) on tcgen05" in text, text
+    compare_outputs(run_oracle(case), run_gpu(case, precision="fp32"), TOL, "simple, default path",
+                    init=initial_parameters(case), delta_tol=DELTA_TOL)
 
 
 def test_adam_on_tensor_core_layers(built_library):
