@@ -35,6 +35,42 @@ static int check_launch(dpc_ctx* ctx, const char* what)
   return DPC_OK;
 }
 
+// How many CTAs of a cluster share the batch rows of one block's columns in the batch reductions
+// (Psi update, bias column sums): doubled while the launch does not fill the SMs yet and every CTA
+// keeps at least `min_rows` rows.  1 for launches over many layers.
+static int row_split(const dpc_ctx* ctx, long long blocks, int batch, int min_rows)
+{
+  int R = 1;
+  while (R < 8 && blocks * R < ctx->sm_count && batch / (2 * R) >= min_rows)
+    R *= 2;
+  return R;
+}
+
+// kern<<<(grid.x, grid.y, R), threads, 0, st>>> as clusters of R CTAs along z (R = 1: a plain launch)
+template <typename... KArgs, typename... Args>
+static void launch_row_split(void (*kern)(KArgs...), dim3 grid, int threads, int R, cudaStream_t st,
+                             Args... args)
+{
+  if (R <= 1)
+  {
+    kern<<<grid, threads, 0, st>>>(args...);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid.x, grid.y, (unsigned)R);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)R;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kern, args...); // an error stays pending for check_launch()
+}
+
 static int check_range(dpc_plan* p, int first, int count)
 {
   if (!p)
@@ -807,6 +843,31 @@ int dpc_feedback_error(dpc_plan* p, int first, int count)
   return DPC_OK;
 }
 
+// Largest output width of layers [f, f+c) when every one of them is "narrow above" (1..16 output
+// units, an input width that is a multiple of 128, 16-byte aligned tensors, a batch of at least 256
+// rows: the layer under a head on a large batch), else 0.  Such layers have kernels of their own
+// for the state update and the weight update (narrow_state_kernel, narrow_weight_kernel).
+static int narrow_above(const dpc_plan* p, int f, int c)
+{
+  if (p->batch < 256)
+    return 0;
+  int widest = 0;
+  for (int i = f; i < f + c; ++i)
+  {
+    const dpc_layer& L = p->h[i];
+    const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+    const float* g = simple ? (i + 1 < p->n ? p->h[i + 1].e : nullptr) : L.fe;
+    const float* zin = simple ? L.zF : L.z;
+    if (L.next_size <= 0 || L.next_size > 16 || L.size % 128 != 0 || !g || !zin || !L.W || !L.z ||
+        !L.e || ((uintptr_t)zin % 16) != 0 || ((uintptr_t)L.W % 16) != 0 || ((uintptr_t)L.z % 16) != 0 ||
+        ((uintptr_t)L.e % 16) != 0 || (L.v && ((uintptr_t)L.v % 16) != 0) ||
+        (i + 1 < p->n && p->h[i + 1].e && ((uintptr_t)p->h[i + 1].e % 16) != 0))
+      return 0;
+    widest = std::max(widest, L.next_size);
+  }
+  return widest;
+}
+
 static int update_state_simt(dpc_plan* p, int first, int count)
 {
   cudaStream_t st = p->ctx->stream;
@@ -817,7 +878,27 @@ static int update_state_simt(dpc_plan* p, int first, int count)
     int tx, ty;
     // Layers whose upper neighbour does not exist are handled by the relax kernel below.
     int cg = (f + c == p->n) ? c - 1 : c;
-    if (cg > 0)
+    int narrow_kc = cg > 0 ? narrow_above(p, f, cg) : 0;
+    if (narrow_kc > 0)
+    {
+      // layers under a narrow one (the heads): 128 columns x a share of the batch rows per block
+      int mxs = 0;
+      for (int i = f; i < f + cg; ++i)
+        mxs = std::max(mxs, p->h[i].size);
+      const int gx = cdiv(mxs, 128);
+      int rpb = p->batch;
+      while (rpb > 128 && (long long)gx * cg * cdiv(p->batch, rpb) < 2 * p->ctx->sm_count)
+        rpb = cdiv(rpb / 2, 128) * 128;
+      dim3 grid(gx, cdiv(p->batch, rpb), cg);
+      if (narrow_kc <= 12)
+        narrow_state_kernel<12><<<grid, 256, 0, st>>>(p->d, f, p->n, p->batch, rpb);
+      else
+        narrow_state_kernel<16><<<grid, 256, 0, st>>>(p->d, f, p->n, p->batch, rpb);
+      int rc = check_launch(p->ctx, "narrow update_state kernel");
+      if (rc != DPC_OK)
+        return rc;
+    }
+    else if (cg > 0)
     {
       max_tiles(p, f, cg, OP_FB, tx, ty);
       if (tx > 0)
@@ -924,6 +1005,29 @@ static int weight_gemm_simt(dpc_plan* p, int first, int count, int mode, int fla
   {
     const int c = std::min(kMaxZ, first + count - f);
     int tx, ty;
+    const int narrow_kc = narrow_above(p, f, c);
+    bool staged_ok = true;
+    for (int i = f; i < f + c; ++i)
+      staged_ok &= !(mode & WG_GRAD_ONLY) || (p->h[i].g_W != nullptr);
+    if (narrow_kc > 0 && staged_ok)
+    {
+      // heads on a large batch: the batch split over warps and the CTAs of a cluster
+      int mxs = 0;
+      for (int i = f; i < f + c; ++i)
+        mxs = std::max(mxs, p->h[i].size);
+      dim3 g(cdiv(mxs, 128), c);
+      const int R = row_split(p->ctx, (long long)g.x * c, p->batch, 256);
+      if (narrow_kc <= 12)
+        launch_row_split(narrow_weight_kernel<12>, g, 256, R, p->ctx->stream, p->d, f, p->n,
+                         p->batch, flags, mode);
+      else
+        launch_row_split(narrow_weight_kernel<16>, g, 256, R, p->ctx->stream, p->d, f, p->n,
+                         p->batch, flags, mode);
+      int rc = check_launch(p->ctx, "narrow weight kernel");
+      if (rc != DPC_OK)
+        return rc;
+      continue;
+    }
     max_tiles(p, f, c, OP_WG, tx, ty);
     if (tx == 0)
       continue;
@@ -1048,10 +1152,13 @@ static int launch_psi_update(dpc_plan* p, int f, int c, int max_size, int grad_o
   if (fast && ts > 0)
   {
     dim3 g(std::max(1, cdiv(max_size, 128)), c);
+    const int R = row_split(p->ctx, (long long)g.x * c, p->batch, 256);
     if (ts <= 12)
-      psi_update4_kernel<12><<<g, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, grad_only);
+      launch_row_split(psi_update4_kernel<12>, g, 256, R, st, p->d, f, p->n, p->batch,
+                       p->e_terminal, grad_only);
     else
-      psi_update4_kernel<16><<<g, 256, 0, st>>>(p->d, f, p->n, p->batch, p->e_terminal, grad_only);
+      launch_row_split(psi_update4_kernel<16>, g, 256, R, st, p->d, f, p->n, p->batch,
+                       p->e_terminal, grad_only);
   }
   else
   {
@@ -1131,8 +1238,11 @@ int dpc_update_weights(dpc_plan* p, int first, int count, int center_rows)
     const FePlanes fp = fe_planes(p);
     // 256 threads: blocks of 64 columns where the feedback error is read from its planes,
     // one column per thread (grid-stride) elsewhere
-    dim3 gb(std::max(1, cdiv(max_next, fp.only ? 64 : 256)), c);
-    bias_update_kernel<<<gb, 256, 0, st>>>(p->d, f, p->n, p->batch, 0, fp);
+    const bool by_blocks = fp.only || p->batch >= kBiasBlockRows;
+    dim3 gb(std::max(1, cdiv(max_next, by_blocks ? 64 : 256)), c);
+    launch_row_split(bias_update_kernel, gb, 256,
+                     by_blocks ? row_split(p->ctx, (long long)gb.x * c, p->batch, 256) : 1, st, p->d,
+                     f, p->n, p->batch, 0, fp);
     if ((rc = check_launch(p->ctx, "bias_update kernel")) != DPC_OK)
       return rc;
     if (any_psi)
@@ -1211,8 +1321,11 @@ int dpc_weight_gradients(dpc_plan* p, int first, int count, int which)
     if ((rc = tc_fe_need(p, f, c)) != DPC_OK)
       return rc;
     const FePlanes fp = fe_planes(p);
-    dim3 gb(std::max(1, cdiv(max_next, fp.only ? 64 : 256)), c);
-    bias_update_kernel<<<gb, 256, 0, st>>>(p->d, f, p->n, p->batch, 1, fp);
+    const bool by_blocks = fp.only || p->batch >= kBiasBlockRows;
+    dim3 gb(std::max(1, cdiv(max_next, by_blocks ? 64 : 256)), c);
+    launch_row_split(bias_update_kernel, gb, 256,
+                     by_blocks ? row_split(p->ctx, (long long)gb.x * c, p->batch, 256) : 1, st, p->d,
+                     f, p->n, p->batch, 1, fp);
     if ((rc = check_launch(p->ctx, "bias gradient kernel")) != DPC_OK)
       return rc;
     if (any_psi)

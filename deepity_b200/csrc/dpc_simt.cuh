@@ -129,6 +129,42 @@ __device__ __forceinline__ void block_energy_add(float local, double* energy)
 }
 
 // ---------------------------------------------------------------------------------------
+// Row split over a thread-block cluster.  The reductions over the batch below (Psi update, bias
+// column sums) give one block a strip of columns and all rows, which fills the GPU when a launch
+// covers thousands of layers but not when it covers four.  Such launches go out as clusters of R
+// CTAs along z: CTA r of a cluster takes every R-th group of rows, leaves its partial sums in its
+// own shared memory, and CTA 0 adds the others' in rank order through distributed shared memory
+// (a fixed order: the result does not depend on timing).  Without the cluster attribute R is 1.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t rows_cluster_rank()
+{
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t rows_cluster_size()
+{
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void rows_cluster_sync()
+{
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the float at the same shared-memory address in CTA `rank` of the cluster
+__device__ __forceinline__ float rows_cluster_load(const float* own, uint32_t rank)
+{
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(own);
+  uint32_t ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------
 // Forward pass of narrow layers (at most 16 output units: the heads, e.g. 1024 -> 10).  The tiled
 // kernel below gives such a layer one column of 64 x 64 tiles, i.e. batch/64 CTAs that each walk
 // all of K: latency-bound (96 us for 4096 x 10 x 1024 against 3 us of traffic).  Here a warp owns
@@ -155,20 +191,35 @@ __global__ void __launch_bounds__(NTHREADS)
     acc[j] = 0.0f;
   if (row_ok)
   {
+    // 1024 elements of the row at a time: the lane's eight 16-byte loads are all issued before the
+    // first use (4 KB in flight per warp), then every weight row is walked over the same chunk
     const float* zrow = L.z + (size_t)m * K;
-    for (int k = lane * 4; k < K; k += 128)
+    for (int kc = 0; kc < K; kc += 1024)
     {
-      const float4 zv = *reinterpret_cast<const float4*>(zrow + k);
+      const int k0 = kc + lane * 4;
+      float4 zv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        zv[i] = (k0 + i * 128 < K) ? *reinterpret_cast<const float4*>(zrow + k0 + i * 128)
+                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
       for (int j = 0; j < 16; ++j)
       {
         if (j < N)
         {
-          const float4 wv = __ldg(reinterpret_cast<const float4*>(L.W + (size_t)j * K + k));
-          acc[j] = fmaf(zv.x, wv.x, acc[j]);
-          acc[j] = fmaf(zv.y, wv.y, acc[j]);
-          acc[j] = fmaf(zv.z, wv.z, acc[j]);
-          acc[j] = fmaf(zv.w, wv.w, acc[j]);
+          const float* wrow = L.W + (size_t)j * K + k0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+          {
+            if (k0 + i * 128 < K)
+            {
+              const float4 wv = __ldg(reinterpret_cast<const float4*>(wrow + i * 128));
+              acc[j] = fmaf(zv[i].x, wv.x, acc[j]);
+              acc[j] = fmaf(zv[i].y, wv.y, acc[j]);
+              acc[j] = fmaf(zv[i].z, wv.z, acc[j]);
+              acc[j] = fmaf(zv[i].w, wv.w, acc[j]);
+            }
+          }
         }
       }
     }
@@ -1007,6 +1058,7 @@ __device__ __forceinline__ void bias_apply(const dpc_layer& L, int j, float s, i
 // Layers whose feedback error exists only as bf16 planes (see FePlanes) are summed by whole
 // blocks instead: 32 row groups x 8 threads of 8 columns each (16-byte loads of both planes,
 // hi + mid = fe to 2^-17), then a fixed-order reduction over the row groups in shared memory.
+constexpr int kBiasBlockRows = 256;
 __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers,
                                    int batch, int grad_only, FePlanes planes)
 {
@@ -1020,25 +1072,46 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
   const float* g = simple ? layers[li + 1].e : L.fe;
   const int n = L.next_size;
   const __nv_bfloat16* hi = (!simple && planes.only) ? fe_plane_of(planes, li) : nullptr;
-  if (hi && n % 64 == 0 && blockDim.x == 256)
+  // Summed by whole blocks: the plane-only layers, and fp32 gradients of large batches (the
+  // one-thread-per-column loop below keeps the reference's row order for the small cases).
+  const bool wide = n % 64 == 0 && blockDim.x == 256 &&
+                    (hi || (batch >= kBiasBlockRows && ((uintptr_t)g % 16) == 0));
+  const uint32_t R = rows_cluster_size(), rank = rows_cluster_rank();
+  if (wide)
   {
     __shared__ float part[32][65];
+    __shared__ float mine[64];
     const int rg = threadIdx.x >> 3, c8 = (threadIdx.x & 7) * 8;
     for (int j0 = blockIdx.x * 64; j0 < n; j0 += gridDim.x * 64)
     {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int b = rg; b < batch; b += 32)
+      if (hi)
       {
-        const size_t o = (size_t)b * n + j0 + c8;
-        const uint4 h = *reinterpret_cast<const uint4*>(hi + o);
-        const uint4 m = *reinterpret_cast<const uint4*>(hi + planes.elems + o);
-        const uint32_t hw[4] = {h.x, h.y, h.z, h.w}, mw[4] = {m.x, m.y, m.z, m.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
+        for (int b = rg + 32 * (int)rank; b < batch; b += 32 * (int)R)
         {
-          // a bf16 is the upper half of the fp32 with the same value
-          acc[2 * q] += __uint_as_float(hw[q] << 16) + __uint_as_float(mw[q] << 16);
-          acc[2 * q + 1] += __uint_as_float(hw[q] & 0xffff0000u) + __uint_as_float(mw[q] & 0xffff0000u);
+          const size_t o = (size_t)b * n + j0 + c8;
+          const uint4 h = *reinterpret_cast<const uint4*>(hi + o);
+          const uint4 m = *reinterpret_cast<const uint4*>(hi + planes.elems + o);
+          const uint32_t hw[4] = {h.x, h.y, h.z, h.w}, mw[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+          {
+            // a bf16 is the upper half of the fp32 with the same value
+            acc[2 * q] += __uint_as_float(hw[q] << 16) + __uint_as_float(mw[q] << 16);
+            acc[2 * q + 1] += __uint_as_float(hw[q] & 0xffff0000u) + __uint_as_float(mw[q] & 0xffff0000u);
+          }
+        }
+      }
+      else
+      {
+#pragma unroll 4
+        for (int b = rg + 32 * (int)rank; b < batch; b += 32 * (int)R)
+        {
+          const size_t o = (size_t)b * n + j0 + c8;
+          const float4 x = *reinterpret_cast<const float4*>(g + o);
+          const float4 y = *reinterpret_cast<const float4*>(g + o + 4);
+          acc[0] += x.x, acc[1] += x.y, acc[2] += x.z, acc[3] += x.w;
+          acc[4] += y.x, acc[5] += y.y, acc[6] += y.z, acc[7] += y.w;
         }
       }
       __syncthreads();
@@ -1046,16 +1119,29 @@ __global__ void bias_update_kernel(const dpc_layer* __restrict__ layers, int fir
       for (int q = 0; q < 8; ++q)
         part[rg][c8 + q] = acc[q];
       __syncthreads();
+      float s = 0.0f;
       if (threadIdx.x < 64)
       {
-        float s = 0.0f;
         for (int r = 0; r < 32; ++r)
           s += part[r][threadIdx.x];
-        bias_apply(L, j0 + threadIdx.x, s, batch, grad_only);
+        if (R > 1 && rank != 0)
+          mine[threadIdx.x] = s;
       }
+      if (R > 1)
+      {
+        rows_cluster_sync();
+        if (rank == 0 && threadIdx.x < 64)
+          for (uint32_t r = 1; r < R; ++r)
+            s += rows_cluster_load(&mine[threadIdx.x], r);
+        rows_cluster_sync(); // `mine` of the other CTAs may be rewritten (or go away) only now
+      }
+      if (threadIdx.x < 64 && rank == 0)
+        bias_apply(L, j0 + threadIdx.x, s, batch, grad_only);
     }
     return;
   }
+  if (rank != 0)
+    return; // (a row-split launch over a layer that takes the column loop: one CTA does it all)
   for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x)
   {
     float s = 0.0f;
@@ -1099,54 +1185,43 @@ __device__ __forceinline__ void psi_apply(const dpc_layer& L, int row, int k, fl
   }
 }
 
-// The same update for the common aligned case (layer width a multiple of 128, at most KC terminal
-// units, KC = 12 or 16): a block owns 128 rows of Psi (= 128 columns of z), lane l of every warp
-// the columns 4l..4l+3 (one 16-byte load per batch row: a warp reads a whole 512-byte row segment),
-// warp w the batch rows w, w+8, ...; the terminal errors of 128 batch rows at a time sit in shared
-// memory.  The eight warps' partial sums are added in a fixed tree order through shared memory.
+// sum over the batch of zin[b][col + c] * g[b][k] for c < 4, k < KC: the common core of the Psi
+// update and of the weight update of a narrow layer.  A block owns 128 columns of zin, lane l of
+// every warp the columns 4l..4l+3 (one 16-byte load per batch row: a warp reads a whole 512-byte row
+// segment), warp w the batch rows w, w+8, ...; the rows of g (at most KC wide, ldg apart) of 128
+// batch rows at a time sit in shared memory.  The eight warps' partial sums are added in a fixed
+// tree order through shared memory, then the CTAs of a row-split cluster in rank order.  Returns
+// true in the threads that end up with the sums (warp 0 of CTA 0 of the cluster).
 // (Measured alternatives, both slower: two columns per lane at twice the blocks per SM, and the
-// terminal errors of the whole batch in shared memory so that the row loop has no barrier.)
+// rows of g of the whole batch in shared memory so that the row loop has no barrier.)
 template <int KC>
-__global__ void __launch_bounds__(256)
-    psi_update4_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
-                       const float* __restrict__ eT, int grad_only)
+__device__ __forceinline__ bool batch_outer4(const float* __restrict__ zin, int s, int col,
+                                             const float* __restrict__ g, int ldg, int TS,
+                                             int batch, float (&acc)[4][KC], float (*es)[KC],
+                                             float (*part)[4 * KC][32])
 {
-  const int li = first + blockIdx.y;
-  if (li + 1 >= n_layers)
-    return;
-  const dpc_layer L = layers[li];
-  if (L.next_size <= 0 || L.Psi == nullptr || (L.flags & DPC_LAYER_INPUT_ACT))
-    return;
-  const int TS = L.terminal_size, s = L.size;
-  const bool full_kind = (L.flags & DPC_LAYER_FULLPC_PSI) != 0;
-  const float rate = full_kind ? L.fl * L.a : L.fl;
-  if ((int)blockIdx.x * 128 >= s)
-    return;
-  constexpr int ROWS = 128, NV = 4 * KC;
-  __shared__ __align__(16) float es[ROWS][KC];
-  __shared__ float part[4][NV][32];
+  constexpr int ROWS = 128;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col = blockIdx.x * 128 + lane * 4;
-  float acc[4][KC];
 #pragma unroll
   for (int c = 0; c < 4; ++c)
 #pragma unroll
     for (int k = 0; k < KC; ++k)
       acc[c][k] = 0.0f;
-  for (int b0 = 0; b0 < batch; b0 += ROWS)
+  const uint32_t R = rows_cluster_size(), rank = rows_cluster_rank();
+  for (int b0 = (int)rank * ROWS; b0 < batch; b0 += (int)R * ROWS)
   {
     __syncthreads();
     for (int idx = threadIdx.x; idx < ROWS * KC; idx += 256)
     {
       const int r = idx / KC, k = idx - r * KC;
-      es[r][k] = (b0 + r < batch && k < TS) ? eT[(size_t)(b0 + r) * TS + k] : 0.0f;
+      es[r][k] = (b0 + r < batch && k < TS) ? g[(size_t)(b0 + r) * ldg + k] : 0.0f;
     }
     __syncthreads();
     const int rows = min(ROWS, batch - b0);
 #pragma unroll 4
     for (int r = warp; r < rows; r += 8)
     {
-      const float4 z4 = *reinterpret_cast<const float4*>(L.z + (size_t)(b0 + r) * s + col);
+      const float4 z4 = *reinterpret_cast<const float4*>(zin + (size_t)(b0 + r) * s + col);
       const float zv[4] = {z4.x, z4.y, z4.z, z4.w};
 #pragma unroll
       for (int k4 = 0; k4 < KC; k4 += 4)
@@ -1186,15 +1261,246 @@ __global__ void __launch_bounds__(256)
           acc[c][k] += part[warp][c * KC + k][lane];
     }
   }
-  if (warp == 0)
+  if (R > 1)
   {
+    // (part[0] was last read by this same warp 0 in the tree above)
+    if (rank != 0 && warp == 0)
+    {
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
-      for (int k = 0; k < KC; ++k)
-        if (k < TS)
-          psi_apply(L, col + c, k, acc[c][k], batch, grad_only, full_kind, rate);
+        for (int k = 0; k < KC; ++k)
+          part[0][c * KC + k][lane] = acc[c][k];
+    }
+    rows_cluster_sync();
+    if (rank == 0 && warp == 0)
+    {
+      for (uint32_t r = 1; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int k = 0; k < KC; ++k)
+            acc[c][k] += rows_cluster_load(&part[0][c * KC + k][lane], r);
+    }
+    rows_cluster_sync(); // nobody leaves while CTA 0 may still read its shared memory
   }
+  return rank == 0 && warp == 0;
+}
+
+// The Psi update for the common aligned case (layer width a multiple of 128, at most KC terminal
+// units, KC = 12 or 16): a block owns 128 rows of Psi (= 128 columns of z).
+template <int KC>
+__global__ void __launch_bounds__(256)
+    psi_update4_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
+                       const float* __restrict__ eT, int grad_only)
+{
+  const int li = first + blockIdx.y;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0 || L.Psi == nullptr || (L.flags & DPC_LAYER_INPUT_ACT))
+    return;
+  const int TS = L.terminal_size, s = L.size;
+  const bool full_kind = (L.flags & DPC_LAYER_FULLPC_PSI) != 0;
+  const float rate = full_kind ? L.fl * L.a : L.fl;
+  if ((int)blockIdx.x * 128 >= s)
+    return;
+  __shared__ __align__(16) float es[128][KC];
+  __shared__ float part[4][4 * KC][32];
+  const int col = blockIdx.x * 128 + (threadIdx.x & 31) * 4;
+  float acc[4][KC];
+  if (!batch_outer4<KC>(L.z, s, col, eT, TS, TS, batch, acc, es, part))
+    return;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int k = 0; k < KC; ++k)
+      if (k < TS)
+        psi_apply(L, col + c, k, acc[c][k], batch, grad_only, full_kind, rate);
+}
+
+// State update of a layer below a narrow one (at most KC <= 16 units above, own width a multiple of
+// 128: the layer under a head, e.g. z[4096 x 1024] += ir (a fe[4096 x 10] W[10 x 1024] - e)).  The
+// product has a K of 10: the tiled kernel spends its time on tile bookkeeping.  Here lane l of
+// every warp keeps the weights of columns 4l..4l+3 in registers, a block owns 128 columns and
+// `rows_per_block` batch rows, warp w the rows w, w+8, ...; the rows of the feedback error go
+// through shared memory 128 at a time.  Same arithmetic per element as pc_gemm_kernel<OP_FB>.
+template <int KC>
+__global__ void __launch_bounds__(256)
+    narrow_state_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
+                        int rows_per_block)
+{
+  const int li = first + blockIdx.z;
+  if (li + 1 >= n_layers)
+    return;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0)
+    return;
+  const dpc_layer* Lup = &layers[li + 1];
+  const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+  const bool residual = (L.flags & DPC_LAYER_RESIDUAL) != 0;
+  const int K = L.next_size, s = L.size;
+  if ((int)blockIdx.x * 128 >= s)
+    return;
+  const float* g = simple ? Lup->e : L.fe;
+  constexpr int ROWS = 128;
+  __shared__ __align__(16) float gs[ROWS][KC];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 128 + lane * 4;
+  float w[4][KC];
+#pragma unroll
+  for (int k = 0; k < KC; ++k)
+  {
+    float4 w4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (k < K)
+      w4 = *reinterpret_cast<const float4*>(L.W + (size_t)k * s + col);
+    w[0][k] = w4.x, w[1][k] = w4.y, w[2][k] = w4.z, w[3][k] = w4.w;
+  }
+  const int b_begin = blockIdx.y * rows_per_block;
+  const int b_end = min(batch, b_begin + rows_per_block);
+  for (int b0 = b_begin; b0 < b_end; b0 += ROWS)
+  {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < ROWS * KC; idx += 256)
+    {
+      const int r = idx / KC, k = idx - r * KC;
+      gs[r][k] = (b0 + r < b_end && k < K) ? g[(size_t)(b0 + r) * K + k] : 0.0f;
+    }
+    __syncthreads();
+    const int rows = min(ROWS, b_end - b0);
+#pragma unroll 2
+    for (int r = warp; r < rows; r += 8)
+    {
+      const size_t o = (size_t)(b0 + r) * s + col;
+      const float4 e4 = *reinterpret_cast<const float4*>(L.e + o);
+      const float4 z4 = *reinterpret_cast<const float4*>(L.z + o);
+      float4 v4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), u4 = v4;
+      if (!simple && L.v)
+        v4 = *reinterpret_cast<const float4*>(L.v + o);
+      if (!simple && residual)
+        u4 = *reinterpret_cast<const float4*>(Lup->e + o);
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int k4 = 0; k4 < KC; k4 += 4)
+      {
+        const float4 g4 = *reinterpret_cast<const float4*>(&gs[r][k4]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+        {
+          acc[c] = fmaf(g4.x, w[c][k4], acc[c]);
+          acc[c] = fmaf(g4.y, w[c][k4 + 1], acc[c]);
+          acc[c] = fmaf(g4.z, w[c][k4 + 2], acc[c]);
+          acc[c] = fmaf(g4.w, w[c][k4 + 3], acc[c]);
+        }
+      }
+      float zz[4] = {z4.x, z4.y, z4.z, z4.w};
+      const float ee[4] = {e4.x, e4.y, e4.z, e4.w};
+      float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+      const float uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+      {
+        if (simple)
+          zz[c] += L.ir * (acc[c] * act_deriv(L.act, zz[c]) - ee[c]);
+        else
+        {
+          const float fb = L.a * acc[c] - ee[c];
+          if (L.v)
+          {
+            vv[c] = L.momentum_beta * vv[c] + (1.0f - L.momentum_beta) * fb;
+            zz[c] += L.ir * vv[c];
+          }
+          else
+            zz[c] += L.ir * fb;
+          if (residual)
+            zz[c] += L.ir * uu[c];
+        }
+      }
+      if (!simple && L.v)
+        *reinterpret_cast<float4*>(L.v + o) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      *reinterpret_cast<float4*>(L.z + o) = make_float4(zz[0], zz[1], zz[2], zz[3]);
+    }
+  }
+}
+
+// One entry of a weight update from the raw sum over the batch (the epilogue of
+// pc_gemm_kernel<OP_WG> for one element).
+__device__ __forceinline__ void weight_apply(const dpc_layer& L, size_t o, float sum, int batch,
+                                             int mode, int flags, bool simple)
+{
+  if (mode & WG_GRAD_ONLY)
+  {
+    L.g_W[o] = sum;
+    return;
+  }
+  const float Bf = (float)batch;
+  float w = L.W[o];
+  if (mode == WG_LEARN && L.opt != DPC_OPT_SGD)
+  {
+    float lr_wd = -1.0f;
+    if (L.opt == DPC_OPT_ADAMW)
+      lr_wd = L.lr * L.lmbda;
+    float mm = L.m_W[o], vv = L.v_W[o];
+    w = adam_update(w, -1.0f * L.a * sum, mm, vv, adam_step_size(L.lr, *L.t), lr_wd);
+    L.m_W[o] = mm;
+    L.v_W[o] = vv;
+  }
+  else
+  {
+    float alpha, decay = 1.0f;
+    if (mode == WG_DFA)
+    {
+      alpha = L.fl * L.a / Bf;
+      if ((flags & 1) && L.lmbda > 0.0f && L.fl != 0.0f)
+        decay = 1.0f - L.lmbda;
+    }
+    else
+    {
+      alpha = simple ? (L.lr / Bf) : (L.a * L.lr / Bf);
+      if (L.lmbda > 0.0f)
+        decay = 1.0f - L.lmbda;
+    }
+    if (decay != 1.0f)
+      w *= decay;
+    w = fmaf(alpha, sum, w);
+  }
+  L.W[o] = w;
+}
+
+// Weight update of a narrow layer (at most KC <= 16 output units, input width a multiple of 128:
+// the heads, e.g. W[10 x 1024] += alpha fe^T z over a batch of 4096).  The tiled kernel gives such
+// a layer size/64 blocks that each walk the whole batch; here the batch is split over warps and
+// over the CTAs of a cluster as in the Psi update, whose shape this product shares.
+template <int KC>
+__global__ void __launch_bounds__(256)
+    narrow_weight_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
+                         int flags, int mode)
+{
+  const int li = first + blockIdx.y;
+  const dpc_layer L = layers[li];
+  if (L.next_size <= 0)
+    return;
+  const bool simple = (L.flags & DPC_LAYER_INPUT_ACT) != 0;
+  const int base_mode = mode & ~WG_GRAD_ONLY;
+  if (base_mode == WG_DFA && (li + 1 >= n_layers || layers[li + 1].Psi == nullptr))
+    return; // DirectFeedbackUpdate is a no-op unless the layer above owns feedback weights
+  const int M = L.next_size, s = L.size;
+  if ((int)blockIdx.x * 128 >= s)
+    return;
+  const float* g = (simple && base_mode == WG_LEARN) ? layers[li + 1].e : L.fe;
+  const float* zin = simple ? L.zF : L.z;
+  __shared__ __align__(16) float es[128][KC];
+  __shared__ float part[4][4 * KC][32];
+  const int col = blockIdx.x * 128 + (threadIdx.x & 31) * 4;
+  float acc[4][KC];
+  if (!batch_outer4<KC>(zin, s, col, g, M, M, batch, acc, es, part))
+    return;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int k = 0; k < KC; ++k)
+      if (k < M)
+        weight_apply(L, (size_t)k * s + col + c, acc[c][k], batch, mode, flags, simple);
 }
 
 // Feedback-weight update Psi[l] (+)= (fl*a/B) z[l]^T e_T.  A block of 256 threads owns 64 rows of
