@@ -36,12 +36,13 @@ static int check_launch(dpc_ctx* ctx, const char* what)
 }
 
 // How many CTAs of a cluster share the batch rows of one block's columns in the batch reductions
-// (Psi update, bias column sums): doubled while the launch does not fill the SMs yet and every CTA
+// (Psi update, bias column sums): doubled while the launch has fewer than four CTAs per SM (a CTA's
+// time is one chain of dependent row loads: more, shorter chains hide more latency) and every CTA
 // keeps at least `min_rows` rows.  1 for launches over many layers.
 static int row_split(const dpc_ctx* ctx, long long blocks, int batch, int min_rows)
 {
   int R = 1;
-  while (R < 8 && blocks * R < ctx->sm_count && batch / (2 * R) >= min_rows)
+  while (R < 8 && blocks * R < 4LL * ctx->sm_count && batch / (2 * R) >= min_rows)
     R *= 2;
   return R;
 }
@@ -646,8 +647,16 @@ static int forward_simt(dpc_plan* p, int first, int count, int flags)
       }
       if (narrow)
       {
-        dim3 grid(cdiv(p->batch, NTHREADS / 32), 1, c);
-        narrow_forward_kernel<<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, flags, p->energy);
+        if (p->batch >= 2048)
+        {
+          dim3 grid(cdiv(p->batch, 2 * (NTHREADS / 32)), 1, c);
+          narrow_forward_kernel<2><<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, flags, p->energy);
+        }
+        else
+        {
+          dim3 grid(cdiv(p->batch, NTHREADS / 32), 1, c);
+          narrow_forward_kernel<1><<<grid, NTHREADS, 0, st>>>(p->d, f, p->n, p->batch, flags, p->energy);
+        }
       }
       else
       {

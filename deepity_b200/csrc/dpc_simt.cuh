@@ -169,9 +169,32 @@ __device__ __forceinline__ float rows_cluster_load(const float* own, uint32_t ra
 // kernel below gives such a layer one column of 64 x 64 tiles, i.e. batch/64 CTAs that each walk
 // all of K: latency-bound (96 us for 4096 x 10 x 1024 against 3 us of traffic).  Here a warp owns
 // one batch row: its lanes stride over K with 16-byte loads of the row and of the (L1-resident)
-// weight rows, the partial dot products are reduced by shuffles, and lane j finishes output unit
+// weight rows, the partial dot products are reduced by shuffles, and lane 2j finishes output unit
 // j with the same epilogue as the tiled kernel.  Needs size % 4 == 0 and 16-byte aligned z, W.
 // ---------------------------------------------------------------------------------------
+// Sums a[0..15] over the 32 lanes with 16 shuffles instead of 80: each step a lane hands the half
+// of its values that its partner keeps to the partner and adds the partner's to the half it
+// keeps.  Returns the total of a[(lane >> 1) & 15] (lanes 2n and 2n + 1 both end with unit n).
+__device__ __forceinline__ float warp_reduce16(float (&a)[16], int lane)
+{
+#pragma unroll
+  for (int w = 8; w >= 1; w >>= 1)
+  {
+    const bool upper = (lane & (2 * w)) != 0;
+#pragma unroll
+    for (int i = 0; i < w; ++i)
+    {
+      const float send = upper ? a[i] : a[i + w];
+      const float keep = upper ? a[i + w] : a[i];
+      a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2 * w);
+    }
+  }
+  return a[0] + __shfl_xor_sync(0xffffffffu, a[0], 1);
+}
+
+// RPW batch rows per warp (2 on large batches: every weight vector fetched from L1 then serves two
+// rows).
+template <int RPW>
 __global__ void __launch_bounds__(NTHREADS)
     narrow_forward_kernel(const dpc_layer* __restrict__ layers, int first, int n_layers, int batch,
                           int flags, double* energy)
@@ -183,25 +206,32 @@ __global__ void __launch_bounds__(NTHREADS)
   const int N = L.next_size, K = L.size;
   const dpc_layer* Lup = (li + 1 < n_layers) ? &layers[li + 1] : nullptr;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m = blockIdx.x * (NTHREADS / 32) + warp;
-  const bool row_ok = m < batch;
-  float acc[16];
+  const int m0 = (blockIdx.x * (NTHREADS / 32) + warp) * RPW;
+  float acc[RPW][16];
 #pragma unroll
-  for (int j = 0; j < 16; ++j)
-    acc[j] = 0.0f;
-  if (row_ok)
+  for (int r = 0; r < RPW; ++r)
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      acc[r][j] = 0.0f;
+  if (m0 < batch)
   {
-    // 1024 elements of the row at a time: the lane's eight 16-byte loads are all issued before the
-    // first use (4 KB in flight per warp), then every weight row is walked over the same chunk
-    const float* zrow = L.z + (size_t)m * K;
+    // 1024 elements of the rows at a time: the lane's eight 16-byte loads per row are all issued
+    // before the first use (4 KB in flight per row), then every weight row is walked over the
+    // same chunk
     for (int kc = 0; kc < K; kc += 1024)
     {
       const int k0 = kc + lane * 4;
-      float4 zv[8];
+      float4 zv[RPW][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        zv[i] = (k0 + i * 128 < K) ? *reinterpret_cast<const float4*>(zrow + k0 + i * 128)
-                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int r = 0; r < RPW; ++r)
+      {
+        const float* zrow = L.z + (size_t)(m0 + r) * K;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          zv[r][i] = (m0 + r < batch && k0 + i * 128 < K)
+                         ? *reinterpret_cast<const float4*>(zrow + k0 + i * 128)
+                         : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
 #pragma unroll
       for (int j = 0; j < 16; ++j)
       {
@@ -214,66 +244,64 @@ __global__ void __launch_bounds__(NTHREADS)
             if (k0 + i * 128 < K)
             {
               const float4 wv = __ldg(reinterpret_cast<const float4*>(wrow + i * 128));
-              acc[j] = fmaf(zv[i].x, wv.x, acc[j]);
-              acc[j] = fmaf(zv[i].y, wv.y, acc[j]);
-              acc[j] = fmaf(zv[i].z, wv.z, acc[j]);
-              acc[j] = fmaf(zv[i].w, wv.w, acc[j]);
+#pragma unroll
+              for (int r = 0; r < RPW; ++r)
+              {
+                acc[r][j] = fmaf(zv[r][i].x, wv.x, acc[r][j]);
+                acc[r][j] = fmaf(zv[r][i].y, wv.y, acc[r][j]);
+                acc[r][j] = fmaf(zv[r][i].z, wv.z, acc[r][j]);
+                acc[r][j] = fmaf(zv[r][i].w, wv.w, acc[r][j]);
+              }
             }
           }
         }
       }
     }
   }
-  // all lanes end up with every sum; lane j keeps sum j
-  float mine = 0.0f;
-#pragma unroll
-  for (int j = 0; j < 16; ++j)
-  {
-    float v = acc[j];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-      v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == j)
-      mine = v;
-  }
   float esum = 0.0f;
   const bool next_ce = Lup && (Lup->flags & DPC_LAYER_SOFTMAX_CE);
   const bool do_err = (flags & DPC_FWD_ERR_NEXT) && Lup && !next_ce;
   const bool do_fe = (flags & DPC_FWD_FE) && Lup && !(next_ce && (flags & DPC_FWD_ERR_NEXT));
   const bool do_copy = (flags & DPC_FWD_COPY_NEXT) && Lup;
-  if (row_ok && lane < N)
+#pragma unroll
+  for (int r = 0; r < RPW; ++r)
   {
-    const int n = lane;
-    const size_t o = (size_t)m * N + n;
-    const float pre = L.a * mine + L.b[n];
-    float mu, d = 1.0f;
-    if (do_fe)
-      act_both(L.act, pre, mu, d);
-    else
-      mu = act_fwd(L.act, pre);
-    if (L.flags & DPC_LAYER_RESIDUAL)
-      mu += L.z[o];
-    if (!(flags & DPC_FWD_TRANSIENT))
+    // lanes 2n and 2n+1 end with the sum of output unit n; the even one finishes it
+    const float mine = warp_reduce16(acc[r], lane);
+    const int m = m0 + r, n = lane >> 1;
+    if (m < batch && !(lane & 1) && n < N)
     {
-      const bool no_mu = do_copy && (flags & DPC_FWD_NO_MU);
-      if (L.preact && !(no_mu && (flags & DPC_FWD_NO_PREACT)))
-        L.preact[o] = pre;
-      if (!no_mu)
-        L.mu[o] = mu;
+      const size_t o = (size_t)m * N + n;
+      const float pre = L.a * mine + L.b[n];
+      float mu, d = 1.0f;
+      if (do_fe)
+        act_both(L.act, pre, mu, d);
+      else
+        mu = act_fwd(L.act, pre);
+      if (L.flags & DPC_LAYER_RESIDUAL)
+        mu += L.z[o];
+      if (!(flags & DPC_FWD_TRANSIENT))
+      {
+        const bool no_mu = do_copy && (flags & DPC_FWD_NO_MU);
+        if (L.preact && !(no_mu && (flags & DPC_FWD_NO_PREACT)))
+          L.preact[o] = pre;
+        if (!no_mu)
+          L.mu[o] = mu;
+      }
+      if (do_copy)
+        Lup->z[o] = mu;
+      float e = 0.0f;
+      if (do_err)
+      {
+        e = (do_copy ? mu : Lup->z[o]) - mu;
+        Lup->e[o] = e;
+        esum += e * e;
+      }
+      else if (do_fe)
+        e = Lup->e[o];
+      if (do_fe)
+        L.fe[o] = e * d;
     }
-    if (do_copy)
-      Lup->z[o] = mu;
-    float e = 0.0f;
-    if (do_err)
-    {
-      e = (do_copy ? mu : Lup->z[o]) - mu;
-      Lup->e[o] = e;
-      esum += e * e;
-    }
-    else if (do_fe)
-      e = Lup->e[o];
-    if (do_fe)
-      L.fe[o] = e * d;
   }
   if (flags & DPC_FWD_ENERGY)
     block_energy_add(do_err ? esum : 0.0f, energy);
